@@ -1,0 +1,178 @@
+/*
+ * neureka_cuda.h -- C ABI of libneureka_cuda, the CUDA (sm_100a) backend library for Neureka's
+ * convolution / broadcast / elementwise path.
+ *
+ * This is the boundary a JVM-side `CudaDevice` / `CudaBackend` binds (Panama FFM or JNI): plain
+ * pointers, sizes and int codes only. Every entry point names the reference interface it replaces;
+ * paths are relative to the reference project root, J = src/main/java/neureka.
+ *
+ * Conventions
+ *  - Every function returns an nk_status (0 = ok). A non-zero status leaves a message readable with
+ *    nk_last_error(). Nothing aborts the process and no kernel traps.
+ *  - A view descriptor ("cfg") is `const int32_t cfg[5*rank]`, exactly NDConfiguration.asInlineArray():
+ *    [ shape | strides | indicesMap | offset | spread ]  (J/ndim/config/NDConfiguration.java:335-345).
+ *    All offset arithmetic inside the library is 64-bit. Views are validated against the buffer size
+ *    before any launch; an out-of-range view yields NK_ERR_BOUNDS instead of a fault.
+ *  - `d` is Arg.DerivIdx exactly as the Java side holds it (J/backend/api/Call.java:107):
+ *    d < 0 forward, d >= 0 derivative / deconvolution variant.
+ *  - Kernels are asynchronous on the context's stream; nk_read() and nk_sync() synchronise
+ *    ("stream-ordered, sync on read", like the in-order queue of J/devices/opencl/OpenCLDevice.java:140-145).
+ *  - The library never computes on the CPU: without a usable CUDA device nk_device_open fails.
+ */
+#ifndef NEUREKA_CUDA_H
+#define NEUREKA_CUDA_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct nk_ctx nk_ctx; /* one CUDA device + one stream; replaces an OpenCLDevice's queue */
+typedef struct nk_buf nk_buf; /* one device allocation; replaces a cl_mem held by OpenCLDevice.cl_tsr */
+
+typedef enum {
+    NK_OK = 0,
+    NK_ERR_BAD_ARG = 1,     /* -> IllegalArgumentException */
+    NK_ERR_UNSUPPORTED = 2, /* dtype / rank / op not supported -> IllegalArgumentException */
+    NK_ERR_OOM = 3,         /* cudaErrorMemoryAllocation -> OutOfMemoryError-like */
+    NK_ERR_CUDA = 4,        /* any other CUDA failure -> IllegalStateException */
+    NK_ERR_TIMEOUT = 5,     /* a bounded device-side wait ran out */
+    NK_ERR_BOUNDS = 6       /* a view reaches outside its buffer -> IllegalArgumentException */
+} nk_status;
+
+typedef enum { NK_F32 = 0, NK_F64 = 1, NK_I8 = 2, NK_I16 = 3, NK_I32 = 4, NK_I64 = 5 } nk_dtype;
+
+/* Binary operators: Addition, Subtraction, Multiplication, Division, Modulo, Power
+ * (J/backend/main/operations/operator/*.java), IDY = AssignLeft's scalar form
+ * (J/backend/main/implementations/broadcast/CPUScalarBroadcastIdentity.java). */
+typedef enum { NK_OP_ADD = 0, NK_OP_SUB = 1, NK_OP_MUL = 2, NK_OP_DIV = 3, NK_OP_MOD = 4, NK_OP_POW = 5, NK_OP_IDY = 6,
+               /* handle*drain product for both derivative slots: the TestBroadcast implementation of
+                  src/test/java/testutility/UnitTester_Tensor.java:414-433; only valid for nk_broadcast */
+               NK_OP_MUL_BOTH = 7 } nk_op;
+
+/* The 23 ScalarFun ids (J/backend/main/implementations/fun/api/ScalarFun.java:5-29), alphabetical by id(). */
+typedef enum {
+    NK_FUN_ABS = 0, NK_FUN_CBRT, NK_FUN_COS, NK_FUN_EXP, NK_FUN_GASU, NK_FUN_GATU, NK_FUN_GAUS, NK_FUN_FAST_GAUS,
+    NK_FUN_GELU, NK_FUN_IDY, NK_FUN_LOG10, NK_FUN_LN, NK_FUN_QUAD, NK_FUN_RELU, NK_FUN_SELU, NK_FUN_SILU, NK_FUN_SIG,
+    NK_FUN_SIN, NK_FUN_SOFTPLUS, NK_FUN_SOFTSIGN, NK_FUN_SQRT, NK_FUN_TANH, NK_FUN_FAST_TANH, NK_FUN_COUNT
+} nk_fun;
+
+/* Which convolution kernel family a call is routed to. AUTO picks from the views; the others force a
+ * family (NK_ERR_UNSUPPORTED if the views do not qualify) -- a testing/measurement knob. */
+typedef enum { NK_CONV_AUTO = 0, NK_CONV_GENERIC = 1, NK_CONV_TILED = 2, NK_CONV_TMA = 3 } nk_conv_path;
+
+typedef struct {
+    char name[256];
+    uint64_t total_mem_bytes;
+    int32_t sm_count;
+    int32_t cc_major, cc_minor;
+    int32_t l2_bytes;
+    int32_t max_smem_per_block;
+    int32_t clock_khz;
+} nk_props;
+
+/* ---- lifecycle: replaces OpenCLPlatform/OpenCLDevice discovery + queue creation
+ *      (J/devices/opencl/OpenCLPlatform.java:60-110, J/devices/opencl/OpenCLDevice.java:140-160) ---- */
+int nk_device_count(int32_t* out_count);
+int nk_device_open(int32_t ordinal, nk_ctx** out_ctx);
+int nk_device_close(nk_ctx* ctx);                 /* Device.dispose(), J/devices/Device.java:155 */
+int nk_device_props(nk_ctx* ctx, nk_props* out);  /* OpenCLDevice.name()/globalMemSize()..., OpenCLDevice.java:728-900 */
+int nk_sync(nk_ctx* ctx);                         /* clFinish equivalent */
+void* nk_stream(nk_ctx* ctx);                     /* the cudaStream_t launches go to (for interop) */
+/* Message of the last failure on ctx (or of the calling thread when ctx is NULL). Never NULL. */
+const char* nk_last_error(nk_ctx* ctx);
+const char* nk_version(void);
+
+/* ---- memory: replaces OpenCLDevice._add/_store/free/access
+ *      (OpenCLDevice.java:355-405 store, :497-524 free, :553-594 allocate*, :616-632 overwrite,
+ *       :676-690 read; Device.Access J/devices/Device.java:305-407) ---- */
+int nk_alloc(nk_ctx* ctx, int32_t dtype, int64_t n_elems, nk_buf** out);    /* Device.allocate(DataType, size) */
+int nk_wrap(nk_ctx* ctx, int32_t dtype, void* device_ptr, int64_t n_elems, nk_buf** out); /* adopt foreign device memory, not owned */
+int nk_free(nk_ctx* ctx, nk_buf* buf);                                       /* Device.free; NULL is a no-op */
+int nk_buf_info(nk_buf* buf, void** device_ptr, int64_t* n_elems, int32_t* dtype);
+/* Access.write(item).intoRange(start, start+n): fill n elements with one value (allocateFromOne) */
+int nk_fill(nk_ctx* ctx, nk_buf* buf, double value, int64_t start, int64_t n);
+/* Access.writeFrom(array, host_off).intoRange(dev_start, dev_start+n); blocking w.r.t. the host array */
+int nk_write(nk_ctx* ctx, nk_buf* buf, const void* host, int64_t host_off, int64_t dev_start, int64_t n);
+/* Access.readArray(type, dev_start, n) / readAll; blocking */
+int nk_read(nk_ctx* ctx, nk_buf* buf, void* host, int64_t dev_start, int64_t n);
+/* device-to-device range copy on the stream (used by swap/actualize; OpenCLDevice.java:574-594) */
+int nk_copy(nk_ctx* ctx, nk_buf* dst, int64_t dst_start, nk_buf* src, int64_t src_start, int64_t n);
+/* page-locked host staging memory + asynchronous variants (new: the reference's transfers are all blocking) */
+int nk_host_alloc(size_t bytes, void** out_host);
+int nk_host_free(void* host);
+int nk_write_async(nk_ctx* ctx, nk_buf* buf, const void* pinned_host, int64_t host_off, int64_t dev_start, int64_t n);
+int nk_read_async(nk_ctx* ctx, nk_buf* buf, void* pinned_host, int64_t dev_start, int64_t n);
+
+/* ---- kernels: each replaces one CLImplementation + its .cl template ---- */
+
+/* Operations "x", "«x", "x»" on algorithm NDConvolution: replaces CLConvolution
+ * (J/backend/main/implementations/convolution/CLConvolution.java:10-32 + resources/kernels/convolution_template.cl)
+ * with the semantics of the CPU implementation (AbstractCPUConvolution.java:70-143 forward, :146-240 deconvolution).
+ * drn/src1/src2 = call.input(0..2) after ConvUtil's input rearrangement; all three have `rank` dims. */
+int nk_conv(nk_ctx* ctx, int32_t dtype, int32_t rank,
+            nk_buf* drn, const int32_t* cfg0, nk_buf* src1, const int32_t* cfg1, nk_buf* src2, const int32_t* cfg2,
+            int32_t d);
+
+/* Algorithm Broadcast: replaces CLBroadcast* (J/backend/main/implementations/broadcast/CLBroadcast.java:10-33 +
+ * kernels/broadcast_template.cl), semantics of CPUBroadcast.java:62-160. d<0: drn = f(a,b) with broadcasting;
+ * d>=0: (origin, handle, drain) reduction over the dims where origin is smaller. */
+int nk_broadcast(nk_ctx* ctx, int32_t op, int32_t dtype, int32_t rank,
+                 nk_buf* drn, const int32_t* cfg0, nk_buf* a, const int32_t* cfg1, nk_buf* b, const int32_t* cfg2,
+                 int32_t d);
+
+/* Algorithm BiElementwise: replaces CLBiElementwise* (J/backend/main/implementations/elementwise/CLBiElementwise.java:7-32 +
+ * kernels/elementwise_template.cl), semantics of CPUBiElementWise.java:56-140. */
+int nk_binary(nk_ctx* ctx, int32_t op, int32_t dtype, int32_t rank,
+              nk_buf* drn, const int32_t* cfg0, nk_buf* a, const int32_t* cfg1, nk_buf* b, const int32_t* cfg2,
+              int32_t d);
+
+/* Algorithm ElementwiseAlgorithm for the 23 activations and AssignLeft (fun = NK_FUN_IDY): replaces
+ * CLElementwiseFunction (J/backend/main/implementations/elementwise/CLElementwiseFunction.java:12-42 +
+ * kernels/activation_template.cl), semantics of CPUElementwiseFunction.java:30-116. */
+int nk_unary(nk_ctx* ctx, int32_t fun, int32_t dtype, int32_t rank,
+             nk_buf* drn, const int32_t* cfg0, nk_buf* src, const int32_t* cfg1, int32_t d);
+
+/* Algorithm BiScalarBroadcast: replaces CLScalarBroadcast* (J/backend/main/implementations/broadcast/CLScalarBroadcast.java:16-64 +
+ * kernels/scalarization_template.cl), semantics of CPUScalarBroadcast.java:29-75: drn = f(src, value). */
+int nk_scalar_binary(nk_ctx* ctx, int32_t op, int32_t dtype, int32_t rank,
+                     nk_buf* drn, const int32_t* cfg0, nk_buf* src, const int32_t* cfg1, double value, int32_t d);
+
+/* Algorithm ScalarBroadcast: replaces the inline OpenCL wiring of J/backend/main/algorithms/ScalarBroadcast.java:65-82 +
+ * kernels/scalar_broadcast.cl: every element of the drain view := fun(value) (or fun'(value) for d>=0).
+ * fun(value) is evaluated on the device by one thread and broadcast. */
+int nk_fill_fun(nk_ctx* ctx, int32_t fun, int32_t dtype, int32_t rank, nk_buf* drn, const int32_t* cfg0,
+                double value, int32_t d);
+
+/* Algorithm SumAlgorithm: replaces CLSum (J/backend/main/operations/linear/internal/opencl/CLSum.java:23-132):
+ * out[out_index] = sum of the n elements of the view, 128-wide tiles reduced recursively in the order of
+ * CPUSum (J/backend/main/operations/other/internal/CPUSum.java:26-76). */
+int nk_sum(nk_ctx* ctx, int32_t dtype, int32_t rank, nk_buf* src, const int32_t* cfg, nk_buf* out, int64_t out_index);
+
+/* ---- routing knobs / introspection (no reference counterpart; measurement support) ---- */
+int nk_set_conv_path(nk_ctx* ctx, int32_t path);        /* nk_conv_path */
+int nk_last_conv_path(nk_ctx* ctx, int32_t* out_path);   /* family the last nk_conv used */
+const char* nk_last_kernel(nk_ctx* ctx);                 /* name of the last kernel launched */
+int nk_launch_count(nk_ctx* ctx, uint64_t* out);         /* kernels launched by this ctx so far */
+int nk_timer_begin(nk_ctx* ctx);                         /* CUDA event on the ctx stream */
+int nk_timer_end(nk_ctx* ctx, float* out_ms);            /* second event + synchronise */
+
+/* ---- multi-GPU (no reference counterpart: the reference has no multi-device execution) ----
+ * One process per GPU. A rank exports a buffer; peers open it and use it as the drain of nk_conv, so a
+ * slab's results are stored straight into the owner's memory over NVLink (plain stores). */
+#define NK_IPC_HANDLE_BYTES 64
+int nk_ipc_export(nk_ctx* ctx, nk_buf* buf, uint8_t handle[NK_IPC_HANDLE_BYTES]);
+int nk_ipc_open(nk_ctx* ctx, const uint8_t handle[NK_IPC_HANDLE_BYTES], int32_t dtype, int64_t n_elems, nk_buf** out);
+
+/* ---- synthetic inputs: java.util.Random-compatible streams (host side) ----
+ * Constants and polar Gaussian as J/backend/main/implementations/elementwise/CPURandomization.java:12-15, :265-284.
+ * dist 0: uniform lo + (hi-lo)*next{Float|Double}(); dist 1: p0 + p1*nextGaussian(). One stream per call,
+ * row-major element order. */
+int nk_jrand_fill(int32_t dtype, int32_t dist, int64_t seed, double p0, double p1, void* host_out, int64_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NEUREKA_CUDA_H */

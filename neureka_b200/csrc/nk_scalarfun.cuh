@@ -1,0 +1,228 @@
+// Device-side scalar math of the elementwise family. The translation unit including this header is
+// compiled with -fmad=false: Neureka's CPU implementation is Java, which never contracts a*b+c, and the
+// F32 definitions of most functions are "evaluate in double, then cast" -- kept verbatim here so that
+// results agree with the reference to the last bit wherever the math library does.
+//
+// Formulas: src/main/java/neureka/backend/main/implementations/fun/Scalar*.java (one class per function),
+// FunUtil.java:8-29 (inverse square root), implementations/fun/api/CPUFun.java:7-9 (float default).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include "../../include/neureka_cuda.h"
+
+namespace nkf {
+
+__device__ __forceinline__ double inv_sqrt(double x) {
+    double xhalf = 0.5 * x;
+    long long i = __double_as_longlong(x);
+    i = 0x5fe6ec85e7de30daLL - (i >> 1);
+    x = __longlong_as_double(i);
+    x *= (1.5 - xhalf * x * x);
+    x *= (1.5 - xhalf * x * x);
+    x *= (1.5 - xhalf * x * x);
+    x *= (1.5 - xhalf * x * x);
+    return x;
+}
+__device__ __forceinline__ float inv_sqrt(float x) {
+    float xhalf = 0.5f * x;
+    int i = __float_as_int(x);
+    i = 0x5f3759df - (i >> 1);
+    x = __int_as_float(i);
+    x *= (1.5f - xhalf * x * x);
+    x *= (1.5f - xhalf * x * x);
+    return x;
+}
+
+#define NKF_SELU_ALPHA 1.6732632423543772848170429916717
+#define NKF_SELU_SCALE 1.0507009873554804934193349852946
+
+__device__ __forceinline__ double sig64(double x) { return 1.0 / (1.0 + exp(-x)); }
+__device__ __forceinline__ double tanh64(double x) { return 2 / (1 + exp(-x * 2)) - 1; }
+__device__ __forceinline__ float tanh32(float x) { return float(2 / (1 + exp(double(-x * 2))) - 1); }
+__device__ __forceinline__ double softsign64(double x) { return x / (1.0 + fabs(x)); }
+__device__ __forceinline__ float softsign32(float x) { return x / (1.0f + fabsf(x)); }
+__device__ __forceinline__ double selu64(double x) {
+    if (x > 0) return NKF_SELU_SCALE * x;
+    else if (x <= 0) return NKF_SELU_SCALE * NKF_SELU_ALPHA * (exp(x) - 1);
+    else return double(__int_as_float(0x7fc00000));
+}
+
+__device__ __forceinline__ double fun(int f, bool derive, double x) {
+    if (!derive) switch (f) {
+        case NK_FUN_ABS: return fabs(x);
+        case NK_FUN_CBRT: return cbrt(x);
+        case NK_FUN_COS: return cos(x);
+        case NK_FUN_EXP: return exp(x);
+        case NK_FUN_GASU: return softsign64(x * x * x);
+        case NK_FUN_GATU: return tanh64(x * x * x);
+        case NK_FUN_GAUS: return exp(-(x * x));
+        case NK_FUN_FAST_GAUS: return 1 / (1 + x * x);
+        case NK_FUN_GELU: return x * sig64(x * 1.702);
+        case NK_FUN_IDY: return x;
+        case NK_FUN_LOG10: return log10(x);
+        case NK_FUN_LN: return log(x);
+        case NK_FUN_QUAD: return x * x;
+        case NK_FUN_RELU: return x >= 0 ? x : x * .01;
+        case NK_FUN_SELU: return selu64(x);
+        case NK_FUN_SILU: return x * sig64(x);
+        case NK_FUN_SIG: return sig64(x);
+        case NK_FUN_SIN: return sin(x);
+        case NK_FUN_SOFTPLUS: return log(1.0 + exp(x));
+        case NK_FUN_SOFTSIGN: return softsign64(x);
+        case NK_FUN_SQRT: return sqrt(x);
+        case NK_FUN_TANH: return tanh64(x);
+        case NK_FUN_FAST_TANH: return x * inv_sqrt(1.0 + x * x);
+    }
+    else switch (f) {
+        case NK_FUN_ABS: return x < 0 ? -1.0 : 1.0;
+        case NK_FUN_CBRT: return 1 / (3 * pow(x, 2.0 / 3.0));
+        case NK_FUN_COS: return -sin(x);
+        case NK_FUN_EXP: return exp(x);
+        case NK_FUN_GASU: { double x2 = x * x, x6 = x2 * x2 * x2; return 3.0 * x2 / (2.0 * x2 * fabs(x) + x6 + 1.0); }
+        case NK_FUN_GATU: {
+            double x2 = x * x, x3 = x2 * x, temp = 3 * x2, t = tanh64(x3), tanh2 = t * t;
+            return -temp * tanh2 + temp;
+        }
+        case NK_FUN_GAUS: return -2 * x * exp(-(x * x));
+        case NK_FUN_FAST_GAUS: { double x2 = x * x; return -2 * x / (x2 * x2 + 2 * x2 + 1); }
+        case NK_FUN_GELU: { double s = sig64(x * 1.702), ds = s * (1.0 - s); return s + ds * x * 1.702; }
+        case NK_FUN_IDY: return 1;
+        case NK_FUN_LOG10: return 1 / (x * log(10.0));
+        case NK_FUN_LN: return 1.0 / x;
+        case NK_FUN_QUAD: return 2 * x;
+        case NK_FUN_RELU: return x >= 0 ? 1 : .01;
+        case NK_FUN_SELU:
+            if (x > 0) return NKF_SELU_SCALE;
+            else if (x <= 0) return NKF_SELU_SCALE * NKF_SELU_ALPHA * exp(x);
+            else return __longlong_as_double(0x7ff8000000000000LL);
+        case NK_FUN_SILU: { double s = sig64(x); return s + (x * s * (1.0 - s)); }
+        case NK_FUN_SIG: { double s = sig64(x); return s * (1 - s); }
+        case NK_FUN_SIN: return cos(x);
+        case NK_FUN_SOFTPLUS: return 1.0 / (1.0 + exp(-x));
+        case NK_FUN_SOFTSIGN: return 1.0 / (2.0 * fabs(x) + x * x + 1.0);
+        case NK_FUN_SQRT: return 0.5 * inv_sqrt(x);
+        case NK_FUN_TANH: { double t = tanh64(x); return 1 - t * t; }   // Math.pow(t, 2) == t*t
+        case NK_FUN_FAST_TANH: { double t1 = x * x, t2 = sqrt(1 + t1); return 1 / (t1 * t2 + t2); }
+    }
+    return __longlong_as_double(0x7ff8000000000000LL);
+}
+
+__device__ __forceinline__ float fun(int f, bool derive, float x) {
+    if (!derive) switch (f) {
+        case NK_FUN_ABS: return fabsf(x);
+        case NK_FUN_CBRT: return float(cbrt(double(x)));
+        case NK_FUN_EXP: return float(exp(double(x)));
+        case NK_FUN_GASU: return softsign32(x * x * x);
+        case NK_FUN_GATU: return tanh32(x * x * x);
+        case NK_FUN_FAST_GAUS: return 1 / (1 + x * x);
+        case NK_FUN_GELU: return float(double(x) * sig64(double(x) * 1.702));
+        case NK_FUN_IDY: return x;
+        case NK_FUN_LOG10: return float(log10(double(x)));
+        case NK_FUN_QUAD: return x * x;
+        case NK_FUN_RELU: return x >= 0 ? x : x * .01f;
+        case NK_FUN_SELU: return float(selu64(double(x)));
+        case NK_FUN_SILU: return float(double(x) * sig64(double(x)));
+        case NK_FUN_SIG: return float(sig64(double(x)));
+        case NK_FUN_SOFTSIGN: return softsign32(x);
+        case NK_FUN_SQRT: return float(sqrt(double(x)));
+        case NK_FUN_TANH: return tanh32(x);
+        case NK_FUN_FAST_TANH: return x * inv_sqrt(1.0f + x * x);
+        default: return float(fun(f, false, double(x)));  // cos, gaus, ln, sin, softplus
+    }
+    else switch (f) {
+        case NK_FUN_ABS: return x < 0.0f ? -1.0f : 1.0f;
+        case NK_FUN_CBRT: return 1 / (3 * float(pow(double(x), double(2.0f / 3.0f))));
+        case NK_FUN_EXP: return float(exp(double(x)));
+        case NK_FUN_GASU: { float x2 = x * x, x6 = x2 * x2 * x2; return 3.0f * x2 / (2.0f * x2 * fabsf(x) + x6 + 1.0f); }
+        case NK_FUN_GATU: {
+            float x2 = x * x, x3 = x2 * x, temp = 3 * x2;
+            double t = double(tanh32(x3));
+            float tanh2 = float(t * t);
+            return -temp * tanh2 + temp;
+        }
+        case NK_FUN_FAST_GAUS: { float x2 = x * x; return -2 * x / (x2 * x2 + 2 * x2 + 1); }
+        case NK_FUN_GELU: { float s = float(sig64(double(x) * 1.702)); float ds = s * (1.0f - s); return s + ds * x * 1.702f; }
+        case NK_FUN_IDY: return 1;
+        case NK_FUN_LOG10: return 1 / (x * float(log(10.0)));
+        case NK_FUN_LN: return 1.0f / x;
+        case NK_FUN_QUAD: return 2 * x;
+        case NK_FUN_RELU: return x >= 0 ? 1.0f : .01f;
+        case NK_FUN_SELU:
+            if (x > 0) return float(NKF_SELU_SCALE);
+            else if (x <= 0) return float(NKF_SELU_SCALE * NKF_SELU_ALPHA * exp(double(x)));
+            else return __int_as_float(0x7fc00000);
+        case NK_FUN_SILU: { float s = float(sig64(double(x))); return s + (x * s * (1.0f - s)); }
+        case NK_FUN_SIG: { float s = float(sig64(double(x))); return s * (1 - s); }
+        case NK_FUN_SOFTSIGN: return 1.0f / (2.0f * fabsf(x) + x * x + 1.0f);
+        case NK_FUN_SQRT: return 0.5f * inv_sqrt(x);
+        case NK_FUN_TANH: { double t = double(tanh32(x)); return float(1 - t * t); }
+        case NK_FUN_FAST_TANH: { float t1 = x * x; float t2 = float(sqrt(double(1 + t1))); return 1 / (t1 * t2 + t2); }
+        default: return float(fun(f, true, double(x)));  // cos, gaus, sin, softplus
+    }
+}
+
+// ---- binary operators ---------------------------------------------------------------------------
+// family 0: Broadcast  (CPUBroadcast{Addition,...,Power}.java)
+// family 1: BiElementwise (CPUBiElementWise{Addition,...,Power}.java)
+// family 2: tensor (op) scalar (CPUScalarBroadcast*.java, CPUScalaBroadcastPower.java)
+// Math.pow(b, 2) is written b*b (identical to HotSpot's result for exponent 2).
+__device__ __forceinline__ double mod(double a, double b) { return fmod(a, b); }
+__device__ __forceinline__ float mod(float a, float b) { return fmodf(a, b); }
+
+template <int FAMILY>
+__device__ __forceinline__ double bin(int op, int d, double a, double b) {
+    switch (op) {
+        case NK_OP_ADD:
+            if (FAMILY == 0) return a + b;
+            return d >= 0 ? 1.0 : a + b;
+        case NK_OP_SUB:
+            if (FAMILY == 0) return d == 0 ? a + b : a - b;
+            return d == 0 ? 1.0 : (d == 1 ? -1.0 : a - b);
+        case NK_OP_MUL: return d == 0 ? b : (d == 1 ? a : a * b);
+        case NK_OP_DIV:
+            if (d == 0) return 1.0 / b;
+            if (d == 1) return FAMILY == 1 ? -a / (b * b) : -(a / (b * b));
+            return a / b;
+        case NK_OP_MOD:
+            if (d == 0) return 1.0 / b;
+            if (d == 1) return FAMILY == 1 ? -a / (b * b) : -(a / (b * b));
+            return mod(a, b);
+        case NK_OP_POW:
+            if (d == 0) return (FAMILY == 0 ? a : b) * pow(a, b - 1);  // Broadcast multiplies by a (sic)
+            if (d == 1) return pow(a, b) * log(a);
+            return pow(a, b);
+        case NK_OP_IDY: return b;
+        case NK_OP_MUL_BOTH: return a * b;
+    }
+    return __longlong_as_double(0x7ff8000000000000LL);
+}
+
+template <int FAMILY>
+__device__ __forceinline__ float bin(int op, int d, float a, float b) {
+    switch (op) {
+        case NK_OP_ADD:
+            if (FAMILY == 0) return a + b;
+            return d >= 0 ? 1.0f : a + b;
+        case NK_OP_SUB:
+            if (FAMILY == 0) return d == 0 ? a + b : a - b;
+            return d == 0 ? 1.0f : (d == 1 ? -1.0f : a - b);
+        case NK_OP_MUL: return d == 0 ? b : (d == 1 ? a : a * b);
+        case NK_OP_DIV:
+            if (d == 0) return 1.0f / b;
+            if (d == 1) return float(-(double(a) / (double(b) * double(b))));
+            return a / b;
+        case NK_OP_MOD:
+            if (d == 0) return 1.0f / b;
+            if (d == 1) return float(-(double(a) / (double(b) * double(b))));
+            return mod(a, b);
+        case NK_OP_POW:
+            if (d == 0) return float(double(FAMILY == 0 ? a : b) * pow(double(a), double(b - 1)));
+            if (d == 1) return float(pow(double(a), double(b)) * log(double(a)));
+            return float(pow(double(a), double(b)));
+        case NK_OP_IDY: return b;
+        case NK_OP_MUL_BOTH: return a * b;
+    }
+    return __int_as_float(0x7fc00000);
+}
+
+}  // namespace nkf

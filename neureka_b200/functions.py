@@ -1,0 +1,333 @@
+"""The caller side of the path: a small `Function` layer that parses Neureka expressions such as
+"i0 x i1" or "tanh(i0*i1+i1)", prepares calls the way the reference's operations and algorithms do, and
+dispatches them to the CUDA implementations registered in `backend.CudaBackend`.
+
+Mirrored behaviour (reference file:line):
+ * operator precedence = ServiceLoader order of the operations, tightest first: ** / * % - + x «x x»
+   (src/main/resources/META-INF/services/neureka.backend.api.Operation, math/parsing/FunctionParser.java:144-197)
+ * n-ary chains execute pairwise, left nested (operator/Addition.java `reducePairwise`, linear/Convolution.java:136-151)
+ * nested functions are not fused: inner nodes are executed first (template/algorithms/AbstractDeviceAlgorithm.java:158-204)
+ * algorithm choice for operators: BiScalarBroadcast if the 2nd operand has one element or is virtual
+   (algorithms/BiScalarBroadcast.java:17-30), BiElementwise for equal shapes (BiElementwise.java:17-25), else
+   Broadcast (Broadcast.java:18-46)
+ * output shapes: conv |a-b|+1 (operations/ConvUtil.java:61-66), broadcast max per dim (Broadcast.java:76-95)
+ * rank padding: Permute.makeFit (operations/other/Permute.java:82-110)
+ * inputs that are not on the executing device are stored for the call and restored afterwards
+   (AbstractDeviceAlgorithm.executeOnCommonDevice, :427-449)
+There is no CPU execution in this package: a call needs at least one operand on a CudaDevice.
+"""
+from __future__ import annotations
+
+import re
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from . import _lib as L
+from . import backend as B
+from .backend import ExecutionCall
+from .device import CudaDevice
+from .tensor import Tensor
+
+# ---------------------------------------------------------------------------------------------------
+# AST + parser
+# ---------------------------------------------------------------------------------------------------
+_PRECEDENCE = ["**", "/", "*", "%", "-", "+", "x", "«x", "x»"]  # tightest first
+_FUN_ALIASES = {name: name for name in L.FUN_IDS}   # the operation identifiers are the ScalarFun ids
+_FUN_ALIASES["sumItems"] = "sumItems"
+
+
+class Node:
+    def __init__(self, kind: str, value=None, children: Optional[List["Node"]] = None):
+        self.kind = kind          # "input" | "const" | "op" | "fun"
+        self.value = value        # input index | constant | operator symbol | function id
+        self.children = children or []
+
+    def depends_on(self, i: int) -> bool:
+        if self.kind == "input":
+            return self.value == i
+        return any(c.depends_on(i) for c in self.children)
+
+    def __str__(self) -> str:
+        if self.kind == "input":
+            return f"I[{self.value}]"
+        if self.kind == "const":
+            return repr(self.value)
+        if self.kind == "fun":
+            return f"{self.value}({self.children[0]})"
+        return "(" + f" {self.value} ".join(str(c) for c in self.children) + ")"
+
+
+_TOKEN = re.compile(r"\s*(?:(?P<num>\d+\.\d*|\.\d+|\d+)|(?P<inp>[iI]\[?\s*(?P<idx>\d+)\s*\]?)|(?P<op>\*\*|<<x|x>>|«x|x»|[-+*/%x()])|(?P<name>[A-Za-z_][A-Za-z_0-9]*))")
+
+
+def _tokenize(expr: str):
+    pos, out = 0, []
+    expr = expr.strip()
+    while pos < len(expr):
+        m = _TOKEN.match(expr, pos)
+        if not m or m.end() == pos:
+            raise ValueError(f"cannot parse '{expr}' at position {pos}")
+        pos = m.end()
+        if m.group("num") is not None:
+            out.append(("num", float(m.group("num"))))
+        elif m.group("inp") is not None:
+            out.append(("inp", int(m.group("idx"))))
+        elif m.group("op") is not None:
+            op = {"<<x": "«x", "x>>": "x»"}.get(m.group("op"), m.group("op"))
+            out.append(("op", op))
+        else:
+            out.append(("name", m.group("name")))
+    return out
+
+
+class _Parser:
+    def __init__(self, tokens):
+        self.t = tokens
+        self.i = 0
+
+    def peek(self):
+        return self.t[self.i] if self.i < len(self.t) else (None, None)
+
+    def take(self):
+        tok = self.peek()
+        self.i += 1
+        return tok
+
+    def parse(self, level: int = len(_PRECEDENCE) - 1) -> Node:
+        if level < 0:
+            return self.atom()
+        sym = _PRECEDENCE[level]
+        parts = [self.parse(level - 1)]
+        while self.peek() == ("op", sym):
+            self.take()
+            parts.append(self.parse(level - 1))
+        if len(parts) == 1:
+            return parts[0]
+        return Node("op", sym, parts)
+
+    def atom(self) -> Node:
+        kind, val = self.take()
+        if kind == "num":
+            return Node("const", val)
+        if kind == "inp":
+            return Node("input", val)
+        if kind == "op" and val == "(":
+            n = self.parse()
+            if self.take() != ("op", ")"):
+                raise ValueError("missing ')'")
+            return n
+        if kind == "op" and val == "-":
+            return Node("op", "*", [Node("const", -1.0), self.atom()])
+        if kind == "name":
+            if val not in _FUN_ALIASES:
+                raise ValueError(f"unknown function '{val}'")
+            if self.take() != ("op", "("):
+                raise ValueError(f"'(' expected after {val}")
+            arg = self.parse()
+            if self.take() != ("op", ")"):
+                raise ValueError("missing ')'")
+            return Node("fun", _FUN_ALIASES[val], [arg])
+        raise ValueError(f"unexpected token {val!r}")
+
+
+# ---------------------------------------------------------------------------------------------------
+# helpers mirroring reference utilities
+# ---------------------------------------------------------------------------------------------------
+def as_tensor(x, like: Tensor) -> Tensor:
+    if isinstance(x, Tensor):
+        return x
+    t = Tensor.of(like.dtype, (1,), [x])
+    return t
+
+
+def shape_of_con(s1: Sequence[int], s2: Sequence[int]) -> Tuple[int, ...]:
+    """ConvUtil.shapeOfCon (operations/ConvUtil.java:61-66)."""
+    return tuple(abs(a - b) + 1 for a, b in zip(s1, s2))
+
+
+def _ends_from(shape: Sequence[int]) -> Tuple[int, int]:
+    """DimTrim.endsFrom: number of leading / trailing 1-axes."""
+    prefix = 0
+    for s in shape:
+        if s == 1: prefix += 1
+        else: break
+    postfix = 0
+    for s in reversed(shape):
+        if s == 1: postfix += 1
+        else: break
+    return prefix, postfix
+
+
+def make_fit(tensors: List[Tensor]) -> List[Tensor]:
+    """Permute.makeFit (operations/other/Permute.java:82-110): pad lower-rank tensors with 1-axes -- in front
+    when the largest tensor has at least as many leading as trailing 1-axes, else at the back."""
+    largest = max(t.rank for t in tensors)
+    shape = next(t.shape for t in tensors if t.rank == largest)
+    prefix, postfix = _ends_from(shape)
+    out = []
+    for t in tensors:
+        if t.rank == largest:
+            out.append(t)
+            continue
+        padding = largest - t.rank
+        if postfix <= prefix:
+            form = [-1] * padding + list(range(t.rank))
+        else:
+            form = list(range(t.rank)) + [-1] * padding
+        out.append(t.permute(*form))
+    return out
+
+
+def _common_device(tensors: Sequence[Optional[Tensor]]) -> CudaDevice:
+    for t in tensors:
+        if t is not None and t.device is not None:
+            return t.device
+    raise L.NeurekaCudaError(L.NK_ERR_UNSUPPORTED,
+                             "no operand lives on a CudaDevice: this package has no CPU execution path (use tensor.to(CudaDevice.get()))")
+
+
+def _execute_on_common_device(call: ExecutionCall, impl) -> Tensor:
+    """AbstractDeviceAlgorithm.executeOnCommonDevice (:427-449) + executeDeviceAlgorithm (:127-156)."""
+    dev = call.device
+    moved = []
+    for t in call.inputs:
+        if t is not None and not dev.has(t):
+            dev.store(t)
+            moved.append(t)
+    dev.approve(call)
+    result = impl.run(call)
+    for t in moved:
+        if t is not result and t._root() is not result._root() and not t.is_intermediate:
+            dev.restore(t)
+    return result
+
+
+def _new_output(dtype, shape, device: CudaDevice) -> Tensor:
+    out = Tensor.of(dtype, shape, 0)
+    out.set_is_virtual(False)
+    out.is_intermediate = True
+    device.store(out)
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# flat operation execution (call preparation + algorithm choice + dispatch)
+# ---------------------------------------------------------------------------------------------------
+def run_conv(a: Tensor, b: Tensor) -> Tensor:
+    """Operation "x" on NDConvolution: FunctionNode rank fitting (FunctionNode.java:92-93), output allocation of
+    Convolution's call preparation (linear/Convolution.java:91-103), then the device implementation."""
+    dev = _common_device([a, b])
+    a, b = make_fit([a, b])
+    out = _new_output(a.dtype, shape_of_con(a.shape, b.shape), dev)
+    call = ExecutionCall([out, a, b], "x", dev, -1)
+    return _execute_on_common_device(call, B.backend().implementation_for("x", B.ND_CONVOLUTION))
+
+
+def run_xconv(op: str, i0: Tensor, i1: Tensor, i2: Tensor) -> Tensor:
+    """Operations "«x" / "x»" (operations/ConvUtil.java:17-59, :68-88): rank fitting, DerivIdx 0,
+    `x»` reverses its inputs before dispatch; input(0) of the dispatched call is the drain."""
+    dev = _common_device([i0, i1, i2])
+    tensors = make_fit([i0, i1, i2])
+    for t in tensors:
+        t.set_is_virtual(False)
+    call = ExecutionCall(list(tensors), op, dev, 0)
+    if op == "x»":
+        call.rearrange_inputs(2, 1, 0)
+    return _execute_on_common_device(call, B.backend().implementation_for(op, B.ND_CONVOLUTION))
+
+
+def choose_algorithm(a: Tensor, b: Tensor) -> str:
+    if b.size == 1 or b.is_virtual:
+        return B.BI_SCALAR_BROADCAST
+    if a.shape == b.shape:
+        return B.BI_ELEMENTWISE
+    return B.BROADCAST
+
+
+def run_operator(sym: str, a: Tensor, b: Tensor, d: int = -1) -> Tensor:
+    dev = _common_device([a, b])
+    algo = choose_algorithm(a, b)
+    be = B.backend()
+    if algo == B.BI_SCALAR_BROADCAST:
+        out = _new_output(a.dtype, a.shape, dev)
+        call = ExecutionCall([out, a, b], sym, dev, d)
+    elif algo == B.BI_ELEMENTWISE:
+        out = _new_output(a.dtype, a.shape, dev)
+        call = ExecutionCall([out, a, b], sym, dev, d)
+    else:
+        if a.rank != b.rank:
+            a, b = make_fit([a, b])
+        for s1, s2 in zip(a.shape, b.shape):
+            if not (s1 == 1 or s2 == 1 or s1 == s2):
+                raise ValueError(f"shapes {a.shape} and {b.shape} cannot be broadcast")
+        shape = tuple(s2 if s1 == 1 else s1 for s1, s2 in zip(a.shape, b.shape))
+        out = _new_output(a.dtype, shape, dev)
+        call = ExecutionCall([out, a, b], sym, dev, d)
+    return _execute_on_common_device(call, be.implementation_for(sym, algo))
+
+
+def run_function(fid: str, x: Tensor, d: int = -1) -> Tensor:
+    """Activation operations (operations/functions/AbstractActivationOperation.java:23-96): ScalarBroadcast for a
+    virtual input, ScalarAlgorithm for a single element, else ElementwiseAlgorithm."""
+    dev = _common_device([x])
+    be = B.backend()
+    if fid == "sumItems":
+        call = ExecutionCall([None, x], fid, dev, d)
+        return _execute_on_common_device(call, be.implementation_for(fid, B.SUM_ALGORITHM))
+    out = _new_output(x.dtype, x.shape, dev)
+    if x.is_virtual:
+        algo = B.SCALAR_BROADCAST
+    elif x.size == 1:
+        algo = B.SCALAR_ALGORITHM
+    else:
+        algo = B.ELEMENTWISE
+    call = ExecutionCall([out, x], fid, dev, d)
+    return _execute_on_common_device(call, be.implementation_for(fid, algo))
+
+
+def assign(dst: Tensor, src: Tensor) -> Tensor:
+    """AssignLeft "<-" (operations/other/AssignLeft.java:32-99): strided copy into dst, in place."""
+    dev = _common_device([dst, src])
+    be = B.backend()
+    if src.size == 1 or src.is_virtual:
+        call = ExecutionCall([dst, dst, src], B.ASSIGN_LEFT, dev, -1)
+        return _execute_on_common_device(call, be.implementation_for(B.ASSIGN_LEFT, B.BI_SCALAR_BROADCAST))
+    call = ExecutionCall([dst, src], B.ASSIGN_LEFT, dev, -1)
+    return _execute_on_common_device(call, be.implementation_for(B.ASSIGN_LEFT, B.ELEMENTWISE))
+
+
+# ---------------------------------------------------------------------------------------------------
+# Function
+# ---------------------------------------------------------------------------------------------------
+class Function:
+    """Function.of(expression[, doAD]) (src/main/java/neureka/math/Function.java)."""
+
+    _cache = {}
+
+    def __init__(self, root: Node, do_ad: bool):
+        self.root = root
+        self.do_ad = do_ad
+
+    @staticmethod
+    def of(expression: str, do_ad: bool = True) -> "Function":
+        key = (expression, do_ad)
+        f = Function._cache.get(key)
+        if f is None:
+            p = _Parser(_tokenize(expression))
+            root = p.parse()
+            if p.i != len(p.t):
+                raise ValueError(f"trailing input in expression '{expression}'")
+            f = Function(root, do_ad)
+            Function._cache[key] = f
+        return f
+
+    def __str__(self) -> str:
+        return str(self.root)
+
+    def call(self, *inputs: Tensor) -> Tensor:
+        from . import autograd
+        return autograd.evaluate(self.root, list(inputs), self.do_ad)
+
+    __call__ = call
+    execute = call

@@ -1,0 +1,128 @@
+"""The reference's end-to-end known answers for the path, run through the Function layer on the CUDA device:
+Function.of("i0 x i1"), XConvLeft/XConvRight, backward() of convolutions, broadcasting + / - / *, tanh."""
+import numpy as np
+import pytest
+
+from neureka_b200.functions import Function
+from neureka_b200.tensor import Tensor
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_conv_operator_golden(device, kat, dt):
+    for v in kat["conv_forward"]:
+        x = Tensor.of(dt, v["a_shape"], v["a"]).to(device)
+        k = Tensor.of(dt, v["b_shape"], v["b"]).to(device)
+        y = x.conv(k)
+        assert y.shape == tuple(v["out_shape"]) and y.items.tolist() == [float(t) for t in v["out"]], v["src"]
+        z = Function.of("I0xi1")(x, k)
+        assert z.items.tolist() == [float(t) for t in v["out"]]
+
+
+def test_host_operand_is_stored_for_the_call_and_restored(device):
+    x = Tensor.of(np.float64, [3, 3], np.arange(1, 10)).to(device)
+    k = Tensor.of(np.float64, [2, 2], [1, 2, 0, -1])          # stays on the host
+    y = Function.of("i0 x i1")(x, k)
+    assert y.items.tolist() == [0, 2, 6, 8]
+    assert not k.is_outsourced and device.has(y)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_xconv_operators(device, kat, dt):
+    v = kat["xconv"][0]
+    t1 = Tensor.of(dt, v["drain_shape"], [0] * 6).to(device)
+    t2 = Tensor.of(dt, v["t1_shape"], v["t1"]).to(device)
+    t3 = Tensor.of(dt, v["t2_shape"], v["t2"]).to(device)
+    r = Function.of("i0<<xi1<<xi2")(t1, t2, t3)
+    assert r.items.tolist() == [float(x) for x in v["out"]]
+    t1 = Tensor.of(dt, v["drain_shape"], [0] * 6).to(device)
+    r = Function.of("i2x>>i1x>>i0")(t1, t2, t3)
+    assert r.items.tolist() == [float(x) for x in v["out"]]
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_conv_backward_golden(device, kat, dt):
+    for v in kat["conv_autograd"]:
+        a = Tensor.of(dt, v["a_shape"], v["a"]).set_rqs_gradient(True).to(device)
+        b = Tensor.of(dt, v["b_shape"], v["b"]).to(device)
+        z = Function.of("i0xi1")(a, b)
+        z.backward(Tensor.of(dt, v["error_shape"], v["error"]))
+        assert a.gradient.items.tolist() == [float(x) for x in v["grad_a"]], v["src"]
+
+
+def test_two_layer_convolution_chain(device, kat):
+    v = kat["conv_autograd_chain"]
+    dt = np.float64
+    i_a = Tensor.of(dt, v["i_a"]["shape"], v["i_a"]["data"]).to(device)
+    w_a = Tensor.of(dt, v["w_a"]["shape"], v["w_a"]["data"]).set_rqs_gradient(True).to(device)
+    w_b = Tensor.of(dt, v["w_b"]["shape"], v["w_b"]["data"]).set_rqs_gradient(True).to(device)
+    w_c = Tensor.of(dt, v["w_c"]["shape"], v["w_c"]["data"]).set_rqs_gradient(True).to(device)
+    conv = Function.of("i0 x i1")
+    o_a = conv(i_a, w_a)
+    o_b, o_c = conv(o_a, w_b), conv(o_a, w_c)
+    out = o_b * o_c
+    assert o_a.items.tolist() == v["o_a"] and o_b.items.tolist() == v["o_b"] and o_c.items.tolist() == v["o_c"]
+    assert out.items.tolist() == v["out"]
+    out.backward(Tensor.of(dt, [2, 1], 1.0))
+    assert w_b.gradient.items.tolist() == v["grad_w_b"]
+    assert (w_a.items + w_a.gradient.items).tolist() == v["w_a_after_apply"]
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_broadcast_autograd_table(device, kat, dt):
+    ops = {"+": lambda x, y: x + y, "-": lambda x, y: x - y, "*": lambda x, y: x * y, "rsub": lambda x, y: y - x}
+    for row in kat["broadcast_autograd"]:
+        wb = row["which_grad"] == "b"
+        a = Tensor.of(dt, [2, 2], [1, 2, 3, 4]).set_rqs_gradient(not wb).to(device)
+        b = Tensor.of(dt, row["b_shape"], [8, 9]).set_rqs_gradient(wb).to(device)
+        c = ops[row["op"]](a, b)
+        assert c.items.tolist() == [float(x) for x in row["c"]], row["src"]
+        c.backward(Tensor.of(dt, [2, 2], [5, -2, 7, 3]))
+        w = b if wb else a
+        assert w.gradient.shape == w.shape
+        assert w.gradient.items.tolist() == [float(x) for x in row["grad"]], row["src"]
+
+
+def test_tanh_chain_golden(device, kat):
+    v = kat["tanh_chain"]
+    x = Tensor.of(np.float64, [1], [v["x"]]).set_rqs_gradient(True).to(device)
+    z = Function.of("i0*100")(Function.of("tanh(i0)")(x))
+    assert round(float(z.item()), 4) == v["value_4dp"]
+    z.backward(Tensor.of(np.float64, [1], [1.0]))
+    assert round(float(x.gradient.item()), 4) == v["grad_4dp"]
+
+
+def test_scaled_config3_forward_and_reduced_gradients(device, oracle):
+    """BASELINE config 3 at a reduced size: y = tanh(i0*i1+i1) with a [n,1,k], b [1,m,k]; backward of sum(y).
+    Forward is checked against the oracle op by op (<= 1 ulp per op => compare the final result to the oracle's
+    own chain); the gradients are the mathematically reduced ones: da = sum_j g*b, db = sum_i g*(a+1)."""
+    import ctypes as C
+    from neureka_b200 import _lib as L
+    from neureka_b200.ndconf import NDConfiguration as ND
+    n, m, k = 24, 16, 160
+    dt = np.float32
+    a_h, b_h = np.zeros(n * k, dtype=dt), np.zeros(m * k, dtype=dt)
+    L.lib.nk_jrand_fill(L.NK_F32, 0, 3, -2.0, 2.0, a_h.ctypes.data_as(C.c_void_p), a_h.size)
+    L.lib.nk_jrand_fill(L.NK_F32, 0, 3, -2.0, 2.0, b_h.ctypes.data_as(C.c_void_p), b_h.size)
+    a = Tensor.of(dt, [n, 1, k], a_h).set_rqs_gradient(True).to(device)
+    b = Tensor.of(dt, [1, m, k], b_h).set_rqs_gradient(True).to(device)
+    y = Function.of("tanh(i0*i1+i1)")(a, b)
+    # oracle chain
+    co, ca, cb = ND.of_shape([n, m, k]), ND.of_shape([n, 1, k]), ND.of_shape([1, m, k])
+    t1, t2, ref = (np.zeros(co.size, dtype=dt) for _ in range(3))
+    oracle.broadcast("*", t1, co.as_inline_array(), a_h, ca.as_inline_array(), b_h, cb.as_inline_array())
+    oracle.broadcast("+", t2, co.as_inline_array(), t1, co.as_inline_array(), b_h, cb.as_inline_array())
+    oracle.unary("tanh", ref, co.as_inline_array(), t2, co.as_inline_array())
+    from helpers import ulp_diff
+    assert ulp_diff(y.items, ref).max() <= 1
+    s = y.sum()
+    assert float(s.item()) == pytest.approx(float(oracle.cpu_sum(y.items)), rel=1e-6)
+    s.backward()
+    g = np.zeros(co.size, dtype=dt)
+    oracle.unary("tanh", g, co.as_inline_array(), t2, co.as_inline_array(), d=0)
+    g3 = g.reshape(n, m, k).astype(np.float64)
+    da = (g3 * b_h.reshape(1, m, k)).sum(axis=1)
+    db = (g3 * (a_h.reshape(n, 1, k).astype(np.float64) + 1)).sum(axis=0)
+    np.testing.assert_allclose(a.gradient.items.reshape(n, k), da, rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(b.gradient.items.reshape(m, k), db, rtol=1e-5, atol=1e-5)

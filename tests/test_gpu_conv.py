@@ -1,0 +1,196 @@
+"""Parity of nk_conv (through the C ABI) with the CPU oracle: golden vectors, random shapes of rank 1..5 over
+dense / sliced / strided / column-major / permuted views, F32 and F64, forward and deconvolution.
+
+Tolerances (stated by the task): relative error <= 1e-5 (F32) / <= 1e-12 (F64). "Relative" is taken against the
+magnitude the sum can reach, |a|.|b| summed the same way (computed by the oracle on absolute values): that is
+the bound that holds for any summation order; a plain max-norm relative check is applied as well."""
+import numpy as np
+import pytest
+
+from helpers import gpu_conv, rand_view
+from neureka_b200 import _lib as L
+from neureka_b200.ndconf import Layout, NDConfiguration as ND
+
+pytestmark = pytest.mark.gpu
+TOL = {np.dtype(np.float32): 1e-5, np.dtype(np.float64): 1e-12}
+
+
+def check_conv(device, oracle, dt, c0, n0, a, c1, b, c2, d, path=L.NK_CONV_AUTO):
+    dt = np.dtype(dt)
+    ref = np.zeros(n0, dtype=dt)
+    oracle.conv(ref, c0.as_inline_array(), a, c1.as_inline_array(), b, c2.as_inline_array(), d=d, threads=4)
+    scale = np.zeros(n0, dtype=dt)
+    oracle.conv(scale, c0.as_inline_array(), np.abs(a), c1.as_inline_array(), np.abs(b), c2.as_inline_array(), d=d, threads=4)
+    sentinel = np.full(n0, 777.0, dtype=dt)
+    got = gpu_conv(device, sentinel, c0, a, c1, b, c2, d=d, path=path)
+    offs = c0.element_offsets()
+    untouched = np.ones(n0, dtype=bool)
+    untouched[offs] = False
+    assert np.all(got[untouched] == 777.0), "elements outside the drain view were written"
+    err = np.abs(got[offs].astype(np.float64) - ref[offs].astype(np.float64))
+    bound = TOL[dt] * np.maximum(scale[offs].astype(np.float64), np.finfo(dt).tiny)
+    assert np.all(err <= bound), f"max err {err.max()} vs bound {bound[err.argmax()]}"
+    m = np.abs(ref[offs]).max()
+    if m > 0:
+        assert err.max() / m <= TOL[dt] * 8
+    return got
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_golden_forward(device, kat, dt):
+    for v in kat["conv_forward"]:
+        out = gpu_conv(device, np.zeros(int(np.prod(v["out_shape"])), dtype=dt), ND.of_shape(v["out_shape"]),
+                       np.asarray(v["a"], dtype=dt), ND.of_shape(v["a_shape"]), np.asarray(v["b"], dtype=dt), ND.of_shape(v["b_shape"]))
+        assert out.tolist() == [float(x) for x in v["out"]], v["src"]
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_golden_constant_matrix_product(device, kat, dt):
+    v = kat["conv_forward_constant"][0]
+    a = np.full(int(np.prod(v["a_shape"])), v["a_fill"], dtype=dt)
+    b = np.full(int(np.prod(v["b_shape"])), v["b_fill"], dtype=dt)
+    out = gpu_conv(device, np.zeros(int(np.prod(v["out_shape"])), dtype=dt), ND.of_shape(v["out_shape"]), a, ND.of_shape(v["a_shape"]), b, ND.of_shape(v["b_shape"]))
+    assert np.all(out == v["out_fill"])
+
+
+def test_golden_column_major_and_slice(device, kat):
+    v = kat["conv_forward_column_major"][0]
+    ca, cb = ND.of_shape(v["a_shape"], Layout.COLUMN_MAJOR), ND.of_shape(v["b_shape"], Layout.COLUMN_MAJOR)
+    a_raw, b_raw = np.zeros(6), np.zeros(6)
+    a_raw[ca.element_offsets()] = v["a"]
+    b_raw[cb.element_offsets()] = v["b"]
+    out = gpu_conv(device, np.zeros(9), ND.of_shape(v["out_shape"]), a_raw, ca, b_raw, cb)
+    assert out.tolist() == [float(x) for x in v["out"]]
+    w = kat["conv_forward_sliced"][0]
+    sl = ND.of_shape(w["parent_shape"]).sliced(w["slice_shape"], w["slice_offset"], w["slice_spread"])
+    out = gpu_conv(device, np.zeros(1), ND.of_shape([1, 1]), np.asarray(w["parent"], dtype=np.float64), sl, np.asarray(w["b"], dtype=np.float64), ND.of_shape(w["b_shape"]))
+    assert out.tolist() == [20.0]
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_golden_xconv_and_autograd_vectors(device, kat, dt):
+    v = kat["xconv"][0]
+    out = gpu_conv(device, np.zeros(6, dtype=dt), ND.of_shape(v["drain_shape"]), np.asarray(v["t1"], dtype=dt), ND.of_shape(v["t1_shape"]),
+                   np.asarray(v["t2"], dtype=dt), ND.of_shape(v["t2_shape"]), d=0)
+    assert out.tolist() == [float(x) for x in v["out"]]
+    for w in kat["conv_autograd"]:
+        g = gpu_conv(device, np.zeros(int(np.prod(w["a_shape"])), dtype=dt), ND.of_shape(w["a_shape"]), np.asarray(w["b"], dtype=dt), ND.of_shape(w["b_shape"]),
+                     np.asarray(w["error"], dtype=dt), ND.of_shape(w["error_shape"]), d=0)
+        assert g.tolist() == [float(x) for x in w["grad_a"]], w["src"]
+
+
+def _random_conv_case(rng, rank, max_dim):
+    sa, sb = [], []
+    for _ in range(rank):
+        kind = rng.integers(0, 4)
+        big = int(rng.integers(1, max_dim + 1))
+        small = int(rng.integers(1, big + 1))
+        if kind == 0: sa.append(big); sb.append(big)          # summed dim
+        elif kind == 1: sa.append(big); sb.append(small)      # a is the image here
+        elif kind == 2: sa.append(small); sb.append(big)      # roles swapped in this dim
+        else: sa.append(big); sb.append(1)
+    return sa, sb
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("seed", range(6))
+def test_random_forward_any_rank_any_view(device, oracle, dt, seed):
+    rng = np.random.default_rng(100 + seed)
+    kinds = ["dense", "sliced", "strided", "colmajor", "permuted"]
+    for trial in range(10):
+        rank = int(rng.integers(1, 6))
+        sa, sb = _random_conv_case(rng, rank, [40, 12, 8, 6, 5][rank - 1])
+        so = [abs(x - y) + 1 for x, y in zip(sa, sb)]
+        c1, n1 = rand_view(rng, sa, kinds[int(rng.integers(0, 5))])
+        c2, n2 = rand_view(rng, sb, kinds[int(rng.integers(0, 5))])
+        c0, n0 = rand_view(rng, so, kinds[int(rng.integers(0, 3))])
+        a = rng.standard_normal(n1).astype(dt)
+        b = rng.standard_normal(n2).astype(dt)
+        check_conv(device, oracle, dt, c0, n0, a, c1, b, c2, d=-1)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("seed", range(4))
+def test_random_deconvolution(device, oracle, dt, seed):
+    """d >= 0 with arbitrary (even inconsistent) shape triples: whatever the CPU state machine computes, the
+    gather kernel must compute too."""
+    rng = np.random.default_rng(200 + seed)
+    kinds = ["dense", "sliced", "strided", "permuted"]
+    for trial in range(10):
+        rank = int(rng.integers(1, 5))
+        md = [24, 9, 6, 4][rank - 1]
+        if trial % 2 == 0:
+            # shapes of a real backward pass: forward o = |a-b|+1, then drain := a, t1 := b, t2 := error(o)
+            sa, sb = _random_conv_case(rng, rank, md)
+            so = [abs(x - y) + 1 for x, y in zip(sa, sb)]
+            s0, s1, s2 = (sa, sb, so) if trial % 4 == 0 else (sb, sa, so)
+        else:
+            s0, s1, s2 = ([int(rng.integers(1, md + 1)) for _ in range(rank)] for _ in range(3))
+        c0, n0 = rand_view(rng, s0, kinds[int(rng.integers(0, 3))])
+        c1, n1 = rand_view(rng, s1, kinds[int(rng.integers(0, 4))])
+        c2, n2 = rand_view(rng, s2, kinds[int(rng.integers(0, 4))])
+        t1 = rng.standard_normal(n1).astype(dt)
+        t2 = rng.standard_normal(n2).astype(dt)
+        check_conv(device, oracle, dt, c0, n0, t1, c1, t2, c2, d=0)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_long_reductions_take_the_split_kernel(device, oracle, dt):
+    """Few drain elements with long sums (dot products, kernel gradients): the split reduction + finish pass."""
+    rng = np.random.default_rng(7)
+    n = 250_000   # the reference benchmark's `vector_multiplication`: x of two equal vectors = dot product
+    a, b = rng.standard_normal(n).astype(dt), rng.standard_normal(n).astype(dt)
+    check_conv(device, oracle, dt, ND.of_shape([1]), 1, a, ND.of_shape([n]), b, ND.of_shape([n]), d=-1)
+    assert device.last_kernel() in ("nk_conv_finish_kernel", "nk_conv_reduce_kernel")
+    # gradient w.r.t. a small kernel: drain [5,5], t1 = image [64,64], t2 = error [60,60]
+    img, err = rng.standard_normal(64 * 64).astype(dt), rng.standard_normal(60 * 60).astype(dt)
+    check_conv(device, oracle, dt, ND.of_shape([5, 5]), 25, img, ND.of_shape([64, 64]), err, ND.of_shape([60, 60]), d=0)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("case", [
+    ([96, 200], [5, 5]), ([3, 70, 150], [1, 3, 3]), ([6, 40, 300], [6, 3, 3]), ([2, 5, 64, 130], [1, 5, 5, 5]),
+    ([5, 5], [96, 200]), ([20, 33, 140], [3, 7, 7]), ([1, 260], [1, 9]), ([300], [4]), ([40, 256], [40, 3]),
+    ([2, 3, 34, 40, 70], [1, 3, 3, 3, 3]),
+])
+def test_stencil_shapes_all_kernel_families(device, oracle, dt, case):
+    """Image-like shapes: AUTO must agree with the oracle and so must every family that accepts the call."""
+    rng = np.random.default_rng(11)
+    sa, sb = case
+    so = [abs(x - y) + 1 for x, y in zip(sa, sb)]
+    a = rng.standard_normal(int(np.prod(sa))).astype(dt)
+    b = rng.standard_normal(int(np.prod(sb))).astype(dt)
+    c0, c1, c2 = ND.of_shape(so), ND.of_shape(sa), ND.of_shape(sb)
+    got = {}
+    for path in (L.NK_CONV_AUTO, L.NK_CONV_GENERIC, L.NK_CONV_TILED, L.NK_CONV_TMA):
+        try:
+            got[path] = check_conv(device, oracle, dt, c0, c0.size, a, c1, b, c2, d=-1, path=path)
+        except ValueError as e:
+            assert path in (L.NK_CONV_TILED, L.NK_CONV_TMA) and "does not apply" in str(e)
+    assert L.NK_CONV_AUTO in got and L.NK_CONV_GENERIC in got
+
+
+def test_tiled_family_on_views(device, oracle):
+    """Sliced image with an offset (unaligned rows), a drain that is a slice of a larger output (the multi-GPU
+    assemble writes that way) and a column-major kernel."""
+    rng = np.random.default_rng(5)
+    for dt in (np.float32, np.float64):
+        parent = ND.of_shape([4, 70, 203])
+        c1 = parent.sliced([4, 64, 199], [0, 3, 1], [1, 1, 1])
+        c2 = ND.of_shape([4, 3, 5])
+        out_parent = ND.of_shape([1, 80, 200])
+        c0 = out_parent.sliced([1, 62, 195], [0, 9, 2], [1, 1, 1])
+        a = rng.standard_normal(parent.size).astype(dt)
+        b = rng.standard_normal(c2.size).astype(dt)
+        check_conv(device, oracle, dt, c0, out_parent.size, a, c1, b, c2, d=-1)
+
+
+def test_argument_errors_are_reported_not_faulted(device):
+    dt = np.float32
+    a, b = np.ones(16, dtype=dt), np.ones(4, dtype=dt)
+    with pytest.raises(ValueError, match="reaches elements"):
+        gpu_conv(device, np.zeros(4, dtype=dt), ND.of_shape([3, 3]), a, ND.of_shape([4, 4]), b, ND.of_shape([2, 2]))
+    with pytest.raises(ValueError, match="drain extent"):
+        gpu_conv(device, np.zeros(16, dtype=dt), ND.of_shape([4, 4]), a, ND.of_shape([4, 4]), b, ND.of_shape([2, 2]))
+    with pytest.raises(ValueError, match="rank"):
+        gpu_conv(device, np.zeros(1, dtype=dt), ND.of_shape([1] * 9), np.ones(1, dtype=dt), ND.of_shape([1] * 9), np.ones(1, dtype=dt), ND.of_shape([1] * 9))

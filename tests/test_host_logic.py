@@ -1,0 +1,109 @@
+"""Host-side logic that needs no GPU: NDConfiguration mirror, expression parser, rank fitting, shapes,
+algorithm choice and the backend registration table."""
+import numpy as np
+import pytest
+
+from neureka_b200.ndconf import Layout, NDConfiguration as ND
+
+
+def test_layouts_match_the_oracle(oracle):
+    rng = np.random.default_rng(1)
+    confs = [ND.of_shape(s) for s in ([1], [5], [3, 4], [1, 7], [7, 1], [2, 3, 4], [1, 1, 3], [2, 1, 3, 4])]
+    confs += [ND.of_shape(s, Layout.COLUMN_MAJOR) for s in ([3, 4], [2, 3, 4], [1, 5])]
+    confs += [ND.of_shape([4, 6]).sliced([3, 4], [1, 0], [1, 1]), ND.of_shape([4, 6]).sliced([2, 2], [0, 1], [2, 2]),
+              ND.of_shape([4, 6]).reshaped([1, 0]), ND.of_shape([2, 3, 4]).reshaped([2, 0, 1]), ND.of_shape([3, 4]).reshaped([-1, 0, 1])]
+    for c in confs:
+        arr = c.as_inline_array()
+        assert oracle.layout(arr) == c.layout().value, c
+        assert oracle.is_simple(arr) == c.is_simple(), c
+        offs = c.element_offsets()
+        for i in rng.integers(0, c.size, size=min(c.size, 16)):
+            assert oracle.index_of_index(arr, int(i)) == c.index_of_index(int(i)) == offs[i]
+
+
+def test_specialised_and_general_configurations_agree():
+    """NDConfiguration_Spec.groovy:41-127: all configuration classes are the same index function; here there
+    is only the general formula, checked against numpy strides."""
+    for shape in ([4], [3, 5], [2, 3, 4], [2, 3, 2, 2]):
+        c = ND.of_shape(shape)
+        ref = np.arange(c.size).reshape(shape)
+        assert (c.element_offsets() == ref.reshape(-1)).all()
+        perm = list(reversed(range(len(shape))))
+        p = c.reshaped(perm)
+        assert (p.element_offsets() == ref.transpose(perm).reshape(-1)).all()
+
+
+def test_construct_validation():
+    with pytest.raises(ValueError):
+        ND.of([2, 0], [1, 1], [1, 1], [1, 1], [0, 0])
+    with pytest.raises(ValueError):
+        ND.of([2, 1], [1, 1], [1, 1], [1, 2], [0, 0])
+
+
+def test_parser_precedence_and_chains():
+    from neureka_b200.functions import Function
+    assert str(Function.of("i0 x i1")) == "(I[0] x I[1])"
+    # 'x' binds looser than '+': the operands of x are the sums
+    assert str(Function.of("i0 + i1 x i2")) == "((I[0] + I[1]) x I[2])"
+    assert str(Function.of("tanh(i0*i1+i1)")) == "tanh(((I[0] * I[1]) + I[1]))"
+    assert str(Function.of("I[0] x>> I[1] x>> I[2]")) == "(I[0] x» I[1] x» I[2])"
+    assert str(Function.of("i0<<xi1<<xi2")) == "(I[0] «x I[1] «x I[2])"
+    assert str(Function.of("i0 ** i1 / i2")) == "((I[0] ** I[1]) / I[2])"
+    with pytest.raises(ValueError):
+        Function.of("nope(i0)")
+
+
+def test_make_fit_and_shapes():
+    from neureka_b200.functions import make_fit, shape_of_con, _ends_from
+    from neureka_b200.tensor import Tensor
+    assert shape_of_con([256, 256], [5, 5]) == (252, 252)
+    assert shape_of_con([64, 512, 512], [64, 3, 3]) == (1, 510, 510)
+    assert shape_of_con([2, 3, 1], [1, 3, 2]) == (2, 1, 2)
+    assert _ends_from([1, 7, 9, 2, 1, 1]) == (1, 2)
+    a = Tensor.of(np.float32, [2, 2], [1, 2, 3, 4])
+    # [2,2] has no leading/trailing 1-axes -> postfix <= prefix -> padding goes in front
+    fit = make_fit([a, Tensor.of(np.float32, [2], [8, 9])])
+    assert fit[1].shape == (1, 2)
+    # the largest tensor has more trailing than leading 1-axes -> padding goes to the back
+    big = Tensor.of(np.float32, [3, 1, 1], [1, 2, 3])
+    fit = make_fit([big, Tensor.of(np.float32, [3], [1, 2, 3])])
+    assert fit[1].shape == (3, 1, 1)
+
+
+def test_algorithm_choice():
+    from neureka_b200 import backend as B
+    from neureka_b200.functions import choose_algorithm
+    from neureka_b200.tensor import Tensor
+    a = Tensor.of(np.float32, [2, 2], [1, 2, 3, 4])
+    assert choose_algorithm(a, Tensor.of(np.float32, [1], [3])) == B.BI_SCALAR_BROADCAST
+    assert choose_algorithm(a, Tensor.of(np.float32, [2, 2], 3)) == B.BI_SCALAR_BROADCAST   # virtual
+    assert choose_algorithm(a, Tensor.of(np.float32, [2, 2], [1, 1, 1, 1])) == B.BI_ELEMENTWISE
+    assert choose_algorithm(a, Tensor.of(np.float32, [2, 1], [1, 1])) == B.BROADCAST
+
+
+def test_backend_registration_table_mirrors_the_opencl_backend():
+    from neureka_b200 import backend as B
+    be = B.CudaBackend()
+    pairs = set(be.pairs())
+    for sym in ["**", "/", "*", "%", "-", "+"]:
+        for algo in (B.BI_SCALAR_BROADCAST, B.BROADCAST, B.BI_ELEMENTWISE):
+            assert (sym, algo) in pairs
+    for sym in ["x", "«x", "x»"]:
+        assert (sym, B.ND_CONVOLUTION) in pairs
+    assert ("<", B.BI_SCALAR_BROADCAST) in pairs and ("<", B.ELEMENTWISE) in pairs
+    from neureka_b200 import _lib as L
+    assert len(L.FUN_IDS) == 23
+    for f in L.FUN_IDS:
+        assert (f, B.ELEMENTWISE) in pairs and (f, B.SCALAR_ALGORITHM) in pairs
+    with pytest.raises(L.NeurekaCudaError):
+        be.implementation_for("@", "MatMulAlgorithm")
+
+
+def test_no_cpu_fallback():
+    """A call whose operands all live on the host has nowhere to run: the package must refuse, not emulate."""
+    from neureka_b200 import _lib as L
+    from neureka_b200.functions import Function
+    from neureka_b200.tensor import Tensor
+    a = Tensor.of(np.float32, [2, 2], [1, 2, 3, 4])
+    with pytest.raises(L.NeurekaCudaError):
+        Function.of("i0 x i1")(a, a)
