@@ -1,0 +1,396 @@
+#!/usr/bin/env python
+"""Benchmark of the convolution hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl cuda|reference] [--assemble peer|nccl] [--scale S]
+
+Workload (config.workload): BASELINE config 5 -- the 4-D F32 convolution a[8,32,2048,2048] (uniform [0,1], seed 5)
+x k[1,32,5,5] (N(0,0.2), seed 6) -> [8,1,2044,2044], 53.48 GFLOP and 4.43 GB of algorithmic traffic per pass; it is the
+largest single-GPU configuration and the one that shards. With N > 1 (one process per GPU, launched by torchrun)
+the output rows (dim 2) are halo-split over the ranks; each rank holds its input slab (+4 halo rows) and, in the
+default `peer` mode, stores its results straight into rank 0's output buffer over NVLink (the assemble is the conv
+kernel's own epilogue); `nccl` keeps a local slab and gathers with NCCL. Total work is fixed => "scaling": "strong".
+
+A step = one full pass. `value` = GFLOP/s with slabs resident in HBM; `e2e` = the same pass from pinned host buffers
+(H2D of the slab, conv, D2H of the result slab inside the timed region). One JSON line on stdout (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+A_SHAPE = [8, 32, 2048, 2048]
+K_SHAPE = [1, 32, 5, 5]
+SPLIT_DIM = 2
+
+
+def shapes(scale: int):
+    """--scale S divides the image's spatial extents by S (smoke / profiling runs); S = 1 is the real workload."""
+    a = list(A_SHAPE)
+    a[2] //= scale
+    a[3] //= scale
+    k = list(K_SHAPE)
+    o = [abs(x - y) + 1 for x, y in zip(a, k)]
+    return a, k, o
+
+
+def read_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons, power = [], None, set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for t, line in self.rows:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                mhz = float(parts[0]); smax = float(parts[1])
+            except ValueError:
+                continue
+            if t0 - 0.05 <= t <= t1 + 0.05:
+                sm.append(mhz)
+                try:
+                    power.append(float(parts[2]))
+                except ValueError:
+                    pass
+                for n, v in zip(names, parts[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power) if power else None}
+
+
+def cpu_sample(a_host, k_host, a_shape, k_shape, o_shape, seconds_target: float, gpu_out=None):
+    """Times the CPU oracle (the line-faithful restatement of Neureka's CPU implementation) on a bounded sample of the
+    same workload: whole output rows of batch 0, split over all host threads like CPU.JVMExecutor splits the flat
+    output range. Returns (GFLOP/s, cores, description, max_rel_err vs gpu_out or None)."""
+    from neureka_b200.ndconf import NDConfiguration as ND
+    from oracle import oracle as O
+    cores = os.cpu_count() or 1
+    macs_per_out = k_shape[1] * k_shape[2] * k_shape[3]
+    cfg_o, cfg_a, cfg_k = (ND.of_shape(s).as_inline_array() for s in (o_shape, a_shape, k_shape))
+    out = np.zeros(int(np.prod(o_shape)), dtype=np.float32)
+    # calibrate on one row per thread, then size the sample for the target time
+    row = o_shape[3]
+
+    def run(n_rows):
+        n = n_rows * row
+        chunk = (n + cores - 1) // cores
+        ths = []
+        t0 = time.perf_counter()
+        for c in range(cores):
+            s, e = c * chunk, min(n, (c + 1) * chunk)
+            if s >= e:
+                break
+            th = threading.Thread(target=O.conv_range, args=(out, cfg_o, a_host, cfg_a, k_host, cfg_k, -1, s, e))
+            th.start()
+            ths.append(th)
+        for th in ths:
+            th.join()
+        return time.perf_counter() - t0, n
+
+    t_cal, n_cal = run(min(cores, o_shape[2]))
+    rate = n_cal / t_cal
+    rows = int(max(cores, min(o_shape[2], seconds_target * rate / row)))
+    t, n = run(rows)
+    gflops = 2.0 * macs_per_out * n / t / 1e9
+    err = None
+    if gpu_out is not None:
+        ref = out[:n].astype(np.float64)
+        err = float(np.abs(gpu_out[:n].astype(np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
+    return gflops, cores, f"first {rows} of {o_shape[2]} output rows of batch 0 ({n} outputs x {macs_per_out} MACs), {t:.1f} s", err
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--assemble", default="peer", choices=["peer", "nccl"])
+    ap.add_argument("--scale", type=int, default=1)
+    ap.add_argument("--conv-path", type=int, default=0, help="0 auto, 1 generic, 2 tiled, 3 tma")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--no-extra", action="store_true")
+    args = ap.parse_args()
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    a_shape, k_shape, o_shape = shapes(args.scale)
+    flops_total = 2.0 * np.prod(o_shape) * k_shape[1] * k_shape[2] * k_shape[3]
+    config = {"workload": f"cfg5: F32 a{a_shape} x k{k_shape} -> {o_shape}, halo-split on dim {SPLIT_DIM}",
+              "parallelism": f"slab{world}", "l2": "inputs larger than L2 (>= 512 MiB per GPU)"}
+
+    from neureka_b200 import _lib as L
+
+    # ------------------------------------------------------------------------------------------------------------
+    # reference arm: the CPU implementation of the path on the host cores (the JVM original cannot run on this box;
+    # the oracle is its line-faithful restatement)
+    # ------------------------------------------------------------------------------------------------------------
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        a_rows = a_shape[2]          # one whole batch plane set: the sample is cut from its output rows
+        sa = [1, a_shape[1], a_rows, a_shape[3]]
+        so = [1, 1, a_rows - k_shape[2] + 1, o_shape[3]]
+        a_host = np.zeros(int(np.prod(sa)), dtype=np.float32)
+        k_host = np.zeros(int(np.prod(k_shape)), dtype=np.float32)
+        L.lib.nk_jrand_fill(L.NK_F32, 0, 5, 0.0, 1.0, a_host.ctypes.data_as(C.c_void_p), a_host.size)
+        L.lib.nk_jrand_fill(L.NK_F32, 1, 6, 0.0, 0.2, k_host.ctypes.data_as(C.c_void_p), k_host.size)
+        vals = []
+        per = max(1.0, min(20.0, 120.0 / (steps + warmup)))
+        for i in range(warmup + steps):
+            g, cores, sample, _ = cpu_sample(a_host, k_host, sa, k_shape, so, per)
+            if i >= warmup:
+                vals.append(g)
+        v = float(np.mean(vals))
+        ms = 1e3 * flops_total / (v * 1e9)
+        line = {"metric": "nd_conv_gflops", "value": v, "unit": "GFLOP/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+                "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "impl": "reference", "config": config,
+                "cpu_baseline": {"value": v, "unit": "GFLOP/s", "cores": cores, "kind": "port",
+                                 "sample": sample + f" per step; ms_per_step extrapolates to the full {flops_total / 1e9:.2f} GFLOP pass"},
+                "e2e": {"value": v, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    # ------------------------------------------------------------------------------------------------------------
+    # CUDA arm
+    # ------------------------------------------------------------------------------------------------------------
+    from neureka_b200.device import CudaDevice
+    from neureka_b200.ndconf import NDConfiguration as ND
+    from neureka_b200.sharding import plan_slabs, slab_views
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group(backend="cpu:gloo,cuda:nccl")
+
+    dev = CudaDevice.get(local_rank)
+    ctx = dev.ctx
+    dev.set_conv_path(args.conv_path)
+
+    def barrier():
+        dev.sync()
+        if dist is not None:
+            dist.barrier()
+
+    halo = k_shape[SPLIT_DIM] - 1
+    slab = plan_slabs(o_shape[SPLIT_DIM], world, halo)[rank]
+    in_view, out_view, local_in_shape = slab_views(a_shape, k_shape, SPLIT_DIM, slab)
+    local_out_shape = list(out_view.shape)
+    n_in = int(np.prod(local_in_shape))
+    n_out_local = int(np.prod(local_out_shape))
+    n_out_full = int(np.prod(o_shape))
+
+    # ---- synthetic inputs: java.util.Random streams, each rank generates only its slab -----------------------
+    host_in = C.c_void_p()
+    L.check(L.lib.nk_host_alloc(n_in * 4, C.byref(host_in)))
+    host_out = C.c_void_p()
+    L.check(L.lib.nk_host_alloc(max(n_out_local, 1) * 4, C.byref(host_out)))
+    a_host = np.ctypeslib.as_array(C.cast(host_in, C.POINTER(C.c_float)), shape=(n_in,))
+    out_host = np.ctypeslib.as_array(C.cast(host_out, C.POINTER(C.c_float)), shape=(max(n_out_local, 1),))
+    plane = a_shape[2] * a_shape[3]
+    seg = slab.in_len * a_shape[3]
+    for pl in range(a_shape[0] * a_shape[1]):
+        start = pl * plane + slab.in_lo * a_shape[3]
+        ptr = C.c_void_p(host_in.value + pl * seg * 4)
+        L.lib.nk_jrand_fill_at(L.NK_F32, 0, 5, 0.0, 1.0, start, ptr, seg)
+    k_host = np.zeros(int(np.prod(k_shape)), dtype=np.float32)
+    L.lib.nk_jrand_fill(L.NK_F32, 1, 6, 0.0, 0.2, k_host.ctypes.data_as(C.c_void_p), k_host.size)
+
+    def alloc(n):
+        b = C.c_void_p()
+        L.check(L.lib.nk_alloc(ctx, L.NK_F32, int(n), C.byref(b)), ctx)
+        return b
+
+    d_in, d_k, d_out_local = alloc(n_in), alloc(k_host.size), alloc(max(n_out_local, 1))
+    L.check(L.lib.nk_write(ctx, d_in, host_in, 0, 0, n_in), ctx)
+    L.check(L.lib.nk_write(ctx, d_k, k_host.ctypes.data_as(C.c_void_p), 0, 0, k_host.size), ctx)
+
+    cfg_in = ND.of_shape(local_in_shape).as_inline_array()
+    cfg_k = ND.of_shape(k_shape).as_inline_array()
+    cfg_out_local = ND.of_shape(local_out_shape).as_inline_array()
+    cfg_out_in_full = out_view.as_inline_array()
+    pi = lambda arr: arr.ctypes.data_as(C.POINTER(C.c_int32))
+
+    # ---- where the assembled result lives ----------------------------------------------------------------------
+    d_full = None
+    torch_full = torch_local = None
+    if world == 1:
+        d_full = d_out_local  # the slab is the whole output
+    elif args.assemble == "peer":
+        handle = (C.c_uint8 * L.NK_IPC_HANDLE_BYTES)()
+        if rank == 0:
+            d_full = alloc(n_out_full)
+            L.check(L.lib.nk_ipc_export(ctx, d_full, handle), ctx)
+        box = [bytes(handle)]
+        dist.broadcast_object_list(box, src=0)
+        if rank != 0:
+            h = (C.c_uint8 * L.NK_IPC_HANDLE_BYTES).from_buffer_copy(box[0])
+            d_full = C.c_void_p()
+            L.check(L.lib.nk_ipc_open(ctx, h, L.NK_F32, n_out_full, C.byref(d_full)), ctx)
+    else:  # nccl: gather the local slabs on rank 0 through torch.distributed
+        import torch
+        ptr = C.c_void_p(); L.lib.nk_buf_info(d_out_local, C.byref(ptr), None, None)
+        stream = torch.cuda.ExternalStream(L.lib.nk_stream(ctx))
+        torch.cuda.set_stream(stream)
+        torch_local = torch.empty(n_out_local, dtype=torch.float32, device=f"cuda:{local_rank}")
+        wrapped = C.c_void_p()
+        L.check(L.lib.nk_wrap(ctx, L.NK_F32, C.c_void_p(torch_local.data_ptr()), n_out_local, C.byref(wrapped)), ctx)
+        d_out_nccl = wrapped
+        sizes = [int(np.prod(slab_views(a_shape, k_shape, SPLIT_DIM, s)[1].shape)) for s in plan_slabs(o_shape[SPLIT_DIM], world, halo)]
+        gather_list = [torch.empty(s, dtype=torch.float32, device=f"cuda:{local_rank}") for s in sizes] if rank == 0 else None
+
+    def conv_step_resident():
+        """One pass with slabs resident: conv into the assembled output (peer stores) or local slab (+ NCCL gather)."""
+        if n_out_local == 0:
+            return
+        if world == 1:
+            L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, d_out_local, pi(cfg_out_local), d_in, pi(cfg_in), d_k, pi(cfg_k), -1), ctx)
+        elif args.assemble == "peer":
+            L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, d_full, pi(cfg_out_in_full), d_in, pi(cfg_in), d_k, pi(cfg_k), -1), ctx)
+        else:
+            L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, d_out_nccl, pi(cfg_out_local), d_in, pi(cfg_in), d_k, pi(cfg_k), -1), ctx)
+            dist.gather(torch_local, gather_list, dst=0)
+
+    def conv_step_e2e():
+        """The same pass from host buffers: H2D of the slab, conv, D2H of the rank's result slab."""
+        if n_out_local == 0:
+            return
+        L.check(L.lib.nk_write_async(ctx, d_in, host_in, 0, 0, n_in), ctx)
+        L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, d_out_local, pi(cfg_out_local), d_in, pi(cfg_in), d_k, pi(cfg_k), -1), ctx)
+        L.check(L.lib.nk_read_async(ctx, d_out_local, host_out, 0, n_out_local), ctx)
+
+    def timed(fn, n_warm, n_steps):
+        """W untimed steps, then exactly K steps between two events on the launch stream, bracketed by barrier +
+        synchronise on both sides; returns (max-over-ranks ms, wall t0, wall t1, kernels this rank launched)."""
+        for _ in range(n_warm):
+            fn()
+        barrier()
+        n0 = dev.launch_count()
+        t0 = time.time()
+        L.check(L.lib.nk_timer_begin(ctx), ctx)
+        for _ in range(n_steps):
+            fn()
+        ms = C.c_float(0)
+        L.check(L.lib.nk_timer_end(ctx, C.byref(ms)), ctx)   # records the end event and synchronises on it
+        barrier()
+        t1 = time.time()
+        n1 = dev.launch_count()
+        m = float(ms.value)
+        if dist is not None:
+            import torch
+            t = torch.tensor([m], dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            m = float(t.item())
+        return m, t0, t1, n1 - n0
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms_total, t0, t1, launches = timed(conv_step_resident, max(warmup, 3), steps)
+    clocks = sampler.stop(t0, t1) if sampler else None
+    last_kernel = dev.last_kernel()
+    conv_family = dev.last_conv_path()
+    ms_step = ms_total / steps
+    value = flops_total / (ms_step * 1e-3) / 1e9
+
+    e2e_ms_total, _, _, _ = timed(conv_step_e2e, 1, max(2, min(steps, 5)))
+    e2e_ms = e2e_ms_total / max(2, min(steps, 5))
+    e2e_value = flops_total / (e2e_ms * 1e-3) / 1e9
+    h2d = n_in * 4
+    d2h = n_out_local * 4
+    if dist is not None:
+        import torch
+        t = torch.tensor([h2d, d2h, launches], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        h2d, d2h, launches = int(t[0].item()), int(t[1].item()), int(t[2].item())
+
+    if rank == 0:
+        peak, peak_kind = read_peaks()
+        # algorithmic bytes of rank 0's launch: its input slab + the kernel + its output slab, each touched once
+        alg_bytes = (n_in + k_host.size + n_out_local) * 4.0
+        alg_flops = 2.0 * n_out_local * k_shape[1] * k_shape[2] * k_shape[3]
+        kernel_ms = ms_step  # one conv kernel per step on this rank (peer mode / 1 GPU)
+        achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                    "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
+                    "kernel": last_kernel, "kernel_ms": kernel_ms, "algorithmic_bytes_per_launch": alg_bytes,
+                    "fp32_fma": {"achieved_tflops": alg_flops / (kernel_ms * 1e-3) / 1e12,
+                                 "nominal_peak_tflops": 148 * 128 * 2 * 1.965e9 / 1e12}}
+        line = {"metric": "nd_conv_gflops", "value": value, "unit": "GFLOP/s", "n_gpus": world, "steps": steps, "warmup": max(warmup, 3),
+                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": dict(config, assemble=("none" if world == 1 else args.assemble), conv_family=conv_family),
+                "e2e": {"value": e2e_value, "unit": "GFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+                "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks}
+        if world == 1:
+            # CPU baseline on a bounded sample of the same workload, checked against the GPU result on the way
+            L.check(L.lib.nk_read(ctx, d_out_local, host_out, 0, n_out_local), ctx)
+            g, cores, sample, err = cpu_sample(a_host, k_host, local_in_shape, k_shape, local_out_shape, args.cpu_seconds, gpu_out=out_host)
+            line["cpu_baseline"] = {"value": g, "unit": "GFLOP/s", "cores": cores, "kind": "port", "sample": sample,
+                                    "gpu_vs_cpu_max_rel_err_on_sample": err}
+            if not args.no_extra:
+                try:
+                    from neureka_b200.extra_bench import run_extra
+                    line["extra"] = run_extra(dev, peak)
+                except Exception as e:  # the headline line must survive a failing side measurement
+                    line["extra"] = {"error": repr(e)}
+        print(json.dumps(line))
+        sys.stdout.flush()
+
+    barrier()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -171,6 +171,10 @@ int nk_ipc_open(nk_ctx* ctx, const uint8_t handle[NK_IPC_HANDLE_BYTES], int32_t 
  * dist 0: uniform lo + (hi-lo)*next{Float|Double}(); dist 1: p0 + p1*nextGaussian(). One stream per call,
  * row-major element order. */
 int nk_jrand_fill(int32_t dtype, int32_t dist, int64_t seed, double p0, double p1, void* host_out, int64_t n);
+/* The same stream entered at element `start` (uniform only: the generator is jumped ahead), so that a rank can
+ * generate just its own slab of a large tensor. */
+int nk_jrand_fill_at(int32_t dtype, int32_t dist, int64_t seed, double p0, double p1, int64_t start,
+                     void* host_out, int64_t n);
 
 #ifdef __cplusplus
 }

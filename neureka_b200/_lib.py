@@ -86,6 +86,7 @@ SIGNATURES = {
     "nk_ipc_export": (C.c_int, [_vp, _vp, C.POINTER(C.c_uint8)]),
     "nk_ipc_open": (C.c_int, [_vp, C.POINTER(C.c_uint8), _i32, _i64, C.POINTER(_vp)]),
     "nk_jrand_fill": (C.c_int, [_i32, _i32, _i64, _dbl, _dbl, _vp, _i64]),
+    "nk_jrand_fill_at": (C.c_int, [_i32, _i32, _i64, _dbl, _dbl, _i64, _vp, _i64]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

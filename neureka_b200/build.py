@@ -29,6 +29,8 @@ SOURCES = [
     ("nk_elementwise.cu", ["-fmad=false"]),
     ("nk_conv.cu", []),
     ("nk_conv_tiled.cu", []),
+    ("nk_conv_tiled_f32.cu", []),
+    ("nk_conv_tiled_f64.cu", []),
     ("nk_jrand.cpp", ["-Xcompiler", "-ffp-contract=off"]),
 ]
 

@@ -38,11 +38,30 @@ struct JRandom {
 };
 }  // namespace
 
+// state after `steps` LCG steps: s -> A*s + C with (A, C) = (MULT, ADD) composed `steps` times (mod 2^48)
+static uint64_t lcg_jump(uint64_t s, uint64_t steps) {
+    uint64_t a = MULT, c = ADD, A = 1, C = 0;
+    while (steps) {
+        if (steps & 1) { A = (A * a) & MASK; C = (C * a + c) & MASK; }
+        c = ((a + 1) * c) & MASK;
+        a = (a * a) & MASK;
+        steps >>= 1;
+    }
+    return (A * s + C) & MASK;
+}
+
 extern "C" int nk_jrand_fill(int32_t dtype, int32_t dist, int64_t seed, double p0, double p1, void* host_out, int64_t n) {
-    if (host_out == nullptr || n < 0) return NK_ERR_BAD_ARG;
+    return nk_jrand_fill_at(dtype, dist, seed, p0, p1, 0, host_out, n);
+}
+
+extern "C" int nk_jrand_fill_at(int32_t dtype, int32_t dist, int64_t seed, double p0, double p1, int64_t start,
+                                void* host_out, int64_t n) {
+    if (host_out == nullptr || n < 0 || start < 0) return NK_ERR_BAD_ARG;
     if (dtype != NK_F32 && dtype != NK_F64) return NK_ERR_UNSUPPORTED;
     if (dist != 0 && dist != 1) return NK_ERR_BAD_ARG;
+    if (dist == 1 && start != 0) return NK_ERR_UNSUPPORTED;   // the polar method consumes a data-dependent number of steps
     JRandom r(seed);
+    if (start > 0) r.seed = lcg_jump(r.seed, uint64_t(start) * (dtype == NK_F32 ? 1u : 2u));
     if (dtype == NK_F32) {
         float* o = static_cast<float*>(host_out);
         if (dist == 0) { const float lo = float(p0), w = float(p1 - p0); for (int64_t i = 0; i < n; i++) o[i] = lo + w * r.next_float(); }

@@ -36,6 +36,18 @@ __device__ __forceinline__ float inv_sqrt(float x) {
 #define NKF_SELU_ALPHA 1.6732632423543772848170429916717
 #define NKF_SELU_SCALE 1.0507009873554804934193349852946
 
+// cbrt with one Newton step on the exactly computed residual x - y^3: the result is the correctly rounded
+// cube root in all but a vanishing fraction of cases, i.e. within half an ulp of what any conforming
+// Math.cbrt returns.
+__device__ __forceinline__ double cbrt_cr(double x) {
+    double y = cbrt(x);
+    if (x == 0.0 || !isfinite(x)) return y;
+    double y2 = y * y, e2 = fma(y, y, -y2);        // y^2 = y2 + e2
+    double y3 = y2 * y, e3 = fma(y2, y, -y3);      // y2*y = y3 + e3
+    double r = ((x - y3) - e3) - e2 * y;           // x - y^3
+    return y + r / (3.0 * y2);
+}
+
 __device__ __forceinline__ double sig64(double x) { return 1.0 / (1.0 + exp(-x)); }
 __device__ __forceinline__ double tanh64(double x) { return 2 / (1 + exp(-x * 2)) - 1; }
 __device__ __forceinline__ float tanh32(float x) { return float(2 / (1 + exp(double(-x * 2))) - 1); }
@@ -50,7 +62,7 @@ __device__ __forceinline__ double selu64(double x) {
 __device__ __forceinline__ double fun(int f, bool derive, double x) {
     if (!derive) switch (f) {
         case NK_FUN_ABS: return fabs(x);
-        case NK_FUN_CBRT: return cbrt(x);
+        case NK_FUN_CBRT: return cbrt_cr(x);
         case NK_FUN_COS: return cos(x);
         case NK_FUN_EXP: return exp(x);
         case NK_FUN_GASU: return softsign64(x * x * x);
@@ -110,7 +122,7 @@ __device__ __forceinline__ double fun(int f, bool derive, double x) {
 __device__ __forceinline__ float fun(int f, bool derive, float x) {
     if (!derive) switch (f) {
         case NK_FUN_ABS: return fabsf(x);
-        case NK_FUN_CBRT: return float(cbrt(double(x)));
+        case NK_FUN_CBRT: return float(cbrt_cr(double(x)));
         case NK_FUN_EXP: return float(exp(double(x)));
         case NK_FUN_GASU: return softsign32(x * x * x);
         case NK_FUN_GATU: return tanh32(x * x * x);

@@ -88,16 +88,20 @@ def gpu_scalar(device, op, drn, c0, a, c1, value, d=-1):
 
 
 def ulp_diff(x: np.ndarray, y: np.ndarray) -> np.ndarray:
-    """Distance in units in the last place between two float arrays of the same dtype (NaN == NaN)."""
+    """Distance in units in the last place between two float arrays of the same dtype, in exact integer
+    arithmetic (NaN == NaN counts as 0; distances beyond 2**62 saturate)."""
     assert x.dtype == y.dtype
     it = np.int32 if x.dtype == np.float32 else np.int64
-    xi = x.view(it).astype(np.int64) if it is np.int32 else x.view(it)
-    yi = y.view(it).astype(np.int64) if it is np.int32 else y.view(it)
-    # map the sign-magnitude float ordering onto a monotone integer line
-    sign = np.int64(np.iinfo(it).min)
-    xi = np.where(xi < 0, sign - xi, xi)
-    yi = np.where(yi < 0, sign - yi, yi)
-    dist = np.abs(xi.astype(np.float64) - yi.astype(np.float64))
+    xi = x.view(it).astype(np.int64)
+    yi = y.view(it).astype(np.int64)
+    lo = np.int64(np.iinfo(it).min)
+    # map the sign-magnitude float ordering onto a monotone integer line: negative floats -> -(magnitude)
+    xm = np.where(xi < 0, lo - xi, xi)
+    ym = np.where(yi < 0, lo - yi, yi)
+    same_side = (xm >= 0) == (ym >= 0)
+    near = np.abs(np.where(same_side, xm - ym, 0))
+    far = np.minimum(np.abs(xm.astype(np.float64)) + np.abs(ym.astype(np.float64)), 2.0 ** 62).astype(np.int64)
+    dist = np.where(same_side, near, far)
     both_nan = np.isnan(x) & np.isnan(y)
     return np.where(both_nan, 0, dist)
 
