@@ -29,8 +29,12 @@ SOURCES = [
     ("nk_elementwise.cu", ["-fmad=false"]),
     ("nk_conv.cu", []),
     ("nk_conv_tiled.cu", []),
-    ("nk_conv_tiled_f32.cu", []),
-    ("nk_conv_tiled_f64.cu", []),
+    ("nk_conv_tiled_inst_f32_ldgsts.cu", []),
+    ("nk_conv_tiled_inst_f32_tma4.cu", []),
+    ("nk_conv_tiled_inst_f32_tma8.cu", []),
+    ("nk_conv_tiled_inst_f64_ldgsts.cu", []),
+    ("nk_conv_tiled_inst_f64_tma4.cu", []),
+    ("nk_conv_tiled_inst_f64_tma8.cu", []),
     ("nk_jrand.cpp", ["-Xcompiler", "-ffp-contract=off"]),
 ]
 

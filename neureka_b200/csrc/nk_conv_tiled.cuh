@@ -7,16 +7,22 @@
 // the CTA's output coordinate or of its reduction loop.
 //
 // One CTA produces a TH x TW output tile for one outer output coordinate and walks the reduction loop
-// ("channels") with a multi-stage shared-memory pipeline: the (TH+KH-1) x (TW+KW-1) image tile of channel c+2
-// is in flight (cp.async, 16-byte chunks, zero-filled past the image edge) while channel c is consumed. A
-// thread owns RH x CW outputs (CW = one 128-bit vector) and slides over the tile rows so that every
-// shared-memory row segment it loads feeds up to KH output rows; the KH x KW weights of the current channel
-// sit in registers. Each input byte is fetched from HBM once per tile (+ halo); with few tiles and many
-// channels the channel range is split across CTAs and a second pass adds the partial planes in a fixed order.
+// ("channels") with a multi-stage shared-memory pipeline: while channel c is consumed, the (TH+KH-1) x (TW+KW-1)
+// image tiles of the next channels are in flight. Two loaders exist for the same compute code:
+//   * TMA  : one elected thread issues one cp.async.bulk.tensor per tile (tensor map over the image view, zero
+//            fill outside the image), completion on an mbarrier -- no per-thread address arithmetic at all;
+//   * LDGSTS: cp.async 16-byte (or element-wise) chunks with per-thread precomputed coordinates, for views whose
+//            base or strides are not 16-byte aligned or whose rank exceeds what a tensor map can describe.
+// A thread owns RH x CW outputs (CW = one 128-bit vector) and slides over the tile rows so that every
+// shared-memory row segment it loads feeds up to KH output rows; the KH x KW weights of the current channel sit
+// in registers. Each input byte is fetched from HBM once per tile (+ halo); with few tiles and many channels
+// the channel range is split across CTAs and a second pass adds the partial planes in a fixed order.
 #pragma once
+#include <cuda.h>
 #include "nk_conv_plan.h"
 
 #define NK_TILED_MAX_OUTER 6
+#define NK_TMA_SPIN_LIMIT (1u << 24)   // bounded mbarrier wait: ~ a second, then the kernel gives up and reports
 
 struct TiledPlan {
     int n_outer;
@@ -29,10 +35,14 @@ struct TiledPlan {
     int64_t sIy, sKy, sKx, sOy;
     int64_t bI, bK, bO;
     int tilesX, tilesY, splits;
-    int vec;       // 16-byte global->shared copies are legal for every chunk
+    int vec;       // LDGSTS: 16-byte global->shared copies are legal for every chunk
     int vec_out;   // 16-byte stores to the drain are legal
+    int has_y;     // the second-to-last dim is the tile's row dim (else tiles are one row high)
+    int tma_nd;    // TMA: dims of the tensor map (2..5)
+    int* status;   // TMA: host-mapped word, set non-zero when a bounded wait ran out
 };
 
+// ---- PTX wrappers -------------------------------------------------------------------------------------------
 __device__ __forceinline__ void nk_cp_async_16(void* smem, const void* gmem, int src_bytes) {
     unsigned s = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(src_bytes) : "memory");
@@ -49,50 +59,94 @@ __device__ __forceinline__ void nk_cp_async_commit() { asm volatile("cp.async.co
 template <int N>
 __device__ __forceinline__ void nk_cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
-template <class T, int KH, int KW>
+__device__ __forceinline__ void nk_mbar_init(uint64_t* bar, unsigned count) {
+    unsigned a = (unsigned)__cvta_generic_to_shared(bar);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(a), "r"(count) : "memory");
+}
+__device__ __forceinline__ void nk_mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    unsigned a = (unsigned)__cvta_generic_to_shared(bar);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(a), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ unsigned nk_mbar_try_wait(uint64_t* bar, unsigned parity) {
+    unsigned a = (unsigned)__cvta_generic_to_shared(bar), ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ void nk_fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
+__device__ __forceinline__ void nk_fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+// One tile load: coordinates are element indices, innermost first. No multicast, local memory only.
+__device__ __forceinline__ void nk_tma_load(void* smem, const CUtensorMap* map, uint64_t* bar, int nd, const int* c) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(smem), b = (unsigned)__cvta_generic_to_shared(bar);
+    unsigned long long m = reinterpret_cast<unsigned long long>(map);
+    if (nd == 2)
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+                     ::"r"(d), "l"(m), "r"(c[0]), "r"(c[1]), "r"(b) : "memory");
+    else if (nd == 3)
+        asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+                     ::"r"(d), "l"(m), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(b) : "memory");
+    else if (nd == 4)
+        asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
+                     ::"r"(d), "l"(m), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(b) : "memory");
+    else
+        asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];\n"
+                     ::"r"(d), "l"(m), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4]), "r"(b) : "memory");
+}
+
+template <class T, int KH, int KW, int RH_>
 struct TiledCfg {
     static constexpr int CW = 16 / int(sizeof(T));            // outputs per thread along x = one 128-bit vector
-    static constexpr int RH = 4;                              // output rows per thread
+    static constexpr int RH = RH_;                            // output rows per thread
     static constexpr int WARPS = 8;
     static constexpr int TW = 32 * CW;
     static constexpr int TH = WARPS * RH;
     static constexpr int HALO_W = ((KW - 1 + CW - 1) / CW) * CW;
     static constexpr int SW = TW + HALO_W;                    // shared row length, a multiple of CW
     static constexpr int SH = TH + KH - 1;
-    static constexpr int STAGES = 3;
+    static constexpr int STAGE_BYTES = ((SH * SW * int(sizeof(T)) + 127) / 128) * 128;
+    static constexpr int STAGES = (STAGE_BYTES * 4 <= 64 * 1024) ? 4 : 3;
     static constexpr int NS = CW + HALO_W;                    // row-segment values a thread loads
     static constexpr int WPAD = ((KH * KW + CW - 1) / CW) * CW;
     static constexpr bool WREG = KH * KW * int(sizeof(T)) <= 200;   // weights of one channel live in registers
+    static constexpr int CPR = SW / CW;                       // LDGSTS chunks per row
+    static constexpr int NIT = (SH * CPR + 255) / 256;        // LDGSTS chunks per thread
     static size_t smem_bytes(int NQ) {
-        return size_t(STAGES) * SH * SW * sizeof(T) + size_t(NQ) * WPAD * sizeof(T) + size_t(NQ) * 2 * sizeof(int64_t);
+        // [stages | mbarriers (64 B) | weights | channel table (3 x int64 per channel)]
+        return size_t(STAGES) * STAGE_BYTES + 64 + size_t(NQ) * WPAD * sizeof(T) + 16 + size_t(NQ) * 3 * sizeof(int64_t);
     }
 };
 
-template <class T, int KH, int KW>
+template <class T, int KH, int KW, int RH, bool TMA>
 __global__ void __launch_bounds__(256) nk_conv_tiled_kernel(T* __restrict__ out, T* __restrict__ partial,
-                                                            const T* __restrict__ I, const T* __restrict__ K, TiledPlan p) {
-    using C = TiledCfg<T, KH, KW>;
-    constexpr int CW = C::CW, RH = C::RH, TW = C::TW, TH = C::TH, SW = C::SW, SH = C::SH, STAGES = C::STAGES, NS = C::NS, WPAD = C::WPAD;
-    extern __shared__ __align__(16) unsigned char nk_smem[];
-    T* tiles = reinterpret_cast<T*>(nk_smem);
-    T* wsm = tiles + STAGES * SH * SW;
-    int64_t* ioff = reinterpret_cast<int64_t*>(wsm + size_t(p.NQ) * WPAD);   // image offset of channel c
+                                                            const T* __restrict__ I, const T* __restrict__ K,
+                                                            const TiledPlan p, const __grid_constant__ CUtensorMap tmap) {
+    using C = TiledCfg<T, KH, KW, RH>;
+    constexpr int CW = C::CW, TW = C::TW, TH = C::TH, SW = C::SW, SH = C::SH, STAGES = C::STAGES, NS = C::NS, WPAD = C::WPAD;
+    extern __shared__ __align__(128) unsigned char nk_smem[];
+    unsigned char* stage_base = nk_smem;
+    uint64_t* mbar = reinterpret_cast<uint64_t*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES);
+    T* wsm = reinterpret_cast<T*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES + 64);
+    // channel table: image offset, kernel offset, packed outer indices (for the tensor-map coordinates)
+    int64_t* ctab = reinterpret_cast<int64_t*>((reinterpret_cast<uintptr_t>(wsm + size_t(p.NQ) * WPAD) + 15) & ~uintptr_t(15));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    // ---- which tile / outer coordinate / channel range ------------------------------------------------
+    // ---- which tile / outer coordinate / channel range ----------------------------------------------------------
     int64_t bid = blockIdx.x;
     const int tx = int(bid % p.tilesX); bid /= p.tilesX;
     const int ty = int(bid % p.tilesY); bid /= p.tilesY;
     const int split = int(bid % p.splits); bid /= p.splits;
     const int64_t pflat = bid;
     int64_t baseI = p.bI, baseK = p.bK, baseO = p.bO;
+    int pidx[NK_TILED_MAX_OUTER];
     {
         int64_t rem = pflat;
         for (int k = p.n_outer - 1; k >= 0; k--) {
             int64_t idx = rem % p.oext[k];
             rem /= p.oext[k];
             baseI += idx * p.pI[k]; baseK += idx * p.pK[k]; baseO += idx * p.os[k];
+            pidx[k] = p.pI[k] != 0 ? int(idx) : 0;   // the image index follows the output index only where pI != 0
         }
     }
     const int x0 = tx * TW, y0 = ty * TH;
@@ -100,49 +154,82 @@ __global__ void __launch_bounds__(256) nk_conv_tiled_kernel(T* __restrict__ out,
     const int c_begin = split * cper;
     const int c_end = (c_begin + cper < p.NQ) ? c_begin + cper : p.NQ;
 
-    // ---- stage the channel offsets and this CTA's weights ---------------------------------------------
+    if (TMA && tid == 0) {
+        for (int s = 0; s < STAGES; s++) nk_mbar_init(&mbar[s], 1);
+        nk_fence_barrier_init();
+    }
+
+    // ---- stage the channel table and this CTA's weights ---------------------------------------------------------
     for (int c = c_begin + tid; c < c_end; c += blockDim.x) {
         int rem = c;
-        int64_t oi = 0, ok = 0;
+        int64_t oi = 0, ok = 0, packed = 0;
         for (int k = p.n_outer - 1; k >= 0; k--) {
             int q = rem % int(p.qext[k]);
             rem /= int(p.qext[k]);
             oi += q * p.qI[k]; ok += q * p.qK[k];
+            packed |= int64_t(q) << (16 * k);          // TMA family: at most 3 outer dims, each loop index < 65536
         }
-        ioff[c] = oi;
-        ioff[p.NQ + c] = ok;
+        ctab[c * 3 + 0] = oi;
+        ctab[c * 3 + 1] = ok;
+        ctab[c * 3 + 2] = packed;
     }
     __syncthreads();
     for (int e = tid; e < (c_end - c_begin) * WPAD; e += blockDim.x) {
         const int c = c_begin + e / WPAD, t = e % WPAD;
         T v = 0;
-        if (t < KH * KW) v = K[baseK + ioff[p.NQ + c] + (t / KW) * p.sKy + (t % KW) * p.sKx];
+        if (t < KH * KW) v = K[baseK + ctab[c * 3 + 1] + (t / KW) * p.sKy + (t % KW) * p.sKx];
         wsm[size_t(c) * WPAD + t] = v;
     }
 
-    // ---- image tile loader ----------------------------------------------------------------------------
-    auto load_stage = [&](int stage, int c) {
-        T* dst = tiles + stage * SH * SW;
-        const T* src = I + baseI + ioff[c];
-        constexpr int CPR = SW / CW;   // chunks per row
-        for (int id = tid; id < SH * CPR; id += 256) {
-            const int row = id / CPR, col = (id - row * CPR) * CW;
+    // ---- loaders ------------------------------------------------------------------------------------------------
+    // LDGSTS: the chunk coordinates of a thread do not depend on the channel -- compute them once
+    int l_soff[TMA ? 1 : C::NIT], l_bytes[TMA ? 1 : C::NIT];
+    int64_t l_goff[TMA ? 1 : C::NIT];
+    if (!TMA) {
+#pragma unroll
+        for (int it = 0; it < C::NIT; it++) {
+            const int id = tid + it * 256;
+            const int row = id / C::CPR, col = (id - row * C::CPR) * CW;
             const int gy = y0 + row, gx = x0 + col;
-            int valid = (gy < p.IH) ? (p.IW - gx) : 0;
+            int valid = (id < SH * C::CPR && gy < p.IH) ? (p.IW - gx) : 0;
             valid = valid < 0 ? 0 : (valid > CW ? CW : valid);
-            const T* g = src + (valid > 0 ? (int64_t(gy) * p.sIy + gx) : 0);
-            T* s = dst + row * SW + col;
+            l_soff[it] = (id < SH * C::CPR) ? (row * SW + col) : -1;
+            l_bytes[it] = valid * int(sizeof(T));
+            l_goff[it] = valid > 0 ? (int64_t(gy) * p.sIy + gx) : 0;
+        }
+    }
+    auto ldgsts_stage = [&](int stage, int c) {
+        T* dst = reinterpret_cast<T*>(stage_base + size_t(stage) * C::STAGE_BYTES);
+        const T* src = I + baseI + ctab[c * 3 + 0];
+#pragma unroll
+        for (int it = 0; it < C::NIT; it++) {
+            if (l_soff[it] < 0) continue;
+            T* s = dst + l_soff[it];
+            const T* g = src + l_goff[it];
             if (p.vec) {
-                nk_cp_async_16(s, g, valid * int(sizeof(T)));
+                nk_cp_async_16(s, g, l_bytes[it]);
             } else {
 #pragma unroll
                 for (int e = 0; e < CW; e++) {
-                    const int ok = e < valid ? int(sizeof(T)) : 0;
+                    const int ok = (e * int(sizeof(T)) < l_bytes[it]) ? int(sizeof(T)) : 0;
                     if (sizeof(T) == 4) nk_cp_async_4(s + e, g + (ok ? e : 0), ok);
                     else nk_cp_async_8(s + e, g + (ok ? e : 0), ok);
                 }
             }
         }
+    };
+    int issued = 0;                             // tiles requested so far (thread 0)
+    auto tma_stage = [&](int stage, int c) {   // executed by thread 0 only
+        int coord[5];
+        coord[0] = x0;
+        int n = 1;
+        if (p.has_y) coord[n++] = y0;
+        const int64_t packed = ctab[c * 3 + 2];
+        for (int k = p.n_outer - 1; k >= 0; k--) coord[n++] = pidx[k] + int((packed >> (16 * k)) & 0xffff);
+        // without a row dim in the map the box is a single row; the other tile rows are never stored from
+        nk_mbar_expect_tx(&mbar[stage], unsigned((p.has_y ? SH : 1) * SW * sizeof(T)));
+        nk_tma_load(stage_base + size_t(stage) * C::STAGE_BYTES, &tmap, &mbar[stage], p.tma_nd, coord);
+        issued++;
     };
 
     T acc[RH][CW];
@@ -151,26 +238,57 @@ __global__ void __launch_bounds__(256) nk_conv_tiled_kernel(T* __restrict__ out,
 #pragma unroll
         for (int x = 0; x < CW; x++) acc[i][x] = T(0);
 
+    __syncthreads();   // weights + table + barrier init visible
+    if (TMA) {
+        if (tid == 0) {
+            nk_fence_proxy_async();
+            for (int s = 0; s < STAGES - 1; s++)
+                if (c_begin + s < c_end) tma_stage(s, c_begin + s);
+        }
+    } else {
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; s++) {
-        if (c_begin + s < c_end) load_stage(s, c_begin + s);
-        nk_cp_async_commit();
-    }
-
-    for (int c = c_begin; c < c_end; c++) {
-        nk_cp_async_wait<STAGES - 2>();
-        __syncthreads();   // tile c has landed for everyone; everyone is done reading the stage refilled below
-        {
-            const int nxt = c + STAGES - 1;
-            if (nxt < c_end) load_stage((nxt - c_begin) % STAGES, nxt);
+        for (int s = 0; s < STAGES - 1; s++) {
+            if (c_begin + s < c_end) ldgsts_stage(s, c_begin + s);
             nk_cp_async_commit();
         }
-        const T* tile = tiles + ((c - c_begin) % STAGES) * SH * SW + (warp * RH) * SW + lane * CW;
+    }
+
+    bool gave_up = false;
+    for (int c = c_begin; c < c_end; c++) {
+        const int it = c - c_begin;
+        const int stage = it % STAGES;
+        if (TMA) {
+            // bounded wait for the tile of channel c; on expiry: flag, stop consuming, fall through to the exit
+            const unsigned parity = unsigned(it / STAGES) & 1u;
+            unsigned spins = 0;
+            while (!nk_mbar_try_wait(&mbar[stage], parity)) {
+                if (++spins > NK_TMA_SPIN_LIMIT) { gave_up = true; break; }
+            }
+            if (gave_up && p.status) atomicExch(p.status, 1);
+            // everyone is past the previous channel's reads before its stage is handed back to the copy engine;
+            // the vote makes the give-up decision uniform across the CTA
+            gave_up = __syncthreads_or(gave_up) != 0;
+            if (gave_up) break;
+            if (tid == 0) {
+                const int nxt = c + STAGES - 1;
+                if (nxt < c_end) tma_stage((nxt - c_begin) % STAGES, nxt);
+            }
+        } else {
+            nk_cp_async_wait<STAGES - 2>();
+            __syncthreads();   // tile c has landed for everyone; everyone is done reading the stage refilled below
+            const int nxt = c + STAGES - 1;
+            if (nxt < c_end) ldgsts_stage((nxt - c_begin) % STAGES, nxt);
+            nk_cp_async_commit();
+        }
+        const T* tile = reinterpret_cast<const T*>(stage_base + size_t(stage) * C::STAGE_BYTES) + (warp * RH) * SW + lane * CW;
         const T* wc = wsm + size_t(c) * WPAD;
-        T w[C::WREG ? KH * KW : 1];
+        T w[C::WREG ? WPAD : CW];
         if (C::WREG) {
 #pragma unroll
-            for (int t = 0; t < KH * KW; t++) w[t] = wc[t];
+            for (int v = 0; v < WPAD / CW; v++) {
+                if (sizeof(T) == 4) *reinterpret_cast<float4*>(&w[v * CW]) = *reinterpret_cast<const float4*>(wc + v * CW);
+                else *reinterpret_cast<double2*>(&w[v * CW]) = *reinterpret_cast<const double2*>(wc + v * CW);
+            }
         }
 #pragma unroll
         for (int j = 0; j < RH + KH - 1; j++) {
@@ -194,9 +312,23 @@ __global__ void __launch_bounds__(256) nk_conv_tiled_kernel(T* __restrict__ out,
             }
         }
     }
-    nk_cp_async_wait<0>();
+    if (!TMA) nk_cp_async_wait<0>();
+    if (TMA && gave_up) {
+        // Requested copies may still be writing into this CTA's shared memory: thread 0 waits for each of the
+        // last STAGES requests (bounded) before anyone exits; nothing is stored.
+        if (tid == 0) {
+            for (int j = (issued > STAGES ? issued - STAGES : 0); j < issued; j++) {
+                unsigned spins = 0;
+                while (!nk_mbar_try_wait(&mbar[j % STAGES], unsigned(j / STAGES) & 1u)) {
+                    if (++spins > NK_TMA_SPIN_LIMIT) break;
+                }
+            }
+        }
+        __syncthreads();
+        return;
+    }
 
-    // ---- epilogue ---------------------------------------------------------------------------------------
+    // ---- epilogue -----------------------------------------------------------------------------------------------
     const int ox = x0 + lane * CW;
 #pragma unroll
     for (int i = 0; i < RH; i++) {
@@ -243,11 +375,20 @@ __global__ void __launch_bounds__(256) nk_conv_tiled_finish_kernel(T* __restrict
     }
 }
 
-template <class T, int KH, int KW>
-int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p) {
-    using C = TiledCfg<T, KH, KW>;
+// Host side of a TMA launch: everything needed to encode the tensor map of the image view.
+struct TmaImage {
+    const void* base;            // address of element (0,..,0) of the view
+    int nd;                      // dims, innermost first
+    uint64_t dims[5];
+    uint64_t strides_bytes[5];   // strides_bytes[0] is the element size
+};
+int nk_tma_encode(nk_ctx* ctx, int dtype, const TmaImage& img, int box_w, int box_h, bool has_y, CUtensorMap* out);
+
+template <class T, int KH, int KW, int RH, bool TMA>
+int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, const TmaImage* img) {
+    using C = TiledCfg<T, KH, KW, RH>;
     const size_t smem = C::smem_bytes(p.NQ);
-    if (smem > size_t(ctx->prop.sharedMemPerBlockOptin)) return -1;   // caller falls back to the generic family
+    if (smem > size_t(ctx->prop.sharedMemPerBlockOptin)) return -1;   // caller falls back to another family
     p.tilesX = (p.OW + C::TW - 1) / C::TW;
     p.tilesY = (p.OH + C::TH - 1) / C::TH;
     const int64_t tiles = int64_t(p.tilesX) * p.tilesY * p.NP;
@@ -261,6 +402,15 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p) {
         if (splits < 1) splits = 1;
     }
     p.splits = splits;
+    CUtensorMap tmap;
+    memset(&tmap, 0, sizeof(tmap));
+    if (TMA) {
+        if (C::SW > 256 || C::SH > 256) return -1;
+        int st = nk_tma_encode(ctx, sizeof(T) == 4 ? NK_F32 : NK_F64, *img, C::SW, C::SH, p.has_y != 0, &tmap);
+        if (st == -1) return -1;
+        if (st) return st;
+        p.status = ctx->tma_status_dev;
+    }
     T* partial = nullptr;
     if (splits > 1) {
         void* scratch = nullptr;
@@ -271,14 +421,10 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p) {
     }
     const int64_t grid = tiles * splits;
     if (grid > 0x7fffffffLL) return -1;
-    static bool attr_set = false;   // per instantiation
-    if (!attr_set || true) {
-        cudaError_t e = cudaFuncSetAttribute(nk_conv_tiled_kernel<T, KH, KW>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel)");
-        attr_set = true;
-    }
-    nk_conv_tiled_kernel<T, KH, KW><<<unsigned(grid), 256, smem, ctx->stream>>>(out, partial, I, K, p);
-    int st = nk_after_launch(ctx, "nk_conv_tiled_kernel");
+    cudaError_t e = cudaFuncSetAttribute(nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel)");
+    nk_conv_tiled_kernel<T, KH, KW, RH, TMA><<<unsigned(grid), 256, smem, ctx->stream>>>(out, partial, I, K, p, tmap);
+    int st = nk_after_launch(ctx, TMA ? "nk_conv_tiled_kernel<tma>" : "nk_conv_tiled_kernel<ldgsts>");
     if (st || splits == 1) return st;
     const int64_t plane = p.NP * int64_t(p.OH) * p.OW;
     int g = nk_grid_for(ctx, plane, 256, 8);

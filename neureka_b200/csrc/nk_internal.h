@@ -37,6 +37,9 @@ struct nk_ctx {
     // scratch for two-pass (split) reductions; grows on demand, owned by the ctx
     void* scratch = nullptr;
     size_t scratch_bytes = 0;
+    // one host-mapped word kernels set when a bounded device-side wait runs out (read after a synchronise)
+    int* tma_status_host = nullptr;
+    int* tma_status_dev = nullptr;
     uint32_t magic = 0x4e4b4358;  // 'NKCX'
 };
 
@@ -44,6 +47,7 @@ size_t nk_dtype_size(int dtype);
 int nk_fail(nk_ctx* ctx, int status, const char* fmt, ...);
 int nk_cuda_fail(nk_ctx* ctx, cudaError_t e, const char* what);
 int nk_scratch(nk_ctx* ctx, size_t bytes, void** out);
+int nk_check_device_status(nk_ctx* ctx);   // NK_ERR_TIMEOUT if a kernel reported an expired wait since the last check
 
 #define NK_CUDA(ctx, call)                                                     \
     do {                                                                       \

@@ -66,6 +66,14 @@ int nk_scratch(nk_ctx* ctx, size_t bytes, void** out) {
     return NK_OK;
 }
 
+int nk_check_device_status(nk_ctx* ctx) {
+    if (ctx->tma_status_host && *ctx->tma_status_host != 0) {
+        *ctx->tma_status_host = 0;
+        return nk_fail(ctx, NK_ERR_TIMEOUT, "a kernel gave up waiting for a tensor copy (bounded mbarrier wait expired); its results are incomplete");
+    }
+    return NK_OK;
+}
+
 // ------------------------------------------------------------------------------------------------
 // views
 // ------------------------------------------------------------------------------------------------
@@ -158,6 +166,8 @@ extern "C" int nk_device_open(int32_t ordinal, nk_ctx** out_ctx) {
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev0);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev1);
+    if (e == cudaSuccess) e = cudaHostAlloc((void**)&ctx->tma_status_host, sizeof(int), cudaHostAllocMapped);
+    if (e == cudaSuccess) { *ctx->tma_status_host = 0; e = cudaHostGetDevicePointer((void**)&ctx->tma_status_dev, ctx->tma_status_host, 0); }
     if (e != cudaSuccess) {
         int st = nk_cuda_fail(nullptr, e, "nk_device_open");
         delete ctx;
@@ -181,6 +191,7 @@ extern "C" int nk_device_close(nk_ctx* ctx) {
     NK_CHECK_CTX(ctx);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->tma_status_host) cudaFreeHost(ctx->tma_status_host);
     cudaEventDestroy(ctx->ev0);
     cudaEventDestroy(ctx->ev1);
     cudaStreamDestroy(ctx->stream);
@@ -209,7 +220,7 @@ extern "C" int nk_device_props(nk_ctx* ctx, nk_props* out) {
 extern "C" int nk_sync(nk_ctx* ctx) {
     NK_CHECK_CTX(ctx);
     NK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    return NK_OK;
+    return nk_check_device_status(ctx);
 }
 
 extern "C" void* nk_stream(nk_ctx* ctx) {
@@ -337,7 +348,7 @@ extern "C" int nk_read(nk_ctx* ctx, nk_buf* buf, void* host, int64_t dev_start, 
     size_t es = nk_dtype_size(buf->dtype);
     NK_CUDA(ctx, cudaMemcpyAsync(host, (const char*)buf->ptr + dev_start * es, size_t(n) * es, cudaMemcpyDeviceToHost, ctx->stream));
     NK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    return NK_OK;
+    return nk_check_device_status(ctx);
 }
 
 extern "C" int nk_write_async(nk_ctx* ctx, nk_buf* buf, const void* host, int64_t host_off, int64_t dev_start, int64_t n) {
@@ -432,7 +443,7 @@ extern "C" int nk_timer_end(nk_ctx* ctx, float* out_ms) {
     NK_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
     NK_CUDA(ctx, cudaEventSynchronize(ctx->ev1));
     NK_CUDA(ctx, cudaEventElapsedTime(out_ms, ctx->ev0, ctx->ev1));
-    return NK_OK;
+    return nk_check_device_status(ctx);
 }
 
 // ------------------------------------------------------------------------------------------------
