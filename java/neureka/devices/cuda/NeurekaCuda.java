@@ -1,0 +1,60 @@
+package neureka.devices.cuda;
+
+import java.lang.foreign.*;
+import java.lang.invoke.MethodHandle;
+
+import static java.lang.foreign.ValueLayout.*;
+
+/**
+ *  Panama FFM (JDK 22+) binding of the C ABI in include/neureka_cuda.h. One static MethodHandle per entry point;
+ *  no JNI, no generated code. COMPILE-UNVERIFIED: the image this repository is built in has no JDK.
+ *  Status codes are turned into the exception types Neureka's implementations throw:
+ *  NK_ERR_BAD_ARG / NK_ERR_UNSUPPORTED / NK_ERR_BOUNDS -> IllegalArgumentException, everything else -> IllegalStateException.
+ */
+public final class NeurekaCuda
+{
+    public static final int F32 = 0, F64 = 1, I8 = 2, I16 = 3, I32 = 4, I64 = 5;
+    public static final int OP_ADD = 0, OP_SUB = 1, OP_MUL = 2, OP_DIV = 3, OP_MOD = 4, OP_POW = 5, OP_IDY = 6;
+
+    private static final Linker LINKER = Linker.nativeLinker();
+    private static final SymbolLookup LIB = SymbolLookup.libraryLookup(
+            System.getProperty("neureka.cuda.library", "libneureka_cuda.so"), Arena.global());
+
+    private static MethodHandle h( String name, FunctionDescriptor d ) {
+        return LINKER.downcallHandle( LIB.find(name).orElseThrow(() -> new UnsatisfiedLinkError(name)), d );
+    }
+
+    static final MethodHandle DEVICE_COUNT = h("nk_device_count", FunctionDescriptor.of(JAVA_INT, ADDRESS));
+    static final MethodHandle DEVICE_OPEN  = h("nk_device_open",  FunctionDescriptor.of(JAVA_INT, JAVA_INT, ADDRESS));
+    static final MethodHandle DEVICE_CLOSE = h("nk_device_close", FunctionDescriptor.of(JAVA_INT, ADDRESS));
+    static final MethodHandle SYNC         = h("nk_sync",         FunctionDescriptor.of(JAVA_INT, ADDRESS));
+    static final MethodHandle LAST_ERROR   = h("nk_last_error",   FunctionDescriptor.of(ADDRESS, ADDRESS));
+    static final MethodHandle ALLOC        = h("nk_alloc",        FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_LONG, ADDRESS));
+    static final MethodHandle FREE         = h("nk_free",         FunctionDescriptor.of(JAVA_INT, ADDRESS, ADDRESS));
+    static final MethodHandle FILL         = h("nk_fill",         FunctionDescriptor.of(JAVA_INT, ADDRESS, ADDRESS, JAVA_DOUBLE, JAVA_LONG, JAVA_LONG));
+    static final MethodHandle WRITE        = h("nk_write",        FunctionDescriptor.of(JAVA_INT, ADDRESS, ADDRESS, ADDRESS, JAVA_LONG, JAVA_LONG, JAVA_LONG));
+    static final MethodHandle READ         = h("nk_read",         FunctionDescriptor.of(JAVA_INT, ADDRESS, ADDRESS, ADDRESS, JAVA_LONG, JAVA_LONG));
+    static final MethodHandle COPY         = h("nk_copy",         FunctionDescriptor.of(JAVA_INT, ADDRESS, ADDRESS, JAVA_LONG, ADDRESS, JAVA_LONG, JAVA_LONG));
+    static final MethodHandle CONV         = h("nk_conv",         FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS, JAVA_INT));
+    static final MethodHandle BROADCAST    = h("nk_broadcast",    FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS, JAVA_INT));
+    static final MethodHandle BINARY       = h("nk_binary",       FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS, JAVA_INT));
+    static final MethodHandle UNARY        = h("nk_unary",        FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, JAVA_INT));
+    static final MethodHandle SCALAR_BIN   = h("nk_scalar_binary",FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, JAVA_DOUBLE, JAVA_INT));
+    static final MethodHandle FILL_FUN     = h("nk_fill_fun",     FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, JAVA_DOUBLE, JAVA_INT));
+    static final MethodHandle SUM          = h("nk_sum",          FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, JAVA_LONG));
+
+    private NeurekaCuda() {}
+
+    /** Converts a non-zero status into the exception the reference's implementations would throw. */
+    static void check( int status, MemorySegment ctx ) {
+        if ( status == 0 ) return;
+        String msg;
+        try { msg = ((MemorySegment) LAST_ERROR.invokeExact(ctx)).reinterpret(1024).getString(0); }
+        catch ( Throwable t ) { msg = "status " + status; }
+        if ( status == 1 || status == 2 || status == 6 ) throw new IllegalArgumentException(msg);
+        throw new IllegalStateException(msg);
+    }
+
+    /** NDConfiguration.asInlineArray() copied into native memory for the duration of one call. */
+    static MemorySegment cfg( Arena arena, int[] inline ) { return arena.allocateFrom(JAVA_INT, inline); }
+}
