@@ -151,6 +151,20 @@ int nk_fill_fun(nk_ctx* ctx, int32_t fun, int32_t dtype, int32_t rank, nk_buf* d
  * CPUSum (J/backend/main/operations/other/internal/CPUSum.java:26-76). */
 int nk_sum(nk_ctx* ctx, int32_t dtype, int32_t rank, nk_buf* src, const int32_t* cfg, nk_buf* out, int64_t out_index);
 
+/* No counterpart in the reference. The same sum as nk_sum (same tiles, same order of additions, identical result)
+ * for callers that must not trigger a device allocation: hosts that have given all of the GPU's memory to their own
+ * tensor pool, where nk_sum's grow-on-demand scratch block could fail or stall the device in the middle of a pass.
+ * The partial sums live in a fixed array of NK_SUM_STATIC_SCRATCH_BYTES that every GPU loading the library holds
+ * until exit. Limits and rules:
+ *  - the view may have at most about 16.6 million F64 / 33.2 million F32 elements (ceil(n/128) + ceil(n/128^2) + 2
+ *    partial sums must fit the array); larger views are rejected with NK_ERR_UNSUPPORTED -- use nk_sum for them;
+ *  - the first call on a device looks up the array's device address; make that first call outside any stream capture;
+ *  - all calls on a device share the array (it keeps the previous call's partial sums; nothing needs clearing, every
+ *    level is rewritten before it is read), so calls that overlap on the GPU race: order them on one stream;
+ *  - the call performs no cudaMalloc/cudaFree and calls no allocating library routine. */
+#define NK_SUM_STATIC_SCRATCH_BYTES (1 << 20)
+int nk_sum_static(nk_ctx* ctx, int32_t dtype, int32_t rank, nk_buf* src, const int32_t* cfg, nk_buf* out, int64_t out_index);
+
 /* ---- routing knobs / introspection (no reference counterpart; measurement support) ---- */
 int nk_set_conv_path(nk_ctx* ctx, int32_t path);        /* nk_conv_path */
 int nk_last_conv_path(nk_ctx* ctx, int32_t* out_path);   /* family the last nk_conv used */
