@@ -1,0 +1,132 @@
+"""Side measurements of the other BASELINE configurations on one GPU (reported under "extra" by bench.py; the
+headline line stays config 5). Everything goes through the C ABI with device-resident buffers and is timed with
+the context's CUDA events after warm-up launches.
+
+  cfg1  F32 [256,256] x [5,5]                  -> latency of one launch (the problem lives in L2: latency-bound)
+  cfg2  F32 [64,512,512] x [64,3,3]            -> GB/s of algorithmic bytes, inputs rotated over 4 copies (> L2 in total)
+  cfg3  F32 tanh(a*b+b), a [n,1,1024], b [1,m,1024] at n*m*1024 = 2^31 outputs (the full 2^33 does not exist in the
+        reference: Java int sizes) -> GB/s of each of the three kernels the reference runs, plus the two gradient reductions
+  cfg4  F64 [128,128,128] x [7,7,7] forward + gradient w.r.t. volume + gradient w.r.t. kernel -> GFLOP/s each
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib as L
+from .ndconf import NDConfiguration as ND
+
+
+class _Buf:
+    def __init__(self, dev, dtype, n, host=None):
+        self.dev, self.n = dev, int(n)
+        self.dt = L.NK_F32 if np.dtype(dtype) == np.float32 else L.NK_F64
+        self.buf = C.c_void_p()
+        L.check(L.lib.nk_alloc(dev.ctx, self.dt, self.n, C.byref(self.buf)), dev.ctx)
+        if host is not None:
+            h = np.ascontiguousarray(host, dtype=dtype)
+            L.check(L.lib.nk_write(dev.ctx, self.buf, h.ctypes.data_as(C.c_void_p), 0, 0, h.size), dev.ctx)
+
+    def free(self):
+        if self.buf:
+            L.lib.nk_free(self.dev.ctx, self.buf)
+            self.buf = None
+
+
+def _cfg(shape_or_conf):
+    c = shape_or_conf if isinstance(shape_or_conf, ND) else ND.of_shape(shape_or_conf)
+    a = c.as_inline_array()
+    return a, a.ctypes.data_as(C.POINTER(C.c_int32))
+
+
+def _time(dev, fn, warm=3, reps=10):
+    for _ in range(warm):
+        fn(0)
+    dev.sync()
+    L.check(L.lib.nk_timer_begin(dev.ctx), dev.ctx)
+    for i in range(reps):
+        fn(i)
+    ms = C.c_float(0)
+    L.check(L.lib.nk_timer_end(dev.ctx, C.byref(ms)), dev.ctx)
+    return float(ms.value) / reps
+
+
+def _rand(dtype, n, dist, seed, p0, p1):
+    a = np.zeros(n, dtype=dtype)
+    dt = L.NK_F32 if np.dtype(dtype) == np.float32 else L.NK_F64
+    L.lib.nk_jrand_fill(dt, dist, seed, p0, p1, a.ctypes.data_as(C.c_void_p), n)
+    return a
+
+
+def run_extra(dev, hbm_peak_gbs: float) -> dict:
+    out = {}
+    ctx = dev.ctx
+
+    # ---- cfg1 -----------------------------------------------------------------------------------------------------
+    a = _Buf(dev, np.float32, 256 * 256, _rand(np.float32, 256 * 256, 0, 42, -1.0, 1.0))
+    k = _Buf(dev, np.float32, 25, _rand(np.float32, 25, 0, 43, -1.0, 1.0))
+    o = _Buf(dev, np.float32, 252 * 252)
+    ca, pa = _cfg([256, 256]); ck, pk = _cfg([5, 5]); co, po = _cfg([252, 252])
+    ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F32, 2, o.buf, po, a.buf, pa, k.buf, pk, -1), ctx), 5, 200)
+    out["cfg1_conv2d_256x256_k5"] = {"us_per_launch": ms * 1e3, "gflops": 3175200 / (ms * 1e-3) / 1e9, "kernel": dev.last_kernel(),
+                                     "note": "0.5 MB problem, L2 resident: launch-latency bound"}
+    for b in (a, k, o): b.free()
+
+    # ---- cfg2 -----------------------------------------------------------------------------------------------------
+    n_in = 64 * 512 * 512
+    host = _rand(np.float32, n_in, 1, 7, 0.0, 1.0)
+    copies = [_Buf(dev, np.float32, n_in, host) for _ in range(4)]
+    k = _Buf(dev, np.float32, 64 * 9, _rand(np.float32, 64 * 9, 1, 8, 0.0, 1.0))
+    o = _Buf(dev, np.float32, 510 * 510)
+    ca, pa = _cfg([64, 512, 512]); ck, pk = _cfg([64, 3, 3]); co, po = _cfg([1, 510, 510])
+    ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F32, 3, o.buf, po, copies[i % 4].buf, pa, k.buf, pk, -1), ctx), 4, 20)
+    gbs = 68151568 / (ms * 1e-3) / 1e9
+    out["cfg2_conv3d_64x512x512_k64x3x3"] = {"ms": ms, "gflops": 299635200 / (ms * 1e-3) / 1e9, "gbs": gbs, "frac_of_hbm_peak": gbs / hbm_peak_gbs,
+                                             "kernel": dev.last_kernel(), "note": "4 rotating input copies (256 MiB) so that L2 cannot serve the reads"}
+    for b in copies + [k, o]: b.free()
+
+    # ---- cfg3 (scaled to 2^31 outputs) ---------------------------------------------------------------------------------
+    n, m, kk = 2048, 1024, 1024
+    a = _Buf(dev, np.float32, n * kk, _rand(np.float32, n * kk, 0, 3, -2.0, 2.0))
+    b = _Buf(dev, np.float32, m * kk, _rand(np.float32, m * kk, 0, 4, -2.0, 2.0))
+    N = n * m * kk
+    t1, t2, y = (_Buf(dev, np.float32, N) for _ in range(3))
+    ca, pa = _cfg([n, 1, kk]); cb, pb = _cfg([1, m, kk]); co, po = _cfg([n, m, kk])
+    r = {}
+    ms = _time(dev, lambda i: L.check(L.lib.nk_broadcast(ctx, L.NK_OP_MUL, L.NK_F32, 3, t1.buf, po, a.buf, pa, b.buf, pb, -1), ctx), 2, 5)
+    r["mul_broadcast"] = {"ms": ms, "gbs": (4.0 * (N + n * kk + m * kk)) / (ms * 1e-3) / 1e9, "kernel": dev.last_kernel()}
+    ms = _time(dev, lambda i: L.check(L.lib.nk_broadcast(ctx, L.NK_OP_ADD, L.NK_F32, 3, t2.buf, po, t1.buf, po, b.buf, pb, -1), ctx), 2, 5)
+    r["add_broadcast"] = {"ms": ms, "gbs": (4.0 * (2 * N + m * kk)) / (ms * 1e-3) / 1e9, "kernel": dev.last_kernel()}
+    ms = _time(dev, lambda i: L.check(L.lib.nk_unary(ctx, L.FUN["tanh"], L.NK_F32, 3, y.buf, po, t2.buf, po, -1), ctx), 2, 5)
+    r["tanh"] = {"ms": ms, "gbs": (8.0 * N) / (ms * 1e-3) / 1e9, "kernel": dev.last_kernel()}
+    ms = _time(dev, lambda i: L.check(L.lib.nk_unary(ctx, L.FUN["tanh"], L.NK_F32, 3, t1.buf, po, t2.buf, po, 0), ctx), 2, 5)
+    r["tanh_derivative"] = {"ms": ms, "gbs": (8.0 * N) / (ms * 1e-3) / 1e9, "kernel": dev.last_kernel()}
+    ga, gb = _Buf(dev, np.float32, n * kk), _Buf(dev, np.float32, m * kk)
+    ms = _time(dev, lambda i: L.check(L.lib.nk_broadcast(ctx, L.NK_OP_MUL_BOTH, L.NK_F32, 3, ga.buf, pa, b.buf, pb, t1.buf, po, 0), ctx), 1, 3)
+    r["grad_a_reduce"] = {"ms": ms, "gbs": (4.0 * (N + n * kk + m * kk)) / (ms * 1e-3) / 1e9, "kernel": dev.last_kernel()}
+    ms = _time(dev, lambda i: L.check(L.lib.nk_broadcast(ctx, L.NK_OP_MUL_BOTH, L.NK_F32, 3, gb.buf, pb, a.buf, pa, t1.buf, po, 0), ctx), 1, 3)
+    r["grad_b_reduce"] = {"ms": ms, "gbs": (4.0 * (N + n * kk + m * kk)) / (ms * 1e-3) / 1e9, "kernel": dev.last_kernel()}
+    for v in r.values():
+        v["frac_of_hbm_peak"] = v["gbs"] / hbm_peak_gbs
+    out["cfg3_broadcast_tanh_2048x1024x1024"] = r
+    for bb in (a, b, t1, t2, y, ga, gb): bb.free()
+
+    # ---- cfg4 -----------------------------------------------------------------------------------------------------
+    v = _Buf(dev, np.float64, 128 ** 3, _rand(np.float64, 128 ** 3, 1, 11, 0.0, 1.0))
+    k = _Buf(dev, np.float64, 343, _rand(np.float64, 343, 1, 12, 0.0, 0.1))
+    yb = _Buf(dev, np.float64, 122 ** 3)
+    gv, gk = _Buf(dev, np.float64, 128 ** 3), _Buf(dev, np.float64, 343)
+    cv, pv = _cfg([128] * 3); ck, pk = _cfg([7] * 3); cy, py = _cfg([122] * 3)
+    flops = 1245671728.0
+    r = {}
+    ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F64, 3, yb.buf, py, v.buf, pv, k.buf, pk, -1), ctx), 3, 10)
+    r["forward"] = {"ms": ms, "gflops": flops / (ms * 1e-3) / 1e9, "kernel": dev.last_kernel()}
+    # gradients for error = y itself (any error tensor does): XConvRight(error, other, zeros) -> (drain, other, error), d = 0
+    ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F64, 3, gv.buf, pv, k.buf, pk, yb.buf, py, 0), ctx), 2, 5)
+    r["grad_volume"] = {"ms": ms, "gflops": flops / (ms * 1e-3) / 1e9, "kernel": dev.last_kernel()}
+    ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F64, 3, gk.buf, pk, v.buf, pv, yb.buf, py, 0), ctx), 2, 5)
+    r["grad_kernel"] = {"ms": ms, "gflops": flops / (ms * 1e-3) / 1e9, "kernel": dev.last_kernel()}
+    out["cfg4_conv3d_f64_128_k7"] = r
+    for bb in (v, k, yb, gv, gk): bb.free()
+    return out

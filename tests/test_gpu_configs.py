@@ -1,0 +1,124 @@
+"""The BASELINE configurations themselves, on their seeded inputs (java.util.Random-compatible streams), against the
+CPU oracle: full output where the oracle finishes in seconds, otherwise oracle spot checks on sampled output ranges
+plus size-independent properties (linearity in the kernel, shift equivariance, gradient = adjoint identity)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from helpers import DevArray, cfgp, gpu_conv
+from neureka_b200 import _lib as L
+from neureka_b200.ndconf import NDConfiguration as ND
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(dtype, n, dist, seed, p0, p1):
+    a = np.zeros(n, dtype=dtype)
+    L.lib.nk_jrand_fill(L.NK_F32 if dtype == np.float32 else L.NK_F64, dist, seed, p0, p1, a.ctypes.data_as(C.c_void_p), n)
+    return a
+
+
+def test_config1_conv2d_matches_the_simple_cpu_convolution(device, oracle):
+    a, k = _rand(np.float32, 256 * 256, 0, 42, -1.0, 1.0), _rand(np.float32, 25, 0, 142, -1.0, 1.0)
+    co, ca, ck = ND.of_shape([252, 252]), ND.of_shape([256, 256]), ND.of_shape([5, 5])
+    ref = np.zeros(co.size, dtype=np.float32)
+    assert oracle.conv(ref, co.as_inline_array(), a, ca.as_inline_array(), k, ck.as_inline_array()) == 1   # SimpleCPUConvolution path
+    got = gpu_conv(device, np.zeros(co.size, dtype=np.float32), co, a, ca, k, ck)
+    assert np.abs(got - ref).max() <= 1e-5 * np.abs(ref).max()
+
+
+def test_config2_channel_collapsing_conv(device, oracle):
+    a, k = _rand(np.float32, 64 * 512 * 512, 1, 7, 0.0, 1.0), _rand(np.float32, 64 * 9, 1, 107, 0.0, 1.0)
+    co, ca, ck = ND.of_shape([1, 510, 510]), ND.of_shape([64, 512, 512]), ND.of_shape([64, 3, 3])
+    ref = np.zeros(co.size, dtype=np.float32)
+    assert oracle.conv(ref, co.as_inline_array(), a, ca.as_inline_array(), k, ck.as_inline_array(), threads=8) == 0   # general nd path
+    scale = np.zeros(co.size, dtype=np.float32)
+    oracle.conv(scale, co.as_inline_array(), np.abs(a), ca.as_inline_array(), np.abs(k), ck.as_inline_array(), threads=8)
+    got = gpu_conv(device, np.zeros(co.size, dtype=np.float32), co, a, ca, k, ck)
+    assert np.all(np.abs(got.astype(np.float64) - ref) <= 1e-5 * scale)
+    assert np.abs(got - ref).max() <= 1e-5 * np.abs(ref).max() * 4
+
+
+def test_config4_f64_forward_and_both_gradients(device, oracle):
+    v, k = _rand(np.float64, 128 ** 3, 1, 11, 0.0, 1.0), _rand(np.float64, 343, 1, 12, 0.0, 0.1)
+    cv, ck, cy = ND.of_shape([128] * 3), ND.of_shape([7] * 3), ND.of_shape([122] * 3)
+    y = gpu_conv(device, np.zeros(cy.size), cy, v, cv, k, ck)
+    # forward: oracle on sampled ranges of the output (the full state machine would take minutes)
+    rng = np.random.default_rng(4)
+    ref = np.zeros(cy.size)
+    for s in rng.integers(0, cy.size - 3000, size=6):
+        oracle.conv_range(ref, cy.as_inline_array(), v, cv.as_inline_array(), k, ck.as_inline_array(), -1, int(s), int(s) + 3000)
+        seg = slice(int(s), int(s) + 3000)
+        assert np.abs(y[seg] - ref[seg]).max() <= 1e-12 * max(1.0, np.abs(ref[seg]).max()) * 50
+    # backward of sum(y): error = ones
+    err = np.ones(cy.size)
+    gk = gpu_conv(device, np.zeros(343), ck, v, cv, err, cy, d=0)             # (drain = kernel-shaped, t1 = volume, t2 = error)
+    gv = gpu_conv(device, np.zeros(128 ** 3), cv, k, ck, err, cy, d=0)         # (drain = volume-shaped, t1 = kernel, t2 = error)
+    # grad wrt kernel with error = ones is a box sum of the volume: check all 343 taps in float128-free numpy
+    V = v.reshape(128, 128, 128)
+    csum = np.zeros((129, 129, 129))
+    csum[1:, 1:, 1:] = V.cumsum(0).cumsum(1).cumsum(2)
+    def box(z, yy, x):
+        z1, y1, x1 = z + 122, yy + 122, x + 122
+        return (csum[z1, y1, x1] - csum[z, y1, x1] - csum[z1, yy, x1] - csum[z1, y1, x] + csum[z, yy, x1] + csum[z, y1, x] + csum[z1, yy, x] - csum[z, yy, x])
+    want_gk = np.array([box(z, yy, x) for z in range(7) for yy in range(7) for x in range(7)])
+    np.testing.assert_allclose(gk, want_gk, rtol=1e-9, atol=1e-6)
+    # oracle (general deconvolution) on a few taps: 122^3 terms each
+    ref_gk = np.zeros(343)
+    oracle.conv_range(ref_gk, ck.as_inline_array(), v, cv.as_inline_array(), err, cy.as_inline_array(), 0, 170, 172)
+    np.testing.assert_allclose(gk[170:172], ref_gk[170:172], rtol=1e-12 * 1e3)
+    # grad wrt volume: oracle on sampled ranges (each element visits all of the error in the reference: keep it short)
+    ref_gv = np.zeros(128 ** 3)
+    for s in (0, 128 * 128 * 64 + 128 * 60 + 50):
+        oracle.conv_range(ref_gv, cv.as_inline_array(), k, ck.as_inline_array(), err, cy.as_inline_array(), 0, s, s + 2)
+        np.testing.assert_allclose(gv[s:s + 2], ref_gv[s:s + 2], rtol=1e-11, atol=1e-13)
+    # adjoint identity <conv(v,k), e> = <v, grad_v(e)> = <k, grad_k(e)> for a random error
+    e = rng.standard_normal(cy.size)
+    gk_e = gpu_conv(device, np.zeros(343), ck, v, cv, e, cy, d=0)
+    gv_e = gpu_conv(device, np.zeros(128 ** 3), cv, k, ck, e, cy, d=0)
+    lhs = float(np.dot(y, e))
+    assert float(np.dot(v, gv_e)) == pytest.approx(lhs, rel=1e-10)
+    assert float(np.dot(k, gk_e)) == pytest.approx(lhs, rel=1e-10)
+
+
+def test_config5_full_size_on_one_gpu(device, oracle):
+    """4 GiB input: oracle spot checks on sampled output ranges, plus properties that hold at any size."""
+    a_shape, k_shape, o_shape = [8, 32, 2048, 2048], [1, 32, 5, 5], [8, 1, 2044, 2044]
+    n_in, n_out = int(np.prod(a_shape)), int(np.prod(o_shape))
+    a = _rand(np.float32, n_in, 0, 5, 0.0, 1.0)
+    k = _rand(np.float32, 800, 1, 6, 0.0, 0.2)
+    A = DevArray(device, a)
+    K = DevArray(device, k)
+    O = DevArray(device, np.zeros(1, dtype=np.float32))
+    O.free()
+    buf = C.c_void_p()
+    L.check(L.lib.nk_alloc(device.ctx, L.NK_F32, n_out, C.byref(buf)), device.ctx)
+    ka, pa = cfgp(ND.of_shape(a_shape)); kk, pk = cfgp(ND.of_shape(k_shape)); ko, po = cfgp(ND.of_shape(o_shape))
+    L.check(L.lib.nk_conv(device.ctx, L.NK_F32, 4, buf, po, A.buf, pa, K.buf, pk, -1), device.ctx)
+    y = np.empty(n_out, dtype=np.float32)
+    L.check(L.lib.nk_read(device.ctx, buf, y.ctypes.data_as(C.c_void_p), 0, n_out), device.ctx)
+    assert device.last_conv_path() in (L.NK_CONV_TILED, L.NK_CONV_TMA)
+    rng = np.random.default_rng(55)
+    ref = np.zeros(n_out, dtype=np.float32)
+    starts = [0, n_out - 500, 2044 * 2044 * 3 + 2044 * 2043 + 1500] + [int(s) for s in rng.integers(0, n_out - 500, size=5)]
+    for s in starts:
+        oracle.conv_range(ref, ko, a, ka, k, kk, -1, s, s + 500)
+        assert np.abs(y[s:s + 500] - ref[s:s + 500]).max() <= 1e-5 * np.abs(ref[s:s + 500]).max()
+    # linearity in the kernel: conv(a, 2k) == 2 conv(a, k) exactly (power-of-two scaling)
+    K2 = DevArray(device, k * 2)
+    L.check(L.lib.nk_conv(device.ctx, L.NK_F32, 4, buf, po, A.buf, pa, K2.buf, pk, -1), device.ctx)
+    y2 = np.empty(n_out, dtype=np.float32)
+    L.check(L.lib.nk_read(device.ctx, buf, y2.ctypes.data_as(C.c_void_p), 0, n_out), device.ctx)
+    assert np.array_equal(y2, 2 * y)
+    # a delta kernel copies a shifted window of one channel: exact
+    delta = np.zeros(800, dtype=np.float32)
+    delta[7 * 25 + 2 * 5 + 3] = 1.0     # channel 7, tap (2, 3)
+    KD = DevArray(device, delta)
+    L.check(L.lib.nk_conv(device.ctx, L.NK_F32, 4, buf, po, A.buf, pa, KD.buf, pk, -1), device.ctx)
+    L.check(L.lib.nk_read(device.ctx, buf, y2.ctypes.data_as(C.c_void_p), 0, n_out), device.ctx)
+    want = a.reshape(a_shape)[:, 7, 2:2 + 2044, 3:3 + 2044]
+    assert np.array_equal(y2.reshape(8, 2044, 2044), want)
+    L.lib.nk_free(device.ctx, buf)
+    for b in (A, K, K2, KD):
+        b.free()
