@@ -53,56 +53,60 @@ def read_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    """Polls one GPU's SM clock, power and clock-event reasons through NVML (read-only) every few milliseconds while
+    the timed region runs."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
 
     def __init__(self, gpu_index: int):
-        self.rows = []
-        self.proc = None
+        self.rows, self.ok, self.stop_flag = [], False, False
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._pump, daemon=True)
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if vis:
+                ids = [v.strip() for v in vis.split(",")]
+                if gpu_index < len(ids) and ids[gpu_index].isdigit():
+                    gpu_index = int(ids[gpu_index])
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.reason_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            self.ok = True
+            self.thread = threading.Thread(target=self._poll, daemon=True)
             self.thread.start()
-        except OSError:
-            self.proc = None
+        except Exception as e:  # no NVML: report that instead of clocks
+            self.err = repr(e)
 
-    def _pump(self):
-        for line in self.proc.stdout:
-            self.rows.append((time.time(), line.strip()))
+    def _poll(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                mask = self.reason_fn(self.h)
+                try:
+                    watts = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                except Exception:
+                    watts = None
+                self.rows.append((time.time(), float(mhz), int(mask), watts))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def stop(self, t0: float, t1: float) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, smax, reasons, power = [], None, set(), []
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for t, line in self.rows:
-            parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                mhz = float(parts[0]); smax = float(parts[1])
-            except ValueError:
-                continue
-            if t0 - 0.05 <= t <= t1 + 0.05:
-                sm.append(mhz)
-                try:
-                    power.append(float(parts[2]))
-                except ValueError:
-                    pass
-                for n, v in zip(names, parts[3:7]):
-                    if v.lower().startswith("active"):
-                        reasons.add(n)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
-                "samples": len(sm), "power_w_max": max(power) if power else None}
+        if not self.ok:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable: " + getattr(self, "err", "?")]}
+        self.stop_flag = True
+        self.thread.join(timeout=1.0)
+        inside = [r for r in self.rows if t0 <= r[0] <= t1] or [r for r in self.rows if t0 - 0.01 <= r[0] <= t1 + 0.01]
+        reasons = set()
+        for r in inside:
+            for bit, name in self.REASONS.items():
+                if r[2] & bit:
+                    reasons.add(name)
+        watts = [r[3] for r in inside if r[3] is not None]
+        return {"sm_mhz": float(np.median([r[1] for r in inside])) if inside else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(reasons), "samples": len(inside), "power_w_max": max(watts) if watts else None}
 
 
 def cpu_sample(a_host, k_host, a_shape, k_shape, o_shape, seconds_target: float, gpu_out=None):
@@ -285,12 +289,14 @@ def main():
         ptr = C.c_void_p(); L.lib.nk_buf_info(d_out_local, C.byref(ptr), None, None)
         stream = torch.cuda.ExternalStream(L.lib.nk_stream(ctx))
         torch.cuda.set_stream(stream)
-        torch_local = torch.empty(n_out_local, dtype=torch.float32, device=f"cuda:{local_rank}")
-        wrapped = C.c_void_p()
-        L.check(L.lib.nk_wrap(ctx, L.NK_F32, C.c_void_p(torch_local.data_ptr()), n_out_local, C.byref(wrapped)), ctx)
-        d_out_nccl = wrapped
+        # NCCL gather wants equal sizes: every rank contributes a buffer of the largest slab's size
         sizes = [int(np.prod(slab_views(a_shape, k_shape, SPLIT_DIM, s)[1].shape)) for s in plan_slabs(o_shape[SPLIT_DIM], world, halo)]
-        gather_list = [torch.empty(s, dtype=torch.float32, device=f"cuda:{local_rank}") for s in sizes] if rank == 0 else None
+        n_pad = max(sizes)
+        torch_local = torch.empty(n_pad, dtype=torch.float32, device=f"cuda:{local_rank}")
+        wrapped = C.c_void_p()
+        L.check(L.lib.nk_wrap(ctx, L.NK_F32, C.c_void_p(torch_local.data_ptr()), n_pad, C.byref(wrapped)), ctx)
+        d_out_nccl = wrapped
+        gather_list = [torch.empty(n_pad, dtype=torch.float32, device=f"cuda:{local_rank}") for _ in sizes] if rank == 0 else None
 
     def conv_step_resident():
         """One pass with slabs resident: conv into the assembled output (peer stores) or local slab (+ NCCL gather)."""

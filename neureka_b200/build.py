@@ -27,6 +27,7 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-O2,-fno-fast-m
 SOURCES = [
     ("nk_runtime.cu", []),
     ("nk_elementwise.cu", ["-fmad=false"]),
+    ("nk_ew_unary.cu", ["-fmad=false"]),
     ("nk_conv.cu", []),
     ("nk_conv_tiled.cu", []),
     ("nk_conv_tiled_inst_f32_ldgsts.cu", []),

@@ -167,7 +167,9 @@ int nk_conv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_
     int family = NK_CONV_TILED;
     if (tma_ok) {
         // 8 output rows per thread halve the shared-memory reads per multiply-add; worth it once the tile is filled
-        const bool tall = p.OH >= 128;
+        // ... i.e. when the 64-row tiles alone give every SM several CTAs; small problems keep the 32-row tiles
+        const int64_t tiles8 = int64_t((p.OW + 127) / 128) * ((p.OH + 63) / 64) * p.NP;
+        const bool tall = p.OH >= 128 && tiles8 >= int64_t(ctx->prop.multiProcessorCount) * 4;
         if (tall) st = f32 ? nk_tiled_dispatch_f32_tma8(ctx, int(KH), int(KW), of, If, Kf, p, &img) : nk_tiled_dispatch_f64_tma8(ctx, int(KH), int(KW), od, Id, Kd, p, &img);
         if (st == -1) st = f32 ? nk_tiled_dispatch_f32_tma4(ctx, int(KH), int(KW), of, If, Kf, p, &img) : nk_tiled_dispatch_f64_tma4(ctx, int(KH), int(KW), od, Id, Kd, p, &img);
         if (st != -1) family = NK_CONV_TMA;

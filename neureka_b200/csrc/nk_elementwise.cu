@@ -1,211 +1,27 @@
-// Broadcast / elementwise / scalar / fill / sum kernels.
-//
-// All of these are HBM-bound streaming kernels: one pass, every input element read once and every
-// output element written once. The host turns the three NDConfiguration views into one iteration plan
-// (per-dimension divisor + one element stride per tensor, broadcast dims get stride 0, adjacent dims
-// are merged when all tensors allow it), passed by value in the kernel parameters, so the kernels do
-// no index-map loads from memory (the reference's OpenCL templates copy 5*rank ints per tensor into
-// private memory and recompute a full strided index per access, kernels/utility.cl:15-70).
+// Entry points nk_broadcast, nk_binary, nk_fill_fun, nk_sum and the backward-broadcast reduction kernel.
+// (nk_unary and nk_scalar_binary live in nk_ew_unary.cu; the forward kernels in nk_ew_kernels.cuh.)
 //
 // Compiled with -fmad=false (see nk_scalarfun.cuh).
 
-#include "nk_internal.h"
-#include "nk_scalarfun.cuh"
+#include "nk_ew_kernels.cuh"
+
+using namespace nkew;
 
 namespace {
 
-struct EwPlan {
-    int nd;                       // dims after merging (>= 1)
-    int64_t total;                // number of drain elements
-    int64_t div[NK_MAX_RANK];     // idx_k = i / div[k]; i %= div[k]
-    int64_t ext[NK_MAX_RANK];     // extent of dim k (row-major plans only)
-    int64_t s0[NK_MAX_RANK], s1[NK_MAX_RANK], s2[NK_MAX_RANK];
-    int64_t b0, b1, b2;
-    bool row_major;               // div[] are the row-major divisors of ext[]
-};
-
-// Builds the iteration plan over the drain's index space. sel1/sel2 give, per original dim, whether the
-// source follows the drain index (true) or stays at 0 (false: a broadcast dim).
-void make_plan(const NkView& v0, const NkView* v1, const bool* follow1, const NkView* v2, const bool* follow2, EwPlan* p) {
-    int rank = v0.rank;
-    p->total = v0.size;
-    p->b0 = v0.base;
-    p->b1 = v1 ? v1->base : 0;
-    p->b2 = v2 ? v2->base : 0;
-    int64_t e[NK_MAX_RANK], a0[NK_MAX_RANK], a1[NK_MAX_RANK], a2[NK_MAX_RANK];
-    for (int k = 0; k < rank; k++) {
-        e[k] = v0.shape[k];
-        a0[k] = v0.estride[k];
-        a1[k] = (v1 && (!follow1 || follow1[k])) ? v1->estride[k] : 0;
-        a2[k] = (v2 && (!follow2 || follow2[k])) ? v2->estride[k] : 0;
-    }
-    if (!v0.imap_row_major) {
-        // Decode with the drain's own indicesMap, exactly as NDConfiguration.indicesOfIndex does.
-        p->nd = rank;
-        p->row_major = false;
-        for (int k = 0; k < rank; k++) {
-            p->div[k] = v0.imap[k]; p->ext[k] = e[k];
-            p->s0[k] = a0[k]; p->s1[k] = a1[k]; p->s2[k] = a2[k];
-        }
-        return;
-    }
-    // drop size-1 dims, merge neighbours (outer k with inner k+1) when every tensor is linear across them
-    int nd = 0;
-    for (int k = 0; k < rank; k++) {
-        if (e[k] == 1) continue;
-        if (nd > 0 && p->s0[nd - 1] == e[k] * a0[k] && p->s1[nd - 1] == e[k] * a1[k] && p->s2[nd - 1] == e[k] * a2[k]) {
-            p->ext[nd - 1] *= e[k];
-            p->s0[nd - 1] = a0[k]; p->s1[nd - 1] = a1[k]; p->s2[nd - 1] = a2[k];
-        } else {
-            p->ext[nd] = e[k];
-            p->s0[nd] = a0[k]; p->s1[nd] = a1[k]; p->s2[nd] = a2[k];
-            nd++;
+// forward + - * / with compile-time functors, everything else through the run-time functor
+template <class T, int FAMILY>
+int launch_binary(nk_ctx* ctx, int op, int d, T* out, const T* a, const T* b, const EwPlan& p) {
+    if (d < 0) {
+        switch (op) {
+            case NK_OP_ADD: return launch_ew<T, 2>(ctx, out, a, b, p, BinFix<T, NK_OP_ADD>{});
+            case NK_OP_SUB: return launch_ew<T, 2>(ctx, out, a, b, p, BinFix<T, NK_OP_SUB>{});
+            case NK_OP_MUL: return launch_ew<T, 2>(ctx, out, a, b, p, BinFix<T, NK_OP_MUL>{});
+            case NK_OP_DIV: return launch_ew<T, 2>(ctx, out, a, b, p, BinFix<T, NK_OP_DIV>{});
+            default: break;
         }
     }
-    if (nd == 0) { p->ext[0] = 1; p->s0[0] = p->s1[0] = p->s2[0] = 0; nd = 1; }
-    p->nd = nd;
-    p->row_major = true;
-    int64_t d = 1;
-    for (int k = nd - 1; k >= 0; k--) { p->div[k] = d; d *= p->ext[k]; }
-}
-
-// ---- functors -------------------------------------------------------------------------------------
-template <class T> struct UnaryF {
-    int f; bool derive;
-    __device__ __forceinline__ T operator()(T a, T) const { return nkf::fun(f, derive, a); }
-};
-template <class T, int FAMILY> struct BinF {
-    int op, d;
-    __device__ __forceinline__ T operator()(T a, T b) const { return nkf::bin<FAMILY>(op, d, a, b); }
-};
-template <class T> struct ScalarF {
-    int op, d; T value;
-    __device__ __forceinline__ T operator()(T a, T) const { return nkf::bin<2>(op, d, a, value); }
-};
-
-template <class T> struct Vec4 { using type = float4; static constexpr int N = 4; };
-template <> struct Vec4<double> { using type = double2; static constexpr int N = 2; };
-
-// ---- kernel 1: fully contiguous, 128-bit accesses ---------------------------------------------------
-// All tensors are linear with element stride 1 (sources may have stride 0 = a broadcast scalar).
-template <class T, int NIN, class F>
-__global__ void __launch_bounds__(256) nk_ew_linear_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b,
-                                                           int64_t n, int sa, int sb, F f) {
-    using V = typename Vec4<T>::type;
-    constexpr int N = Vec4<T>::N;
-    const int64_t nvec = n / N;
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    for (int64_t i = tid; i < nvec; i += stride) {
-        T av[N], bv[N], ov[N];
-        if (sa) *reinterpret_cast<V*>(av) = __ldcs(reinterpret_cast<const V*>(a) + i);
-        else { T s = a[0]; for (int k = 0; k < N; k++) av[k] = s; }
-        if (NIN == 2) {
-            if (sb) *reinterpret_cast<V*>(bv) = __ldcs(reinterpret_cast<const V*>(b) + i);
-            else { T s = b[0]; for (int k = 0; k < N; k++) bv[k] = s; }
-        }
-#pragma unroll
-        for (int k = 0; k < N; k++) ov[k] = f(av[k], NIN == 2 ? bv[k] : T(0));
-        __stcs(reinterpret_cast<V*>(out) + i, *reinterpret_cast<V*>(ov));
-    }
-    for (int64_t i = nvec * N + tid; i < n; i += stride)
-        out[i] = f(a[sa ? i : 0], NIN == 2 ? b[sb ? i : 0] : T(0));
-}
-
-// ---- kernel 2: rows ---------------------------------------------------------------------------------
-// The innermost merged dim is long and every tensor has stride 1 or 0 along it. A CTA walks rows
-// (all outer dims, decoded once per row) and streams the row with 128-bit accesses when VEC.
-template <class T, int NIN, class F, bool VEC>
-__global__ void __launch_bounds__(256) nk_ew_rows_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b,
-                                                         EwPlan p, int64_t rows, int64_t inner, F f) {
-    using V = typename Vec4<T>::type;
-    constexpr int N = Vec4<T>::N;
-    const int last = p.nd - 1;
-    const int sa = int(p.s1[last]), sb = int(p.s2[last]);
-    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
-        int64_t rem = r, o0 = p.b0, o1 = p.b1, o2 = p.b2;
-        for (int k = 0; k < last; k++) {
-            int64_t dk = p.div[k] / inner;  // divisor in units of rows
-            int64_t idx = rem / dk;
-            rem -= idx * dk;
-            o0 += idx * p.s0[k]; o1 += idx * p.s1[k]; o2 += idx * p.s2[k];
-        }
-        T* orow = out + o0;
-        const T* arow = a + o1;
-        const T* brow = (NIN == 2) ? b + o2 : nullptr;
-        if (VEC) {
-            const int64_t nvec = inner / N;
-            for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
-                T av[N], bv[N], ov[N];
-                if (sa) *reinterpret_cast<V*>(av) = __ldg(reinterpret_cast<const V*>(arow) + i);
-                else { T s = arow[0]; for (int k = 0; k < N; k++) av[k] = s; }
-                if (NIN == 2) {
-                    if (sb) *reinterpret_cast<V*>(bv) = __ldg(reinterpret_cast<const V*>(brow) + i);
-                    else { T s = brow[0]; for (int k = 0; k < N; k++) bv[k] = s; }
-                }
-#pragma unroll
-                for (int k = 0; k < N; k++) ov[k] = f(av[k], NIN == 2 ? bv[k] : T(0));
-                __stcs(reinterpret_cast<V*>(orow) + i, *reinterpret_cast<V*>(ov));
-            }
-        } else {
-            for (int64_t i = threadIdx.x; i < inner; i += blockDim.x)
-                orow[i] = f(arow[sa ? i : 0], NIN == 2 ? brow[sb ? i : 0] : T(0));
-        }
-    }
-}
-
-// ---- kernel 3: flat, any view -----------------------------------------------------------------------
-template <class T, int NIN, class F>
-__global__ void __launch_bounds__(256) nk_ew_flat_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b,
-                                                         EwPlan p, F f) {
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < p.total; i += stride) {
-        int64_t rem = i, o0 = p.b0, o1 = p.b1, o2 = p.b2;
-        for (int k = 0; k < p.nd; k++) {
-            int64_t idx = rem / p.div[k];
-            rem -= idx * p.div[k];
-            o0 += idx * p.s0[k]; o1 += idx * p.s1[k]; o2 += idx * p.s2[k];
-        }
-        out[o0] = f(a[o1], NIN == 2 ? b[o2] : T(0));
-    }
-}
-
-bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
-
-template <class T, int NIN, class F>
-int launch_ew(nk_ctx* ctx, T* out, const T* a, const T* b, const EwPlan& p, F f) {
-    constexpr int N = Vec4<T>::N;
-    const int block = 256;
-    const int last = p.nd - 1;
-    const bool inner_ok = p.row_major && p.s0[last] == 1 && (p.s1[last] == 1 || p.s1[last] == 0) &&
-                          (NIN == 1 || p.s2[last] == 1 || p.s2[last] == 0);
-    if (inner_ok && p.nd == 1) {
-        T* o = out + p.b0;
-        const T* pa = a + p.b1;
-        const T* pb = NIN == 2 ? b + p.b2 : nullptr;
-        // 128-bit path needs all streamed pointers 16-byte aligned
-        bool al = aligned16(o) && (p.s1[0] == 0 || aligned16(pa)) && (NIN == 1 || p.s2[0] == 0 || aligned16(pb));
-        if (al) {
-            int grid = nk_grid_for(ctx, (p.total + N - 1) / N, block, 16);
-            nk_ew_linear_kernel<T, NIN, F><<<grid, block, 0, ctx->stream>>>(o, pa, pb, p.total, int(p.s1[0]), int(p.s2[0]), f);
-            return nk_after_launch(ctx, "nk_ew_linear_kernel");
-        }
-    }
-    if (inner_ok && p.nd > 1 && p.ext[last] >= 128) {
-        const int64_t inner = p.ext[last];
-        const int64_t rows = p.total / inner;
-        bool vec = (inner % N == 0) && aligned16(out + p.b0) && aligned16(a + p.b1) && (NIN == 1 || aligned16(b + p.b2));
-        for (int k = 0; k < last && vec; k++)
-            vec = (p.s0[k] % N == 0) && (p.s1[k] % N == 0) && (NIN == 1 || p.s2[k] % N == 0);
-        int64_t cap = int64_t(ctx->prop.multiProcessorCount) * 16;
-        int grid = int(rows < cap ? rows : cap);
-        if (vec) nk_ew_rows_kernel<T, NIN, F, true><<<grid, block, 0, ctx->stream>>>(out, a, b, p, rows, inner, f);
-        else nk_ew_rows_kernel<T, NIN, F, false><<<grid, block, 0, ctx->stream>>>(out, a, b, p, rows, inner, f);
-        return nk_after_launch(ctx, "nk_ew_rows_kernel");
-    }
-    int grid = nk_grid_for(ctx, p.total, block, 16);
-    nk_ew_flat_kernel<T, NIN, F><<<grid, block, 0, ctx->stream>>>(out, a, b, p, f);
-    return nk_after_launch(ctx, "nk_ew_flat_kernel");
+    return launch_ew<T, 2>(ctx, out, a, b, p, BinF<T, FAMILY>{op, d});
 }
 
 // ---- broadcast backward: reduction over the dims where the origin is smaller -------------------------
@@ -302,15 +118,6 @@ __global__ void __launch_bounds__(128) nk_sum_tiles_kernel(const T* __restrict__
     }
 }
 
-template <class T> T* data_of(nk_buf* b) { return reinterpret_cast<T*>(b->ptr); }
-
-bool known_op(int op, bool allow_idy, bool allow_both) {
-    if (op >= NK_OP_ADD && op <= NK_OP_POW) return true;
-    if (op == NK_OP_IDY) return allow_idy;
-    if (op == NK_OP_MUL_BOTH) return allow_both;
-    return false;
-}
-
 }  // namespace
 
 // ------------------------------------------------------------------------------------------------
@@ -341,8 +148,8 @@ extern "C" int nk_broadcast(nk_ctx* ctx, int32_t op, int32_t dtype, int32_t rank
         }
         EwPlan p;
         make_plan(v0, &v1, f1, &v2, f2, &p);
-        if (dtype == NK_F32) return launch_ew<float, 2>(ctx, data_of<float>(drn), data_of<float>(a), data_of<float>(b), p, BinF<float, 0>{op, -1});
-        return launch_ew<double, 2>(ctx, data_of<double>(drn), data_of<double>(a), data_of<double>(b), p, BinF<double, 0>{op, -1});
+        if (dtype == NK_F32) return launch_binary<float, 0>(ctx, op, -1, data_of<float>(drn), data_of<float>(a), data_of<float>(b), p);
+        return launch_binary<double, 0>(ctx, op, -1, data_of<double>(drn), data_of<double>(a), data_of<double>(b), p);
     }
     // d >= 0: (origin t0, handle t1, drain t2), CPUBroadcast.java:99-158
     if (d > 1) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_broadcast: derivative index %d, expected 0 or 1", d);
@@ -396,45 +203,8 @@ extern "C" int nk_binary(nk_ctx* ctx, int32_t op, int32_t dtype, int32_t rank,
     EwPlan p;
     make_plan(v0, &v1, nullptr, &v2, nullptr, &p);
     int dd = d < 0 ? -1 : d;
-    if (dtype == NK_F32) return launch_ew<float, 2>(ctx, data_of<float>(drn), data_of<float>(a), data_of<float>(b), p, BinF<float, 1>{op, dd});
-    return launch_ew<double, 2>(ctx, data_of<double>(drn), data_of<double>(a), data_of<double>(b), p, BinF<double, 1>{op, dd});
-}
-
-extern "C" int nk_unary(nk_ctx* ctx, int32_t fun, int32_t dtype, int32_t rank,
-                        nk_buf* drn, const int32_t* cfg0, nk_buf* src, const int32_t* cfg1, int32_t d) {
-    NK_CHECK_CTX(ctx);
-    if (dtype != NK_F32 && dtype != NK_F64) return nk_fail(ctx, NK_ERR_UNSUPPORTED, "nk_unary: dtype %d not supported (F32/F64 only)", dtype);
-    if (fun < 0 || fun >= NK_FUN_COUNT) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_unary: unknown function id %d", fun);
-    NkView v0, v1;
-    int st;
-    if ((st = nk_view_parse(ctx, "nk_unary(drain)", drn, cfg0, rank, dtype, &v0))) return st;
-    if ((st = nk_view_parse(ctx, "nk_unary(src)", src, cfg1, rank, dtype, &v1))) return st;
-    for (int k = 0; k < rank; k++)
-        if (v0.shape[k] != v1.shape[k])
-            return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_unary: shapes differ at dim %d (%lld vs %lld)", k, (long long)v0.shape[k], (long long)v1.shape[k]);
-    EwPlan p;
-    make_plan(v0, &v1, nullptr, nullptr, nullptr, &p);
-    if (dtype == NK_F32) return launch_ew<float, 1>(ctx, data_of<float>(drn), data_of<float>(src), (const float*)nullptr, p, UnaryF<float>{fun, d >= 0});
-    return launch_ew<double, 1>(ctx, data_of<double>(drn), data_of<double>(src), (const double*)nullptr, p, UnaryF<double>{fun, d >= 0});
-}
-
-extern "C" int nk_scalar_binary(nk_ctx* ctx, int32_t op, int32_t dtype, int32_t rank,
-                                nk_buf* drn, const int32_t* cfg0, nk_buf* src, const int32_t* cfg1, double value, int32_t d) {
-    NK_CHECK_CTX(ctx);
-    if (dtype != NK_F32 && dtype != NK_F64) return nk_fail(ctx, NK_ERR_UNSUPPORTED, "nk_scalar_binary: dtype %d not supported (F32/F64 only)", dtype);
-    if (!known_op(op, true, false)) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_scalar_binary: unknown op %d", op);
-    NkView v0, v1;
-    int st;
-    if ((st = nk_view_parse(ctx, "nk_scalar_binary(drain)", drn, cfg0, rank, dtype, &v0))) return st;
-    if ((st = nk_view_parse(ctx, "nk_scalar_binary(src)", src, cfg1, rank, dtype, &v1))) return st;
-    for (int k = 0; k < rank; k++)
-        if (v0.shape[k] != v1.shape[k])
-            return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_scalar_binary: shapes differ at dim %d (%lld vs %lld)", k, (long long)v0.shape[k], (long long)v1.shape[k]);
-    EwPlan p;
-    make_plan(v0, &v1, nullptr, nullptr, nullptr, &p);
-    int dd = d < 0 ? -1 : d;
-    if (dtype == NK_F32) return launch_ew<float, 1>(ctx, data_of<float>(drn), data_of<float>(src), (const float*)nullptr, p, ScalarF<float>{op, dd, float(value)});
-    return launch_ew<double, 1>(ctx, data_of<double>(drn), data_of<double>(src), (const double*)nullptr, p, ScalarF<double>{op, dd, value});
+    if (dtype == NK_F32) return launch_binary<float, 1>(ctx, op, dd, data_of<float>(drn), data_of<float>(a), data_of<float>(b), p);
+    return launch_binary<double, 1>(ctx, op, dd, data_of<double>(drn), data_of<double>(a), data_of<double>(b), p);
 }
 
 extern "C" int nk_fill_fun(nk_ctx* ctx, int32_t fun, int32_t dtype, int32_t rank, nk_buf* drn, const int32_t* cfg0,

@@ -20,7 +20,8 @@ def _rand(dtype, n, dist, seed, p0, p1):
 
 
 def test_config1_conv2d_matches_the_simple_cpu_convolution(device, oracle):
-    a, k = _rand(np.float32, 256 * 256, 0, 42, -1.0, 1.0), _rand(np.float32, 25, 0, 142, -1.0, 1.0)
+    both = _rand(np.float32, 256 * 256 + 25, 0, 42, -1.0, 1.0)   # one stream of seed 42: the image, then the kernel
+    a, k = both[:256 * 256].copy(), both[256 * 256:].copy()
     co, ca, ck = ND.of_shape([252, 252]), ND.of_shape([256, 256]), ND.of_shape([5, 5])
     ref = np.zeros(co.size, dtype=np.float32)
     assert oracle.conv(ref, co.as_inline_array(), a, ca.as_inline_array(), k, ck.as_inline_array()) == 1   # SimpleCPUConvolution path
@@ -29,7 +30,8 @@ def test_config1_conv2d_matches_the_simple_cpu_convolution(device, oracle):
 
 
 def test_config2_channel_collapsing_conv(device, oracle):
-    a, k = _rand(np.float32, 64 * 512 * 512, 1, 7, 0.0, 1.0), _rand(np.float32, 64 * 9, 1, 107, 0.0, 1.0)
+    both = _rand(np.float32, 64 * 512 * 512 + 576, 1, 7, 0.0, 1.0)   # one N(0,1) stream of seed 7: the image, then the kernel
+    a, k = both[:64 * 512 * 512].copy(), both[64 * 512 * 512:].copy()
     co, ca, ck = ND.of_shape([1, 510, 510]), ND.of_shape([64, 512, 512]), ND.of_shape([64, 3, 3])
     ref = np.zeros(co.size, dtype=np.float32)
     assert oracle.conv(ref, co.as_inline_array(), a, ca.as_inline_array(), k, ck.as_inline_array(), threads=8) == 0   # general nd path
