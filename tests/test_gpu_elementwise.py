@@ -153,7 +153,10 @@ def test_broadcast_backward_reduction(device, oracle, dt, op, d):
     hence bit-exact for + - * and within 1 ulp per term for the pow/div derivative formulas."""
     rng = np.random.default_rng(31)
     cases = [([1, 3], [2, 1], [2, 3]), ([4, 1, 33], [1, 5, 33], [4, 5, 33]), ([1, 5, 33], [4, 1, 33], [4, 5, 33]),
-             ([1, 1, 6], [7, 8, 1], [7, 8, 6]), ([3, 4], [3, 4], [3, 4]), ([1], [9], [9])]
+             ([1, 1, 6], [7, 8, 1], [7, 8, 6]), ([3, 4], [3, 4], [3, 4]), ([1], [9], [9]),
+             # shapes that take the vectorised reduction (inner dim kept, multiple of the vector width)
+             ([8, 1, 64], [1, 6, 64], [8, 6, 64]), ([1, 5, 64], [4, 1, 64], [4, 5, 64]), ([3, 1, 64], [1, 5, 1], [3, 5, 64]),
+             ([1, 1, 128], [6, 7, 128], [6, 7, 128]), ([2, 1, 1, 32], [1, 3, 4, 32], [2, 3, 4, 32])]
     for s0, s1, s2 in cases:
         h = _inputs(rng, int(np.prod(s1)), dt, positive=(op == "**"))
         dr = _inputs(rng, int(np.prod(s2)), dt)
