@@ -67,6 +67,10 @@ __device__ __forceinline__ void nk_mbar_expect_tx(uint64_t* bar, unsigned bytes)
     unsigned a = (unsigned)__cvta_generic_to_shared(bar);
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(a), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void nk_mbar_arrive(uint64_t* bar) {
+    unsigned a = (unsigned)__cvta_generic_to_shared(bar);
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(a) : "memory");
+}
 __device__ __forceinline__ unsigned nk_mbar_try_wait(uint64_t* bar, unsigned parity) {
     unsigned a = (unsigned)__cvta_generic_to_shared(bar), ok;
     asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
@@ -112,13 +116,13 @@ struct TiledCfg {
     static constexpr int CPR = SW / CW;                       // LDGSTS chunks per row
     static constexpr int NIT = (SH * CPR + 255) / 256;        // LDGSTS chunks per thread
     static size_t smem_bytes(int NQ) {
-        // [stages | mbarriers (64 B) | weights | channel table (3 x int64 per channel)]
-        return size_t(STAGES) * STAGE_BYTES + 64 + size_t(NQ) * WPAD * sizeof(T) + 16 + size_t(NQ) * 3 * sizeof(int64_t);
+        // [stages | mbarriers + abort word (128 B) | weights | channel table (3 x int64 per channel)]
+        return size_t(STAGES) * STAGE_BYTES + 128 + size_t(NQ) * WPAD * sizeof(T) + 16 + size_t(NQ) * 3 * sizeof(int64_t);
     }
 };
 
 template <class T, int KH, int KW, int RH, bool TMA>
-__global__ void __launch_bounds__(256) nk_conv_tiled_kernel(T* __restrict__ out, T* __restrict__ partial,
+__global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __restrict__ out, T* __restrict__ partial,
                                                             const T* __restrict__ I, const T* __restrict__ K,
                                                             const TiledPlan p, const __grid_constant__ CUtensorMap tmap) {
     using C = TiledCfg<T, KH, KW, RH>;
@@ -126,7 +130,7 @@ __global__ void __launch_bounds__(256) nk_conv_tiled_kernel(T* __restrict__ out,
     extern __shared__ __align__(128) unsigned char nk_smem[];
     unsigned char* stage_base = nk_smem;
     uint64_t* mbar = reinterpret_cast<uint64_t*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES);
-    T* wsm = reinterpret_cast<T*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES + 64);
+    T* wsm = reinterpret_cast<T*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES + 128);
     // channel table: image offset, kernel offset, packed outer indices (for the tensor-map coordinates)
     int64_t* ctab = reinterpret_cast<int64_t*>((reinterpret_cast<uintptr_t>(wsm + size_t(p.NQ) * WPAD) + 15) & ~uintptr_t(15));
 
@@ -154,8 +158,14 @@ __global__ void __launch_bounds__(256) nk_conv_tiled_kernel(T* __restrict__ out,
     const int c_begin = split * cper;
     const int c_end = (c_begin + cper < p.NQ) ? c_begin + cper : p.NQ;
 
+    // TMA family: warps 0..7 compute, warp 8 feeds the pipeline. full[s] completes when the tile has landed
+    // (1 arrival + the tile's bytes), empty[s] when all 8 compute warps have finished reading stage s.
+    uint64_t* full_bar = mbar;
+    uint64_t* empty_bar = mbar + STAGES;
+    volatile int* abort_word = reinterpret_cast<volatile int*>(mbar + 2 * STAGES);
     if (TMA && tid == 0) {
-        for (int s = 0; s < STAGES; s++) nk_mbar_init(&mbar[s], 1);
+        for (int s = 0; s < STAGES; s++) { nk_mbar_init(&full_bar[s], 1); nk_mbar_init(&empty_bar[s], 8); }
+        *abort_word = 0;
         nk_fence_barrier_init();
     }
 
@@ -227,8 +237,8 @@ __global__ void __launch_bounds__(256) nk_conv_tiled_kernel(T* __restrict__ out,
         const int64_t packed = ctab[c * 3 + 2];
         for (int k = p.n_outer - 1; k >= 0; k--) coord[n++] = pidx[k] + int((packed >> (16 * k)) & 0xffff);
         // without a row dim in the map the box is a single row; the other tile rows are never stored from
-        nk_mbar_expect_tx(&mbar[stage], unsigned((p.has_y ? SH : 1) * SW * sizeof(T)));
-        nk_tma_load(stage_base + size_t(stage) * C::STAGE_BYTES, &tmap, &mbar[stage], p.tma_nd, coord);
+        nk_mbar_expect_tx(&full_bar[stage], unsigned((p.has_y ? SH : 1) * SW * sizeof(T)));
+        nk_tma_load(stage_base + size_t(stage) * C::STAGE_BYTES, &tmap, &full_bar[stage], p.tma_nd, coord);
         issued++;
     };
 
@@ -239,47 +249,10 @@ __global__ void __launch_bounds__(256) nk_conv_tiled_kernel(T* __restrict__ out,
         for (int x = 0; x < CW; x++) acc[i][x] = T(0);
 
     __syncthreads();   // weights + table + barrier init visible
-    if (TMA) {
-        if (tid == 0) {
-            nk_fence_proxy_async();
-            for (int s = 0; s < STAGES - 1; s++)
-                if (c_begin + s < c_end) tma_stage(s, c_begin + s);
-        }
-    } else {
-#pragma unroll
-        for (int s = 0; s < STAGES - 1; s++) {
-            if (c_begin + s < c_end) ldgsts_stage(s, c_begin + s);
-            nk_cp_async_commit();
-        }
-    }
+    const int n_it = c_end - c_begin;
 
-    bool gave_up = false;
-    for (int c = c_begin; c < c_end; c++) {
-        const int it = c - c_begin;
-        const int stage = it % STAGES;
-        if (TMA) {
-            // bounded wait for the tile of channel c; on expiry: flag, stop consuming, fall through to the exit
-            const unsigned parity = unsigned(it / STAGES) & 1u;
-            unsigned spins = 0;
-            while (!nk_mbar_try_wait(&mbar[stage], parity)) {
-                if (++spins > NK_TMA_SPIN_LIMIT) { gave_up = true; break; }
-            }
-            if (gave_up && p.status) atomicExch(p.status, 1);
-            // everyone is past the previous channel's reads before its stage is handed back to the copy engine;
-            // the vote makes the give-up decision uniform across the CTA
-            gave_up = __syncthreads_or(gave_up) != 0;
-            if (gave_up) break;
-            if (tid == 0) {
-                const int nxt = c + STAGES - 1;
-                if (nxt < c_end) tma_stage((nxt - c_begin) % STAGES, nxt);
-            }
-        } else {
-            nk_cp_async_wait<STAGES - 2>();
-            __syncthreads();   // tile c has landed for everyone; everyone is done reading the stage refilled below
-            const int nxt = c + STAGES - 1;
-            if (nxt < c_end) ldgsts_stage((nxt - c_begin) % STAGES, nxt);
-            nk_cp_async_commit();
-        }
+    // One channel's worth of multiply-adds for this thread (tile rows warp*RH .. +RH, columns lane*CW .. +CW).
+    auto consume = [&](int stage, int c) {
         const T* tile = reinterpret_cast<const T*>(stage_base + size_t(stage) * C::STAGE_BYTES) + (warp * RH) * SW + lane * CW;
         const T* wc = wsm + size_t(c) * WPAD;
         T w[C::WREG ? WPAD : CW];
@@ -311,21 +284,69 @@ __global__ void __launch_bounds__(256) nk_conv_tiled_kernel(T* __restrict__ out,
                 }
             }
         }
-    }
-    if (!TMA) nk_cp_async_wait<0>();
-    if (TMA && gave_up) {
-        // Requested copies may still be writing into this CTA's shared memory: thread 0 waits for each of the
-        // last STAGES requests (bounded) before anyone exits; nothing is stored.
-        if (tid == 0) {
-            for (int j = (issued > STAGES ? issued - STAGES : 0); j < issued; j++) {
-                unsigned spins = 0;
-                while (!nk_mbar_try_wait(&mbar[j % STAGES], unsigned(j / STAGES) & 1u)) {
-                    if (++spins > NK_TMA_SPIN_LIMIT) break;
+    };
+
+    if (TMA) {
+        // Every wait below is bounded; whoever runs out raises the CTA's abort word (and the host-visible status),
+        // everybody else notices it while polling, and the CTA leaves without storing anything.
+        auto wait_or_abort = [&](uint64_t* bar, unsigned parity) -> bool {
+            unsigned spins = 0;
+            while (!nk_mbar_try_wait(bar, parity)) {
+                ++spins;
+                if ((spins & 1023u) == 0 && *abort_word) return false;
+                if (spins > NK_TMA_SPIN_LIMIT) {
+                    *abort_word = 1;
+                    if (p.status) atomicExch(p.status, 1);
+                    return false;
                 }
+            }
+            return true;
+        };
+        if (warp == 8) {
+            if (lane == 0) {
+                nk_fence_proxy_async();
+                bool ok = true;
+                for (int it = 0; it < n_it && ok; it++) {
+                    const int stage = it % STAGES;
+                    if (it >= STAGES) ok = wait_or_abort(&empty_bar[stage], unsigned(it / STAGES - 1) & 1u);
+                    if (ok) tma_stage(stage, c_begin + it);
+                }
+                if (!ok || *abort_word) {
+                    // requested copies may still be landing in this CTA's shared memory: wait for the last ones (bounded)
+                    for (int j = (issued > STAGES ? issued - STAGES : 0); j < issued; j++) {
+                        unsigned spins = 0;
+                        while (!nk_mbar_try_wait(&full_bar[j % STAGES], unsigned(j / STAGES) & 1u))
+                            if (++spins > NK_TMA_SPIN_LIMIT) break;
+                    }
+                }
+            }
+        } else {
+            for (int it = 0; it < n_it; it++) {
+                const int stage = it % STAGES;
+                if (!wait_or_abort(&full_bar[stage], unsigned(it / STAGES) & 1u)) break;
+                consume(stage, c_begin + it);
+                __syncwarp();
+                if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
             }
         }
         __syncthreads();
-        return;
+        if (*abort_word) return;
+        if (warp == 8) return;   // the producer warp owns no outputs
+    } else {
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; s++) {
+            if (s < n_it) ldgsts_stage(s, c_begin + s);
+            nk_cp_async_commit();
+        }
+        for (int it = 0; it < n_it; it++) {
+            nk_cp_async_wait<STAGES - 2>();
+            __syncthreads();   // tile `it` has landed for everyone; everyone is done reading the stage refilled below
+            const int nxt = it + STAGES - 1;
+            if (nxt < n_it) ldgsts_stage(nxt % STAGES, c_begin + nxt);
+            nk_cp_async_commit();
+            consume(it % STAGES, c_begin + it);
+        }
+        nk_cp_async_wait<0>();
     }
 
     // ---- epilogue -----------------------------------------------------------------------------------------------
@@ -423,7 +444,7 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     if (grid > 0x7fffffffLL) return -1;
     cudaError_t e = cudaFuncSetAttribute(nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel)");
-    nk_conv_tiled_kernel<T, KH, KW, RH, TMA><<<unsigned(grid), 256, smem, ctx->stream>>>(out, partial, I, K, p, tmap);
+    nk_conv_tiled_kernel<T, KH, KW, RH, TMA><<<unsigned(grid), TMA ? 288 : 256, smem, ctx->stream>>>(out, partial, I, K, p, tmap);
     int st = nk_after_launch(ctx, TMA ? "nk_conv_tiled_kernel<tma>" : "nk_conv_tiled_kernel<ldgsts>");
     if (st || splits == 1) return st;
     const int64_t plane = p.NP * int64_t(p.OH) * p.OW;
