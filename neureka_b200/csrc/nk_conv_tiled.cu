@@ -2,7 +2,10 @@
 // encoding and the (KH, KW) dispatch. The kernels themselves are instantiated per dtype / loader / rows-per-thread
 // in nk_conv_tiled_inst_*.cu.
 
-#include "nk_conv_tiled.cuh"
+#include "nk_conv_wgrad.cuh"
+
+int nk_wgrad_dispatch_f32(nk_ctx*, int, int, float*, WgradPlan&, const TmaImage&, const TmaImage&);
+int nk_wgrad_dispatch_f64(nk_ctx*, int, int, double*, WgradPlan&, const TmaImage&, const TmaImage&);
 
 #define NK_DECL(suf, ty)                                                                                                   \
     int nk_tiled_dispatch_##suf##_ldgsts(nk_ctx*, int, int, ty*, const ty*, const ty*, TiledPlan&, const TmaImage*);       \
@@ -57,12 +60,211 @@ int nk_tma_encode(nk_ctx* ctx, int dtype, const TmaImage& img, int box_w, int bo
     return NK_OK;
 }
 
+// Tensor map description of a whole view: X, optionally Y, then the outer dims (innermost first). False when the
+// view cannot be described (unaligned base, strides that are not positive multiples of 16 bytes).
+static bool nk_describe_for_tma(const nk_buf* buf, const NkView& v, size_t es, bool has_y, int n_outer, TmaImage* img) {
+    const int rank = v.rank, X = rank - 1, Y = rank - 2;
+    const char* base = static_cast<const char*>(buf->ptr) + v.base * int64_t(es);
+    if (reinterpret_cast<uintptr_t>(base) % 16 || v.estride[X] != 1) return false;
+    int n = 0;
+    img->base = base;
+    img->dims[n] = uint64_t(v.shape[X]); img->strides_bytes[n] = es; n++;
+    if (has_y) {
+        if (v.estride[Y] <= 0 || (v.estride[Y] * int64_t(es)) % 16) return false;
+        img->dims[n] = uint64_t(v.shape[Y]); img->strides_bytes[n] = uint64_t(v.estride[Y]) * es; n++;
+    }
+    for (int k = n_outer - 1; k >= 0; k--) {
+        const int64_t ext = v.shape[k], st = v.estride[k];
+        img->dims[n] = uint64_t(ext);
+        if (ext == 1) {
+            uint64_t prev = img->strides_bytes[n - 1] * img->dims[n - 1];
+            img->strides_bytes[n] = ((prev + 15) / 16) * 16;
+            if (img->strides_bytes[n] == 0) img->strides_bytes[n] = 16;
+        } else {
+            if (st <= 0 || (st * int64_t(es)) % 16 || uint64_t(st) * es >= (uint64_t(1) << 40)) return false;
+            img->strides_bytes[n] = uint64_t(st) * es;
+        }
+        n++;
+    }
+    img->nd = n;
+    return n >= 2 && n <= 5;
+}
+
+// Deconvolution (d >= 0) whose result is the small, kernel-like tensor: D[p] = sum_q T1[p+q] * T2[q] in every dim
+// (the drain is not larger than T1 anywhere), the last one or two dims being a window of few taps over large planes.
+static int nk_wgrad_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_buf* s1, const NkView& v1,
+                        nk_buf* s2, const NkView& v2, bool* handled) {
+    if (ctx->conv_path == NK_CONV_TILED) return NK_OK;
+    const int rank = v0.rank, X = rank - 1, Y = rank - 2;
+    if (rank < 2 || !v0.imap_row_major) return NK_OK;
+    for (int k = 0; k < rank; k++)
+        if (v0.shape[k] > v1.shape[k]) return NK_OK;          // tau = p + q everywhere
+    const int64_t KW = v0.shape[X];
+    if (v2.shape[X] < 64 || KW > 9) return NK_OK;             // a real plane to reduce over, a real window
+    bool has_y = v0.shape[Y] <= 7 && v2.shape[Y] > 1;
+    int64_t KH = has_y ? v0.shape[Y] : 1;
+    const int n_outer = has_y ? rank - 2 : rank - 1;
+    if (n_outer > 3) return NK_OK;
+    // long reductions only: otherwise the generic family is as good
+    int64_t terms = 1;
+    for (int k = 0; k < rank; k++) terms *= v2.shape[k];
+    if (terms < 65536) return NK_OK;
+    WgradPlan p;
+    memset(&p, 0, sizeof(p));
+    p.n_outer = n_outer;
+    p.has_y = has_y ? 1 : 0;
+    p.NP = 1; p.NQ = 1;
+    for (int k = 0; k < n_outer; k++) {
+        p.oext[k] = v0.shape[k]; p.os[k] = v0.estride[k];
+        p.qext[k] = v2.shape[k];
+        p.NP *= v0.shape[k];
+        p.NQ *= v2.shape[k];
+    }
+    p.EW = int(v2.shape[X]);
+    p.EH = has_y ? int(v2.shape[Y]) : 1;
+    p.sDx = v0.estride[X];
+    p.sDy = has_y ? v0.estride[Y] : 0;
+    p.bD = v0.base;
+    const size_t es = nk_dtype_size(dtype);
+    TmaImage imgA, imgE;
+    if (!nk_describe_for_tma(s1, v1, es, has_y, n_outer, &imgA)) return NK_OK;
+    if (!nk_describe_for_tma(s2, v2, es, has_y, n_outer, &imgE)) return NK_OK;
+    p.nd = imgA.nd;
+    int st = (dtype == NK_F32) ? nk_wgrad_dispatch_f32(ctx, int(KH), int(KW), (float*)drn->ptr, p, imgA, imgE)
+                               : nk_wgrad_dispatch_f64(ctx, int(KH), int(KW), (double*)drn->ptr, p, imgA, imgE);
+    if (st == -1) return NK_OK;
+    if (st != NK_OK) return st;
+    ctx->last_conv_path = NK_CONV_TMA;
+    *handled = true;
+    return NK_OK;
+}
+
+// Deconvolution (d >= 0) whose result is the larger, image-like tensor -- the gradient of a convolution w.r.t. its
+// image: D[p] = sum_t T1[t] * T2[p - t] in the sliding dims. Rewritten as a correlation of the zero-padded error T2
+// with the flipped weights T1, it runs on the same TMA kernel: tile loads start s1-1 elements before the output
+// coordinate (the tensor map returns zeros outside T2, which is exactly the reference's "no such term"), and the
+// weights are staged back to front through negative kernel strides. Outer dims may be batch-like (T1 extent 1: T2
+// follows the output index), flipped outer windows, or follow T1 (T2 extent 1, e.g. the channels of the image).
+static int nk_deconv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_buf* s1, const NkView& v1,
+                               nk_buf* s2, const NkView& v2, bool* handled) {
+    if (ctx->conv_path == NK_CONV_TILED) return NK_OK;      // the padded form needs the tensor map's zero fill
+    const int rank = v0.rank;
+    const int X = rank - 1;
+    if (!v0.imap_row_major || rank < 2) return NK_OK;
+    {
+        int st = nk_wgrad_try(ctx, dtype, drn, v0, s1, v1, s2, v2, handled);
+        if (st || *handled) return st;
+    }
+    const NkView& vi = v2;   // image = T2 (the error)
+    const NkView& vk = v1;   // weights = T1
+    if (vi.estride[X] != 1 || v0.estride[X] != 1) return NK_OK;
+    // sliding dim X: tau = p - q (drain larger than T1), window of s1 taps
+    if (!(v0.shape[X] > vk.shape[X])) return NK_OK;
+    const int64_t KW = vk.shape[X];
+    if (v0.shape[X] < 16) return NK_OK;
+    int n_outer = rank - 1;
+    int64_t KH = 1;
+    bool has_y = false;
+    const int Y = rank - 2;
+    if (v0.shape[Y] > vk.shape[Y] && vk.shape[Y] <= 7 && v0.shape[Y] > 1 && vi.shape[Y] > 1) { has_y = true; KH = vk.shape[Y]; n_outer = rank - 2; }
+    if (n_outer > 3 || 1 + (has_y ? 1 : 0) + n_outer > 5) return NK_OK;
+    TiledPlan p;
+    memset(&p, 0, sizeof(p));
+    p.n_outer = n_outer;
+    p.has_y = has_y ? 1 : 0;
+    p.NP = 1;
+    int64_t NQ = 1;
+    int64_t bK = vk.base;
+    for (int k = 0; k < n_outer; k++) {
+        const int64_t e0 = v0.shape[k], e1 = vk.shape[k], e2 = vi.shape[k];
+        p.oext[k] = e0; p.os[k] = v0.estride[k];
+        if (e0 > e1) {
+            // tau = p - q: flipped window of e1 taps over T2 starting at p - (e1 - 1); e1 == 1 is the batch-like case
+            p.qext[k] = e1; p.pI[k] = vi.estride[k]; p.qI[k] = vi.estride[k];
+            p.pK[k] = 0; p.qK[k] = -vk.estride[k];
+            bK += (e1 - 1) * vk.estride[k];
+            p.padO[k] = int(e1 - 1);
+        } else {
+            // tau = p + q, q over T2: only the consistent case p + q < e1 for every p, q is taken here
+            if (e0 + e2 - 1 > e1) return NK_OK;
+            p.qext[k] = e2; p.pI[k] = 0; p.qI[k] = vi.estride[k];
+            p.pK[k] = vk.estride[k]; p.qK[k] = vk.estride[k];
+            p.padO[k] = 0;
+        }
+        if (p.qext[k] > 65535) return NK_OK;
+        p.NP *= e0;
+        NQ *= p.qext[k];
+    }
+    if (NQ > 4096) return NK_OK;
+    p.NQ = int(NQ);
+    if (vi.shape[X] > 0x3fffffff || v0.shape[X] > 0x3fffffff) return NK_OK;
+    const size_t es = nk_dtype_size(dtype);
+    const int CW = int(16 / es);
+    p.IW = int(vi.shape[X]); p.OW = int(v0.shape[X]);
+    p.padX = int(KW - 1);
+    p.xoff = (CW - p.padX % CW) % CW;
+    p.sKx = -vk.estride[X];
+    bK += (KW - 1) * vk.estride[X];
+    if (has_y) {
+        p.IH = int(vi.shape[Y]); p.OH = int(v0.shape[Y]);
+        p.padY = int(KH - 1);
+        p.sIy = vi.estride[Y]; p.sOy = v0.estride[Y];
+        p.sKy = -vk.estride[Y];
+        bK += (KH - 1) * vk.estride[Y];
+    } else {
+        p.IH = 1; p.OH = 1;
+    }
+    p.bI = vi.base; p.bK = bK; p.bO = v0.base;
+    p.vec = 0;
+    bool vec_out = p.xoff == 0 && aligned_to(drn->ptr, 16) && (p.bO % CW == 0) && (p.sOy % CW == 0);
+    for (int k = 0; k < n_outer; k++)
+        if (p.os[k] % CW) vec_out = false;
+    p.vec_out = vec_out ? 1 : 0;
+
+    // tensor map over T2
+    TmaImage img;
+    if (!aligned_to(static_cast<const char*>(s2->ptr) + p.bI * int64_t(es), 16)) return NK_OK;
+    int n = 0;
+    img.base = static_cast<const char*>(s2->ptr) + p.bI * int64_t(es);
+    img.dims[n] = uint64_t(p.IW); img.strides_bytes[n] = es; n++;
+    if (has_y) {
+        if (p.sIy <= 0 || (p.sIy * int64_t(es)) % 16) return NK_OK;
+        img.dims[n] = uint64_t(p.IH); img.strides_bytes[n] = uint64_t(p.sIy) * es; n++;
+    }
+    for (int k = n_outer - 1; k >= 0; k--) {
+        const int64_t ext = vi.shape[k], st = vi.estride[k];
+        img.dims[n] = uint64_t(ext);
+        if (ext == 1) {
+            uint64_t prev = img.strides_bytes[n - 1] * img.dims[n - 1];
+            img.strides_bytes[n] = ((prev + 15) / 16) * 16;
+            if (img.strides_bytes[n] == 0) img.strides_bytes[n] = 16;
+        } else {
+            if (st <= 0 || (st * int64_t(es)) % 16 || uint64_t(st) * es >= (uint64_t(1) << 40)) return NK_OK;
+            img.strides_bytes[n] = uint64_t(st) * es;
+        }
+        n++;
+    }
+    if (n < 2) return NK_OK;
+    img.nd = n;
+    p.tma_nd = n;
+
+    int st;
+    const bool f32 = dtype == NK_F32;
+    if (f32) st = nk_tiled_dispatch_f32_tma4(ctx, int(KH), int(KW), (float*)drn->ptr, (const float*)s2->ptr, (const float*)s1->ptr, p, &img);
+    else st = nk_tiled_dispatch_f64_tma4(ctx, int(KH), int(KW), (double*)drn->ptr, (const double*)s2->ptr, (const double*)s1->ptr, p, &img);
+    if (st == -1) return NK_OK;
+    if (st != NK_OK) return st;
+    ctx->last_conv_path = NK_CONV_TMA;
+    *handled = true;
+    return NK_OK;
+}
+
 // Returns NK_OK with *handled = true when the call was launched on a tiled family, NK_OK with *handled = false
 // when the views do not qualify (the caller then uses the generic family).
 int nk_conv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_buf* s1, const NkView& v1,
                       nk_buf* s2, const NkView& v2, int d, bool force, bool* handled) {
     *handled = false;
-    if (d >= 0) return NK_OK;
+    if (d >= 0) return nk_deconv_tiled_try(ctx, dtype, drn, v0, s1, v1, s2, v2, handled);
     const int rank = v0.rank;
     const int X = rank - 1;
     if (!v0.imap_row_major) return NK_OK;

@@ -39,6 +39,11 @@ struct TiledPlan {
     int vec_out;   // 16-byte stores to the drain are legal
     int has_y;     // the second-to-last dim is the tile's row dim (else tiles are one row high)
     int tma_nd;    // TMA: dims of the tensor map (2..5)
+    // Deconvolution as a padded correlation (TMA family only): tile loads start pad elements before the output
+    // coordinate (the tensor map zero-fills outside the image) and the weights are staged flipped by the host's
+    // choice of kernel strides. xoff shifts the tile grid left so that x0 - padX stays 16-byte aligned.
+    int padX, padY, xoff;
+    int padO[NK_MAX_RANK];
     int* status;   // TMA: host-mapped word, set non-zero when a bounded wait ran out
 };
 
@@ -153,7 +158,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             pidx[k] = p.pI[k] != 0 ? int(idx) : 0;   // the image index follows the output index only where pI != 0
         }
     }
-    const int x0 = tx * TW, y0 = ty * TH;
+    const int x0 = tx * TW - p.xoff, y0 = ty * TH;
     const int cper = (p.NQ + p.splits - 1) / p.splits;
     const int c_begin = split * cper;
     const int c_end = (c_begin + cper < p.NQ) ? c_begin + cper : p.NQ;
@@ -231,11 +236,11 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     int issued = 0;                             // tiles requested so far (thread 0)
     auto tma_stage = [&](int stage, int c) {   // executed by thread 0 only
         int coord[5];
-        coord[0] = x0;
+        coord[0] = x0 - p.padX;
         int n = 1;
-        if (p.has_y) coord[n++] = y0;
+        if (p.has_y) coord[n++] = y0 - p.padY;
         const int64_t packed = ctab[c * 3 + 2];
-        for (int k = p.n_outer - 1; k >= 0; k--) coord[n++] = pidx[k] + int((packed >> (16 * k)) & 0xffff);
+        for (int k = p.n_outer - 1; k >= 0; k--) coord[n++] = pidx[k] + int((packed >> (16 * k)) & 0xffff) - p.padO[k];
         // without a row dim in the map the box is a single row; the other tile rows are never stored from
         nk_mbar_expect_tx(&full_bar[stage], unsigned((p.has_y ? SH : 1) * SW * sizeof(T)));
         nk_tma_load(stage_base + size_t(stage) * C::STAGE_BYTES, &tmap, &full_bar[stage], p.tma_nd, coord);
@@ -354,7 +359,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
 #pragma unroll
     for (int i = 0; i < RH; i++) {
         const int oy = y0 + warp * RH + i;
-        if (oy >= p.OH || ox >= p.OW) continue;
+        if (oy >= p.OH || ox >= p.OW || ox + CW <= 0) continue;
         T* dst;
         bool vec_ok;
         if (p.splits == 1) {
@@ -364,13 +369,13 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             dst = partial + ((int64_t(split) * p.NP + pflat) * p.OH + oy) * int64_t(p.OW) + ox;
             vec_ok = (p.OW % CW) == 0;
         }
-        if (vec_ok && ox + CW <= p.OW) {
+        if (vec_ok && ox >= 0 && ox + CW <= p.OW) {
             if (sizeof(T) == 4) *reinterpret_cast<float4*>(dst) = *reinterpret_cast<float4*>(&acc[i][0]);
             else *reinterpret_cast<double2*>(dst) = *reinterpret_cast<double2*>(&acc[i][0]);
         } else {
 #pragma unroll
             for (int x = 0; x < CW; x++)
-                if (ox + x < p.OW) dst[x] = acc[i][x];
+                if (ox + x >= 0 && ox + x < p.OW) dst[x] = acc[i][x];
         }
     }
 }
@@ -410,7 +415,7 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     using C = TiledCfg<T, KH, KW, RH>;
     const size_t smem = C::smem_bytes(p.NQ);
     if (smem > size_t(ctx->prop.sharedMemPerBlockOptin)) return -1;   // caller falls back to another family
-    p.tilesX = (p.OW + C::TW - 1) / C::TW;
+    p.tilesX = (p.OW + p.xoff + C::TW - 1) / C::TW;
     p.tilesY = (p.OH + C::TH - 1) / C::TH;
     const int64_t tiles = int64_t(p.tilesX) * p.tilesY * p.NP;
     // channel split: only when the tiles alone cannot fill the machine and each part keeps >= 4 channels

@@ -1,0 +1,239 @@
+// Deconvolution (d >= 0) whose result is the SMALL, kernel-like tensor -- the gradient of a convolution w.r.t. its
+// kernel: D[p] = sum_q T1[p + q] * T2[q], q over the whole (large) T2, p over a window of KH x KW taps (times a few
+// outer coordinates). Few outputs, each a reduction over millions of products.
+//
+// One CTA walks a list of work units; a unit is one TH x TW tile of T2 (the error) for one outer reduction index,
+// together with the (TH+KH-1) x (TW+KW-1) tile of T1 (the image) at the same position. Both tiles arrive by TMA
+// (zero fill outside the tensors: a missing term contributes 0, exactly like the reference's range check) into a
+// two-stage shared-memory ring. A thread owns RH x CW positions of the error tile and keeps all KH x KW partial
+// sums in registers; every image row segment it loads feeds up to KH taps rows. After its last unit the CTA reduces
+// the partial sums (warp shuffles, then the eight warp results in order) and writes one partial window to scratch;
+// a second kernel adds the CTAs' windows in CTA order, so the result does not depend on scheduling.
+#pragma once
+#include "nk_conv_tiled.cuh"
+
+struct WgradPlan {
+    int n_outer;
+    int64_t oext[NK_MAX_RANK], os[NK_MAX_RANK];   // outer output extents and drain strides
+    int64_t qext[NK_MAX_RANK];                    // outer reduction extents (T2's extents)
+    int64_t NP;                                   // outer outputs
+    int64_t NQ;                                   // outer reduction indices
+    int EH, EW;                                   // error tile grid is laid over EH x EW
+    int tilesX, tilesY;
+    int64_t units;                                // NQ * tilesY * tilesX work units per outer output
+    int chunks;                                   // CTAs per outer output
+    int has_y;
+    int nd;                                       // tensor-map dims (same for both maps)
+    int64_t sDy, sDx, bD;                         // drain strides of the window dims and base
+    int* status;
+};
+
+template <class T, int KH, int KW>
+struct WgradCfg {
+    static constexpr int CW = 16 / int(sizeof(T));
+    static constexpr int RH = 4;
+    static constexpr int TW = 32 * CW;
+    static constexpr int TH = 8 * RH;
+    static constexpr int HALO_W = ((KW - 1 + CW - 1) / CW) * CW;
+    static constexpr int SW = TW + HALO_W;
+    static constexpr int SH = TH + KH - 1;
+    static constexpr int NS = CW + HALO_W;
+    static constexpr int A_BYTES = ((SH * SW * int(sizeof(T)) + 127) / 128) * 128;
+    static constexpr int E_BYTES = ((TH * TW * int(sizeof(T)) + 127) / 128) * 128;
+    static constexpr int STAGES = 2;
+    static size_t smem_bytes() { return size_t(STAGES) * (A_BYTES + E_BYTES) + 128 + size_t(8) * KH * KW * sizeof(T); }
+};
+
+template <class T, int KH, int KW>
+__global__ void __launch_bounds__(256) nk_conv_wgrad_kernel(T* __restrict__ partial, const WgradPlan p,
+                                                            const __grid_constant__ CUtensorMap mapA,
+                                                            const __grid_constant__ CUtensorMap mapE) {
+    using C = WgradCfg<T, KH, KW>;
+    constexpr int CW = C::CW, RH = C::RH, TW = C::TW, TH = C::TH, SW = C::SW, SH = C::SH, NS = C::NS, STAGES = C::STAGES;
+    extern __shared__ __align__(128) unsigned char nk_smem[];
+    unsigned char* a_base = nk_smem;
+    unsigned char* e_base = nk_smem + size_t(STAGES) * C::A_BYTES;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(nk_smem + size_t(STAGES) * (C::A_BYTES + C::E_BYTES));
+    volatile int* abort_word = reinterpret_cast<volatile int*>(full_bar + STAGES);
+    T* red = reinterpret_cast<T*>(nk_smem + size_t(STAGES) * (C::A_BYTES + C::E_BYTES) + 128);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int64_t pflat = blockIdx.x / p.chunks;
+    const int chunk = int(blockIdx.x % p.chunks);
+    int pidx[NK_TILED_MAX_OUTER];
+    {
+        int64_t rem = pflat;
+        for (int k = p.n_outer - 1; k >= 0; k--) { pidx[k] = int(rem % p.oext[k]); rem /= p.oext[k]; }
+    }
+    const int64_t per = (p.units + p.chunks - 1) / p.chunks;
+    const int64_t u_begin = per * chunk;
+    const int64_t u_end = (u_begin + per < p.units) ? u_begin + per : p.units;
+    const int64_t n_it = u_end - u_begin;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) nk_mbar_init(&full_bar[s], 1);
+        *abort_word = 0;
+        nk_fence_barrier_init();
+    }
+    __syncthreads();
+
+    int64_t last_issued = -1;
+    auto issue = [&](int stage, int64_t u) {   // thread 0
+        last_issued = u - u_begin;
+        int64_t rem = u;
+        const int tx = int(rem % p.tilesX); rem /= p.tilesX;
+        const int ty = int(rem % p.tilesY); rem /= p.tilesY;
+        int ca[5], ce[5];
+        ca[0] = ce[0] = tx * TW;
+        int n = 1;
+        if (p.has_y) { ca[n] = ce[n] = ty * TH; n++; }
+        for (int k = p.n_outer - 1; k >= 0; k--) {
+            const int q = int(rem % p.qext[k]);
+            rem /= p.qext[k];
+            ce[n] = q;
+            ca[n] = pidx[k] + q;
+            n++;
+        }
+        const unsigned bytes = unsigned(((p.has_y ? SH : 1) * SW + (p.has_y ? TH : 1) * TW) * sizeof(T));
+        nk_mbar_expect_tx(&full_bar[stage], bytes);
+        nk_tma_load(a_base + size_t(stage) * C::A_BYTES, &mapA, &full_bar[stage], p.nd, ca);
+        nk_tma_load(e_base + size_t(stage) * C::E_BYTES, &mapE, &full_bar[stage], p.nd, ce);
+    };
+
+    T acc[KH][KW];
+#pragma unroll
+    for (int a = 0; a < KH; a++)
+#pragma unroll
+        for (int b = 0; b < KW; b++) acc[a][b] = T(0);
+
+    if (tid == 0) {
+        nk_fence_proxy_async();
+        if (n_it > 0) issue(0, u_begin);
+    }
+    bool gave_up = false;
+    for (int64_t it = 0; it < n_it; it++) {
+        const int stage = int(it % STAGES);
+        unsigned spins = 0;
+        while (!nk_mbar_try_wait(&full_bar[stage], unsigned(it / STAGES) & 1u)) {
+            if (++spins > NK_TMA_SPIN_LIMIT) { gave_up = true; break; }
+        }
+        if (gave_up && p.status) atomicExch(p.status, 1);
+        // everyone has finished reading the other stage (previous unit) before it is refilled; uniform give-up vote
+        gave_up = __syncthreads_or(gave_up) != 0;
+        if (gave_up) break;
+        if (tid == 0 && it + 1 < n_it) issue(int((it + 1) % STAGES), u_begin + it + 1);
+
+        const T* at = reinterpret_cast<const T*>(a_base + size_t(stage) * C::A_BYTES) + (warp * RH) * SW + lane * CW;
+        const T* et = reinterpret_cast<const T*>(e_base + size_t(stage) * C::E_BYTES) + (warp * RH) * TW + lane * CW;
+        // when the maps have no row dim only row 0 of each tile is real: rows beyond it must not contribute
+        const int rows = p.has_y ? RH : (warp == 0 ? 1 : 0);
+        if (rows == 0) continue;   // nothing real in this warp's tile rows (and they were never written)
+        T ev[RH][CW];
+#pragma unroll
+        for (int i = 0; i < RH; i++) {
+            if (i < rows) {
+                if (sizeof(T) == 4) *reinterpret_cast<float4*>(ev[i]) = *reinterpret_cast<const float4*>(et + i * TW);
+                else *reinterpret_cast<double2*>(ev[i]) = *reinterpret_cast<const double2*>(et + i * TW);
+            } else {
+#pragma unroll
+                for (int x = 0; x < CW; x++) ev[i][x] = T(0);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < RH + KH - 1; j++) {
+            if (!p.has_y && j > 0) break;
+            T seg[NS];
+#pragma unroll
+            for (int v = 0; v < NS / CW; v++) {
+                if (sizeof(T) == 4) *reinterpret_cast<float4*>(&seg[v * CW]) = *reinterpret_cast<const float4*>(at + j * SW + v * CW);
+                else *reinterpret_cast<double2*>(&seg[v * CW]) = *reinterpret_cast<const double2*>(at + j * SW + v * CW);
+            }
+#pragma unroll
+            for (int ky = 0; ky < KH; ky++) {
+                const int i = j - ky;   // error row that meets image row j at tap row ky
+                if (i >= 0 && i < RH) {
+#pragma unroll
+                    for (int kx = 0; kx < KW; kx++)
+#pragma unroll
+                        for (int x = 0; x < CW; x++) acc[ky][kx] = fma(seg[kx + x], ev[i][x], acc[ky][kx]);
+                }
+            }
+        }
+    }
+    if (gave_up) {
+        // the request for the next unit may still be landing: wait for it (bounded) before leaving
+        if (tid == 0 && last_issued >= 0) {
+            unsigned spins = 0;
+            while (!nk_mbar_try_wait(&full_bar[last_issued % STAGES], unsigned(last_issued / STAGES) & 1u))
+                if (++spins > NK_TMA_SPIN_LIMIT) break;
+        }
+        __syncthreads();
+        return;
+    }
+
+    // ---- CTA reduction: lanes by shuffle (fixed tree), then the 8 warps in order ----------------------------------
+#pragma unroll
+    for (int a = 0; a < KH; a++)
+#pragma unroll
+        for (int b = 0; b < KW; b++) {
+            T v = acc[a][b];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
+            if (lane == 0) red[warp * KH * KW + a * KW + b] = v;
+        }
+    __syncthreads();
+    if (tid < KH * KW) {
+        T total = 0;
+        for (int w = 0; w < 8; w++) total += red[w * KH * KW + tid];
+        partial[(pflat * p.chunks + chunk) * int64_t(KH * KW) + tid] = total;
+    }
+}
+
+template <class T>
+__global__ void nk_conv_wgrad_finish_kernel(T* __restrict__ out, const T* __restrict__ partial, WgradPlan p, int KH, int KW) {
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int win = KH * KW;
+    if (i >= p.NP * win) return;
+    const int64_t pflat = i / win;
+    const int t = int(i % win);
+    T total = 0;
+    for (int c = 0; c < p.chunks; c++) total += partial[(pflat * p.chunks + c) * int64_t(win) + t];
+    int64_t o = p.bD + (t / KW) * p.sDy + (t % KW) * p.sDx;
+    int64_t rem = pflat;
+    for (int k = p.n_outer - 1; k >= 0; k--) { o += (rem % p.oext[k]) * p.os[k]; rem /= p.oext[k]; }
+    out[o] = total;
+}
+
+template <class T, int KH, int KW>
+int nk_launch_wgrad(nk_ctx* ctx, T* out, WgradPlan& p, const TmaImage& imgA, const TmaImage& imgE) {
+    using C = WgradCfg<T, KH, KW>;
+    const size_t smem = C::smem_bytes();
+    if (smem > size_t(ctx->prop.sharedMemPerBlockOptin) || C::SW > 256 || C::SH > 256) return -1;
+    p.tilesX = (p.EW + C::TW - 1) / C::TW;
+    p.tilesY = p.has_y ? (p.EH + C::TH - 1) / C::TH : 1;
+    p.units = p.NQ * int64_t(p.tilesY) * p.tilesX;
+    int64_t chunks = (int64_t(ctx->prop.multiProcessorCount) * 4 + p.NP - 1) / p.NP;
+    if (chunks > p.units) chunks = p.units;
+    if (chunks > 4096) chunks = 4096;
+    if (chunks < 1) chunks = 1;
+    p.chunks = int(chunks);
+    if (p.NP * chunks > 0x7fffffffLL) return -1;
+    const int dt = sizeof(T) == 4 ? NK_F32 : NK_F64;
+    CUtensorMap mapA, mapE;
+    int st = nk_tma_encode(ctx, dt, imgA, C::SW, C::SH, p.has_y != 0, &mapA);
+    if (st) return st;
+    st = nk_tma_encode(ctx, dt, imgE, C::TW, C::TH, p.has_y != 0, &mapE);
+    if (st) return st;
+    void* scratch = nullptr;
+    st = nk_scratch(ctx, size_t(p.NP) * size_t(chunks) * KH * KW * sizeof(T), &scratch);
+    if (st) return st;
+    p.status = ctx->tma_status_dev;
+    cudaError_t e = cudaFuncSetAttribute(nk_conv_wgrad_kernel<T, KH, KW>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_wgrad_kernel)");
+    nk_conv_wgrad_kernel<T, KH, KW><<<unsigned(p.NP * chunks), 256, smem, ctx->stream>>>(reinterpret_cast<T*>(scratch), p, mapA, mapE);
+    st = nk_after_launch(ctx, "nk_conv_wgrad_kernel");
+    if (st) return st;
+    const int64_t n = p.NP * KH * KW;
+    nk_conv_wgrad_finish_kernel<T><<<unsigned((n + 127) / 128), 128, 0, ctx->stream>>>(out, reinterpret_cast<const T*>(scratch), p, KH, KW);
+    return nk_after_launch(ctx, "nk_conv_wgrad_finish_kernel");
+}

@@ -36,6 +36,23 @@ def check_conv(device, oracle, dt, c0, n0, a, c1, b, c2, d, path=L.NK_CONV_AUTO)
     return got
 
 
+def check_against_oracle_sampled(oracle, dt, got, c0, a, c1, b, c2, d, rng, n_ranges=6, span=400):
+    """The reference's deconvolution scans all of T2 for every drain element, so the oracle is only affordable on
+    sampled ranges of a large drain (dense drains only: flat index == data offset)."""
+    dt = np.dtype(dt)
+    n = c0.size
+    span = min(span, n)
+    starts = sorted(set([0, n - span] + [int(x) for x in rng.integers(0, n - span + 1, size=n_ranges)]))
+    ref, scale = np.zeros(n, dtype=dt), np.zeros(n, dtype=dt)
+    for s0 in starts:
+        oracle.conv_range(ref, c0.as_inline_array(), a, c1.as_inline_array(), b, c2.as_inline_array(), d, s0, s0 + span)
+        oracle.conv_range(scale, c0.as_inline_array(), np.abs(a), c1.as_inline_array(), np.abs(b), c2.as_inline_array(), d, s0, s0 + span)
+        seg = slice(s0, s0 + span)
+        err = np.abs(got[seg].astype(np.float64) - ref[seg].astype(np.float64))
+        bound = TOL[dt] * np.maximum(scale[seg].astype(np.float64), np.finfo(dt).tiny)
+        assert np.all(err <= bound), f"max err {err.max()} vs bound {bound[err.argmax()]} in range starting at {s0}"
+
+
 @pytest.mark.parametrize("dt", [np.float32, np.float64])
 def test_golden_forward(device, kat, dt):
     for v in kat["conv_forward"]:
@@ -168,6 +185,60 @@ def test_stencil_shapes_all_kernel_families(device, oracle, dt, case):
         except ValueError as e:
             assert path in (L.NK_CONV_TILED, L.NK_CONV_TMA) and "does not apply" in str(e)
     assert L.NK_CONV_AUTO in got and L.NK_CONV_GENERIC in got
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("case", [
+    ([96, 200], [5, 5]), ([3, 70, 150], [1, 3, 3]), ([6, 40, 300], [6, 3, 3]), ([2, 5, 64, 130], [1, 5, 5, 5]),
+    ([20, 33, 140], [3, 7, 7]), ([1, 260], [1, 9]), ([40, 256], [40, 3]), ([2, 3, 34, 40, 70], [1, 3, 3, 3, 3]), ([16, 24, 72], [7, 7, 7]),
+])
+def test_image_gradient_as_padded_correlation(device, oracle, dt, case):
+    """Gradient of a convolution w.r.t. its image: XConvRight(error, kernel, zeros(image shape)) -> the implementation
+    sees (drain = image-shaped, T1 = kernel, T2 = error) with d = 0. AUTO routes it to the zero-padded, flipped
+    TMA correlation; it must agree with the oracle's deconvolution and with the generic gather family."""
+    rng = np.random.default_rng(13)
+    sa, sb = case
+    so = [abs(x - y) + 1 for x, y in zip(sa, sb)]
+    k = rng.standard_normal(int(np.prod(sb))).astype(dt)
+    e = rng.standard_normal(int(np.prod(so))).astype(dt)
+    c0, c1, c2 = ND.of_shape(sa), ND.of_shape(sb), ND.of_shape(so)
+    auto = gpu_conv(device, np.zeros(c0.size, dtype=dt), c0, k, c1, e, c2, d=0)
+    family = device.last_conv_path()
+    generic = gpu_conv(device, np.zeros(c0.size, dtype=dt), c0, k, c1, e, c2, d=0, path=L.NK_CONV_GENERIC)
+    assert device.last_conv_path() == L.NK_CONV_GENERIC
+    check_against_oracle_sampled(oracle, dt, auto, c0, k, c1, e, c2, 0, rng)
+    # a tensor map needs the error's row stride to be a multiple of 16 bytes; other shapes stay on the gather family
+    row_bytes = so[-1] * np.dtype(dt).itemsize
+    if row_bytes % 16 == 0:
+        assert family == L.NK_CONV_TMA, "the image gradient did not take the tiled path"
+    scale = np.abs(generic).max()
+    assert np.abs(auto - generic).max() <= (1e-5 if dt == np.float32 else 1e-12) * scale * 4
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("case", [
+    ([300, 520], [5, 5]), ([3, 70, 150], [1, 3, 3]), ([4, 8, 100, 260], [1, 8, 5, 5]), ([64, 64, 64], [7, 7, 7]),
+    ([2, 1040], [1, 5]), ([6, 130, 264], [6, 3, 3]), ([40, 72, 136], [3, 7, 7]),
+])
+def test_kernel_gradient_reduction(device, oracle, dt, case):
+    """Gradient of a convolution w.r.t. its kernel: (drain = kernel-shaped, T1 = image, T2 = error), d = 0: few
+    outputs, each a sum over the whole error. AUTO may take the TMA reduction kernel; it must agree with the oracle's
+    deconvolution and with the generic family."""
+    rng = np.random.default_rng(17)
+    sa, sb = case
+    so = [abs(x - y) + 1 for x, y in zip(sa, sb)]
+    a = rng.standard_normal(int(np.prod(sa))).astype(dt)
+    e = rng.standard_normal(int(np.prod(so))).astype(dt)
+    c0, c1, c2 = ND.of_shape(sb), ND.of_shape(sa), ND.of_shape(so)
+    auto = check_conv(device, oracle, dt, c0, c0.size, a, c1, e, c2, d=0)
+    family, kernel = device.last_conv_path(), device.last_kernel()
+    generic = gpu_conv(device, np.zeros(c0.size, dtype=dt), c0, a, c1, e, c2, d=0, path=L.NK_CONV_GENERIC)
+    isz = np.dtype(dt).itemsize
+    eligible = (so[-1] * isz) % 16 == 0 and (sa[-1] * isz) % 16 == 0 and int(np.prod(so)) >= 65536 and so[-1] >= 64
+    if eligible:
+        assert family == L.NK_CONV_TMA and kernel == "nk_conv_wgrad_finish_kernel", (family, kernel)
+    scale = np.abs(generic).max()
+    assert np.abs(auto - generic).max() <= (1e-5 if dt == np.float32 else 1e-12) * scale * 16
 
 
 def test_tiled_family_on_views(device, oracle):
