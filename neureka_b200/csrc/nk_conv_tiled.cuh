@@ -418,11 +418,21 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     p.tilesX = (p.OW + p.xoff + C::TW - 1) / C::TW;
     p.tilesY = (p.OH + C::TH - 1) / C::TH;
     const int64_t tiles = int64_t(p.tilesX) * p.tilesY * p.NP;
-    // channel split: only when the tiles alone cannot fill the machine and each part keeps >= 4 channels
-    const int64_t want_ctas = int64_t(ctx->prop.multiProcessorCount) * 2;
+    {
+        cudaError_t e = cudaFuncSetAttribute(nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel)");
+    }
+    // channel split: only when the tiles alone cannot fill the machine and each part keeps >= 4 channels; the
+    // CTA count stays within one resident wave (a second, nearly empty wave would double the time)
+    int per_sm = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, TMA ? 288 : 256, smem) != cudaSuccess || per_sm < 1) {
+        cudaGetLastError();
+        per_sm = 1;
+    }
+    const int64_t slots = int64_t(ctx->prop.multiProcessorCount) * per_sm;
     int splits = 1;
-    if (tiles < want_ctas && p.NQ >= 8) {
-        splits = int((want_ctas + tiles - 1) / tiles);
+    if (tiles < slots && p.NQ >= 8) {
+        splits = int(slots / tiles);
         if (splits > p.NQ / 4) splits = p.NQ / 4;
         if (splits > 32) splits = 32;
         if (splits < 1) splits = 1;
@@ -447,8 +457,6 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     }
     const int64_t grid = tiles * splits;
     if (grid > 0x7fffffffLL) return -1;
-    cudaError_t e = cudaFuncSetAttribute(nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel)");
     nk_conv_tiled_kernel<T, KH, KW, RH, TMA><<<unsigned(grid), TMA ? 288 : 256, smem, ctx->stream>>>(out, partial, I, K, p, tmap);
     int st = nk_after_launch(ctx, TMA ? "nk_conv_tiled_kernel<tma>" : "nk_conv_tiled_kernel<ldgsts>");
     if (st || splits == 1) return st;
