@@ -172,6 +172,9 @@ const char* nk_last_kernel(nk_ctx* ctx);                 /* name of the last ker
 int nk_launch_count(nk_ctx* ctx, uint64_t* out);         /* kernels launched by this ctx so far */
 int nk_timer_begin(nk_ctx* ctx);                         /* CUDA event on the ctx stream */
 int nk_timer_end(nk_ctx* ctx, float* out_ms);            /* second event + synchronise */
+/* FMA throughput of the device measured with a register-resident loop (TFLOP/s, 2 flops per FMA): the roofline
+ * denominator for the FMA-bound kernels (F32 stencil, F64 convolution, double-evaluated activations). */
+int nk_measure_fma_peak(nk_ctx* ctx, int32_t dtype, double* out_tflops);
 
 /* ---- multi-GPU (no reference counterpart: the reference has no multi-device execution) ----
  * One process per GPU. A rank exports a buffer; peers open it and use it as the drain of nk_conv, so a

@@ -84,6 +84,7 @@ SIGNATURES = {
     "nk_launch_count": (C.c_int, [_vp, C.POINTER(C.c_uint64)]),
     "nk_timer_begin": (C.c_int, [_vp]),
     "nk_timer_end": (C.c_int, [_vp, C.POINTER(C.c_float)]),
+    "nk_measure_fma_peak": (C.c_int, [_vp, _i32, C.POINTER(C.c_double)]),
     "nk_ipc_export": (C.c_int, [_vp, _vp, C.POINTER(C.c_uint8)]),
     "nk_ipc_open": (C.c_int, [_vp, C.POINTER(C.c_uint8), _i32, _i64, C.POINTER(_vp)]),
     "nk_jrand_fill": (C.c_int, [_i32, _i32, _i64, _dbl, _dbl, _vp, _i64]),

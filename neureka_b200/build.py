@@ -38,6 +38,7 @@ SOURCES = [
     ("nk_conv_tiled_inst_f64_tma8.cu", []),
     ("nk_conv_wgrad_inst_f32.cu", []),
     ("nk_conv_wgrad_inst_f64.cu", []),
+    ("nk_probe.cu", []),
     ("nk_sum_static.cu", ["-fmad=false"]),
     ("nk_jrand.cpp", ["-Xcompiler", "-ffp-contract=off"]),
 ]

@@ -368,10 +368,14 @@ int nk_conv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_
     double* od = (double*)drn->ptr; const double* Id = (const double*)bi->ptr; const double* Kd = (const double*)bk->ptr;
     int family = NK_CONV_TILED;
     if (tma_ok) {
-        // 8 output rows per thread halve the shared-memory reads per multiply-add; worth it once the tile is filled
-        // ... i.e. when the 64-row tiles alone give every SM several CTAs; small problems keep the 32-row tiles
+        // 8 output rows per thread halve the shared-memory reads per multiply-add but double the work unit:
+        // compare the two tilings by resident waves x relative tile time (32-row tiles are ~10 % less efficient)
+        const int64_t slots = int64_t(ctx->prop.multiProcessorCount) * 2;
         const int64_t tiles8 = int64_t((p.OW + 127) / 128) * ((p.OH + 63) / 64) * p.NP;
-        const bool tall = p.OH >= 128 && tiles8 >= int64_t(ctx->prop.multiProcessorCount) * 4;
+        const int64_t tiles4 = int64_t((p.OW + 127) / 128) * ((p.OH + 31) / 32) * p.NP;
+        const double cost8 = double((tiles8 + slots - 1) / slots) * 2.0;
+        const double cost4 = double((tiles4 + slots - 1) / slots) * 1.1;
+        const bool tall = p.OH >= 128 && cost8 <= cost4;
         if (tall) st = f32 ? nk_tiled_dispatch_f32_tma8(ctx, int(KH), int(KW), of, If, Kf, p, &img) : nk_tiled_dispatch_f64_tma8(ctx, int(KH), int(KW), od, Id, Kd, p, &img);
         if (st == -1) st = f32 ? nk_tiled_dispatch_f32_tma4(ctx, int(KH), int(KW), of, If, Kf, p, &img) : nk_tiled_dispatch_f64_tma4(ctx, int(KH), int(KW), od, Id, Kd, p, &img);
         if (st != -1) family = NK_CONV_TMA;

@@ -1,0 +1,47 @@
+// Measured arithmetic ceilings of the device the context runs on: a register-resident FMA loop with enough
+// independent chains to saturate the pipe. The benchmark uses the results as roofline denominators for the
+// FP32-FMA-bound stencil and the FP64-bound kernels (F64 convolution, the double-evaluated activations).
+#include "nk_internal.h"
+
+template <class T>
+__global__ void __launch_bounds__(256) nk_fma_peak_kernel(T* __restrict__ sink, int iters, T seed) {
+    T a[16];
+#pragma unroll
+    for (int k = 0; k < 16; k++) a[k] = seed + T(threadIdx.x + k);
+    const T m = T(0.999999), c = T(1e-7);
+    for (int i = 0; i < iters; i++) {
+#pragma unroll
+        for (int k = 0; k < 16; k++) a[k] = fma(a[k], m, c);
+    }
+    T s = 0;
+#pragma unroll
+    for (int k = 0; k < 16; k++) s += a[k];
+    if (s == T(-1)) sink[0] = s;   // never true: keeps the loop alive without a store
+}
+
+extern "C" int nk_measure_fma_peak(nk_ctx* ctx, int32_t dtype, double* out_tflops) {
+    NK_CHECK_CTX(ctx);
+    if (!out_tflops) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_measure_fma_peak: out pointer is null");
+    if (dtype != NK_F32 && dtype != NK_F64) return nk_fail(ctx, NK_ERR_UNSUPPORTED, "nk_measure_fma_peak: F32/F64 only");
+    void* sink = nullptr;
+    int st = nk_scratch(ctx, 64, &sink);
+    if (st) return st;
+    const int grid = ctx->prop.multiProcessorCount * 8, block = 256;
+    const int iters = dtype == NK_F32 ? 8192 : 2048;
+    float best = 1e30f;
+    for (int rep = 0; rep < 4; rep++) {
+        NK_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
+        if (dtype == NK_F32) nk_fma_peak_kernel<float><<<grid, block, 0, ctx->stream>>>((float*)sink, iters, 1.0f);
+        else nk_fma_peak_kernel<double><<<grid, block, 0, ctx->stream>>>((double*)sink, iters, 1.0);
+        st = nk_after_launch(ctx, "nk_fma_peak_kernel");
+        if (st) return st;
+        NK_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
+        NK_CUDA(ctx, cudaEventSynchronize(ctx->ev1));
+        float ms = 0;
+        NK_CUDA(ctx, cudaEventElapsedTime(&ms, ctx->ev0, ctx->ev1));
+        if (rep > 0 && ms < best) best = ms;
+    }
+    const double flops = 2.0 * 16.0 * double(iters) * double(grid) * block;
+    *out_tflops = flops / (double(best) * 1e-3) / 1e12;
+    return NK_OK;
+}
