@@ -371,8 +371,9 @@ int nk_conv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_
         // 8 output rows per thread halve the shared-memory reads per multiply-add but double the work unit:
         // compare the two tilings by resident waves x relative tile time (32-row tiles are ~10 % less efficient)
         const int64_t slots = int64_t(ctx->prop.multiProcessorCount) * 2;
-        const int64_t tiles8 = int64_t((p.OW + 127) / 128) * ((p.OH + 63) / 64) * p.NP;
-        const int64_t tiles4 = int64_t((p.OW + 127) / 128) * ((p.OH + 31) / 32) * p.NP;
+        const int tw = 32 * CW;
+        const int64_t tiles8 = int64_t((p.OW + tw - 1) / tw) * ((p.OH + 63) / 64) * p.NP;
+        const int64_t tiles4 = int64_t((p.OW + tw - 1) / tw) * ((p.OH + 31) / 32) * p.NP;
         const double cost8 = double((tiles8 + slots - 1) / slots) * 2.0;
         const double cost4 = double((tiles4 + slots - 1) / slots) * 1.1;
         const bool tall = p.OH >= 128 && cost8 <= cost4;
