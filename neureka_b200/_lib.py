@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libneureka_cuda.so")
+# NEUREKA_CUDA_LIB points at another build of the same library (e.g. one installed system-wide)
+LIB_PATH = os.environ.get("NEUREKA_CUDA_LIB") or os.path.join(_HERE, "lib", "libneureka_cuda.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(

@@ -19,6 +19,8 @@
 // the channel range is split across CTAs and a second pass adds the partial planes in a fixed order.
 #pragma once
 #include <cuda.h>
+#include <cooperative_groups.h>
+#include <type_traits>
 #include "nk_conv_plan.h"
 
 #define NK_TILED_MAX_OUTER 6
@@ -35,6 +37,7 @@ struct TiledPlan {
     int64_t sIy, sKy, sKx, sOy;
     int64_t bI, bK, bO;
     int tilesX, tilesY, splits;
+    int cluster;   // channel-split CTAs of a tile form one thread-block cluster and add their tiles through shared memory
     int vec;       // LDGSTS: 16-byte global->shared copies are legal for every chunk
     int vec_out;   // 16-byte stores to the drain are legal
     int has_y;     // the second-to-last dim is the tile's row dim (else tiles are one row high)
@@ -86,6 +89,11 @@ __device__ __forceinline__ void nk_fence_barrier_init() { asm volatile("fence.mb
 __device__ __forceinline__ void nk_fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
 // One tile load: coordinates are element indices, innermost first. No multicast, local memory only.
+__device__ __forceinline__ void nk_tma_load(void* smem, const CUtensorMap* map, uint64_t* bar, int nd, const int* c);
+__device__ __forceinline__ void nk_tma_load5(void* smem, const CUtensorMap* map, uint64_t* bar, int nd, int c0, int c1, int c2, int c3, int c4) {
+    const int c[5] = {c0, c1, c2, c3, c4};   // constant indices only below: stays in registers
+    nk_tma_load(smem, map, bar, nd, c);
+}
 __device__ __forceinline__ void nk_tma_load(void* smem, const CUtensorMap* map, uint64_t* bar, int nd, const int* c) {
     unsigned d = (unsigned)__cvta_generic_to_shared(smem), b = (unsigned)__cvta_generic_to_shared(bar);
     unsigned long long m = reinterpret_cast<unsigned long long>(map);
@@ -117,12 +125,12 @@ struct TiledCfg {
     static constexpr int STAGES = (STAGE_BYTES * 4 <= 64 * 1024) ? 4 : 3;
     static constexpr int NS = CW + HALO_W;                    // row-segment values a thread loads
     static constexpr int WPAD = ((KH * KW + CW - 1) / CW) * CW;
-    static constexpr bool WREG = KH * KW * int(sizeof(T)) <= 200;   // weights of one channel live in registers
+    static constexpr bool WREG = KH * KW * int(sizeof(T)) <= 400;   // weights of one channel live in registers
     static constexpr int CPR = SW / CW;                       // LDGSTS chunks per row
     static constexpr int NIT = (SH * CPR + 255) / 256;        // LDGSTS chunks per thread
     static size_t smem_bytes(int NQ) {
-        // [stages | mbarriers + abort word (128 B) | weights | channel table (3 x int64 per channel)]
-        return size_t(STAGES) * STAGE_BYTES + 128 + size_t(NQ) * WPAD * sizeof(T) + 16 + size_t(NQ) * 3 * sizeof(int64_t);
+        // [stages | mbarriers + abort word (128 B) | weights | channel table (32 bytes per channel)]
+        return size_t(STAGES) * STAGE_BYTES + 128 + size_t(NQ) * WPAD * sizeof(T) + 16 + size_t(NQ) * 4 * sizeof(int64_t);
     }
 };
 
@@ -136,16 +144,18 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     unsigned char* stage_base = nk_smem;
     uint64_t* mbar = reinterpret_cast<uint64_t*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES);
     T* wsm = reinterpret_cast<T*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES + 128);
-    // channel table: image offset, kernel offset, packed outer indices (for the tensor-map coordinates)
+    // channel table, 32 bytes per channel: image offset, kernel offset, then the tile's tensor-map coordinates 1..4
+    // (everything but x) ready for the producer thread -- it runs on the same issue port as two compute warps per
+    // CTA, and every instruction it spends per tile is taken from them
     int64_t* ctab = reinterpret_cast<int64_t*>((reinterpret_cast<uintptr_t>(wsm + size_t(p.NQ) * WPAD) + 15) & ~uintptr_t(15));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     // ---- which tile / outer coordinate / channel range ----------------------------------------------------------
     int64_t bid = blockIdx.x;
+    const int split = int(bid % p.splits); bid /= p.splits;   // fastest: the parts of one tile are neighbours (one cluster)
     const int tx = int(bid % p.tilesX); bid /= p.tilesX;
     const int ty = int(bid % p.tilesY); bid /= p.tilesY;
-    const int split = int(bid % p.splits); bid /= p.splits;
     const int64_t pflat = bid;
     int64_t baseI = p.bI, baseK = p.bK, baseO = p.bO;
     int pidx[NK_TILED_MAX_OUTER];
@@ -168,31 +178,61 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     uint64_t* full_bar = mbar;
     uint64_t* empty_bar = mbar + STAGES;
     volatile int* abort_word = reinterpret_cast<volatile int*>(mbar + 2 * STAGES);
-    if (TMA && tid == 0) {
+    const int n_it = c_end - c_begin;
+    int issued = 0;                            // tiles requested so far (producer thread)
+    // Tensor-map coordinates 1..4 of channel c's tile (coordinate 0 is x0 - padX for every channel).
+    auto tma_coords = [&](int c, int* cc) {
+        cc[0] = cc[1] = cc[2] = cc[3] = 0;
+        int n = 0;
+        if (p.has_y) cc[n++] = y0 - p.padY;
+        int rem = c;
+        for (int k = p.n_outer - 1; k >= 0; k--) {
+            const int q = rem % int(p.qext[k]);
+            rem /= int(p.qext[k]);
+            if (n < 4) cc[n] = pidx[k] + q - p.padO[k];
+            n++;
+        }
+    };
+    auto tma_fire = [&](int stage, int c1, int c2, int c3, int c4) {
+        // without a row dim in the map the box is a single row; the other tile rows are never stored from
+        nk_mbar_expect_tx(&full_bar[stage], unsigned((p.has_y ? SH : 1) * SW * sizeof(T)));
+        nk_tma_load5(stage_base + size_t(stage) * C::STAGE_BYTES, &tmap, &full_bar[stage], p.tma_nd, x0 - p.padX, c1, c2, c3, c4);
+        issued++;
+    };
+    if (TMA && tid == 256) {
+        // the producer thread sets the barriers up and requests the first tiles right away, so that they travel
+        // while the other warps stage the weights; everybody else meets the barriers only after the __syncthreads below
         for (int s = 0; s < STAGES; s++) { nk_mbar_init(&full_bar[s], 1); nk_mbar_init(&empty_bar[s], 8); }
         *abort_word = 0;
         nk_fence_barrier_init();
+        nk_fence_proxy_async();
+        for (int it = 0; it < STAGES && it < n_it; it++) {
+            int cc[4];
+            tma_coords(c_begin + it, cc);
+            tma_fire(it, cc[0], cc[1], cc[2], cc[3]);
+        }
     }
 
     // ---- stage the channel table and this CTA's weights ---------------------------------------------------------
     for (int c = c_begin + tid; c < c_end; c += blockDim.x) {
         int rem = c;
-        int64_t oi = 0, ok = 0, packed = 0;
+        int64_t oi = 0, ok = 0;
         for (int k = p.n_outer - 1; k >= 0; k--) {
             int q = rem % int(p.qext[k]);
             rem /= int(p.qext[k]);
             oi += q * p.qI[k]; ok += q * p.qK[k];
-            packed |= int64_t(q) << (16 * k);          // TMA family: at most 3 outer dims, each loop index < 65536
         }
-        ctab[c * 3 + 0] = oi;
-        ctab[c * 3 + 1] = ok;
-        ctab[c * 3 + 2] = packed;
+        ctab[c * 4 + 0] = oi;
+        ctab[c * 4 + 1] = ok;
+        int cc[4];
+        tma_coords(c, cc);
+        *reinterpret_cast<int4*>(&ctab[c * 4 + 2]) = make_int4(cc[0], cc[1], cc[2], cc[3]);
     }
     __syncthreads();
     for (int e = tid; e < (c_end - c_begin) * WPAD; e += blockDim.x) {
         const int c = c_begin + e / WPAD, t = e % WPAD;
         T v = 0;
-        if (t < KH * KW) v = K[baseK + ctab[c * 3 + 1] + (t / KW) * p.sKy + (t % KW) * p.sKx];
+        if (t < KH * KW) v = K[baseK + ctab[c * 4 + 1] + (t / KW) * p.sKy + (t % KW) * p.sKx];
         wsm[size_t(c) * WPAD + t] = v;
     }
 
@@ -215,7 +255,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     }
     auto ldgsts_stage = [&](int stage, int c) {
         T* dst = reinterpret_cast<T*>(stage_base + size_t(stage) * C::STAGE_BYTES);
-        const T* src = I + baseI + ctab[c * 3 + 0];
+        const T* src = I + baseI + ctab[c * 4 + 0];
 #pragma unroll
         for (int it = 0; it < C::NIT; it++) {
             if (l_soff[it] < 0) continue;
@@ -233,19 +273,6 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             }
         }
     };
-    int issued = 0;                             // tiles requested so far (thread 0)
-    auto tma_stage = [&](int stage, int c) {   // executed by thread 0 only
-        int coord[5];
-        coord[0] = x0 - p.padX;
-        int n = 1;
-        if (p.has_y) coord[n++] = y0 - p.padY;
-        const int64_t packed = ctab[c * 3 + 2];
-        for (int k = p.n_outer - 1; k >= 0; k--) coord[n++] = pidx[k] + int((packed >> (16 * k)) & 0xffff) - p.padO[k];
-        // without a row dim in the map the box is a single row; the other tile rows are never stored from
-        nk_mbar_expect_tx(&full_bar[stage], unsigned((p.has_y ? SH : 1) * SW * sizeof(T)));
-        nk_tma_load(stage_base + size_t(stage) * C::STAGE_BYTES, &tmap, &full_bar[stage], p.tma_nd, coord);
-        issued++;
-    };
 
     T acc[RH][CW];
 #pragma unroll
@@ -254,7 +281,6 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         for (int x = 0; x < CW; x++) acc[i][x] = T(0);
 
     __syncthreads();   // weights + table + barrier init visible
-    const int n_it = c_end - c_begin;
 
     // One channel's worth of multiply-adds for this thread (tile rows warp*RH .. +RH, columns lane*CW .. +CW).
     auto consume = [&](int stage, int c) {
@@ -291,6 +317,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         }
     };
 
+    bool aborted = false;
     if (TMA) {
         // Every wait below is bounded; whoever runs out raises the CTA's abort word (and the host-visible status),
         // everybody else notices it while polling, and the CTA leaves without storing anything.
@@ -309,12 +336,12 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         };
         if (warp == 8) {
             if (lane == 0) {
-                nk_fence_proxy_async();
                 bool ok = true;
-                for (int it = 0; it < n_it && ok; it++) {
+                for (int it = STAGES; it < n_it && ok; it++) {   // the first STAGES tiles were requested in the prologue
                     const int stage = it % STAGES;
-                    if (it >= STAGES) ok = wait_or_abort(&empty_bar[stage], unsigned(it / STAGES - 1) & 1u);
-                    if (ok) tma_stage(stage, c_begin + it);
+                    const int4 cc = *reinterpret_cast<const int4*>(&ctab[(c_begin + it) * 4 + 2]);
+                    ok = wait_or_abort(&empty_bar[stage], unsigned(it / STAGES - 1) & 1u);
+                    if (ok) tma_fire(stage, cc.x, cc.y, cc.z, cc.w);
                 }
                 if (!ok || *abort_word) {
                     // requested copies may still be landing in this CTA's shared memory: wait for the last ones (bounded)
@@ -335,8 +362,11 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             }
         }
         __syncthreads();
-        if (*abort_word) return;
-        if (warp == 8) return;   // the producer warp owns no outputs
+        if (*abort_word) {
+            if (!p.cluster) return;
+            aborted = true;   // the cluster's barriers below still have to be met; the host reports the time-out
+        }
+        if (warp == 8 && !p.cluster) return;   // the producer warp owns no outputs
     } else {
 #pragma unroll
         for (int s = 0; s < STAGES - 1; s++) {
@@ -355,6 +385,49 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     }
 
     // ---- epilogue -----------------------------------------------------------------------------------------------
+    if (p.cluster) {
+        // The p.splits CTAs of this tile are one cluster (rank == split). Each leaves its partial tile in its own
+        // shared memory; then CTA r adds slice r of the tile over all ranks, in rank order (the same order as the
+        // two-pass path, so both give the same bits), reading the peers' tiles through distributed shared memory.
+        namespace cg = cooperative_groups;
+        cg::cluster_group cl = cg::this_cluster();
+        using V = typename std::conditional<sizeof(T) == 4, float4, double2>::type;
+        T* red = reinterpret_cast<T*>(stage_base);   // every tile load has been consumed: the ring is free
+        __syncthreads();
+        if (warp < 8 && !aborted) {
+#pragma unroll
+            for (int i = 0; i < RH; i++)
+                *reinterpret_cast<V*>(red + ((warp * RH + i) * TW + lane * CW)) = *reinterpret_cast<V*>(&acc[i][0]);
+        }
+        cl.sync();
+        constexpr int VPR = TW / CW, NV = TH * VPR;
+        const int per = (NV + p.splits - 1) / p.splits;
+        const int v_end = ((split + 1) * per < NV) ? (split + 1) * per : NV;
+        for (int v = split * per + tid; v < v_end && !aborted; v += blockDim.x) {
+            T sum[CW];
+#pragma unroll
+            for (int x = 0; x < CW; x++) sum[x] = T(0);
+            for (int s = 0; s < p.splits; s++) {
+                const T* peer = cl.map_shared_rank(red, s);
+                T part[CW];
+                *reinterpret_cast<V*>(part) = *reinterpret_cast<const V*>(peer + size_t(v) * CW);
+#pragma unroll
+                for (int x = 0; x < CW; x++) sum[x] += part[x];
+            }
+            const int oy = y0 + v / VPR, ox = x0 + (v % VPR) * CW;
+            if (oy >= p.OH || ox >= p.OW || ox + CW <= 0) continue;
+            T* dst = out + baseO + int64_t(oy) * p.sOy + ox;
+            if (p.vec_out && ox >= 0 && ox + CW <= p.OW) {
+                *reinterpret_cast<V*>(dst) = *reinterpret_cast<V*>(sum);
+            } else {
+#pragma unroll
+                for (int x = 0; x < CW; x++)
+                    if (ox + x >= 0 && ox + x < p.OW) dst[x] = sum[x];
+            }
+        }
+        cl.sync();   // nobody leaves while a peer may still be reading its tile
+        return;
+    }
     const int ox = x0 + lane * CW;
 #pragma unroll
     for (int i = 0; i < RH; i++) {
@@ -438,6 +511,7 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
         if (splits < 1) splits = 1;
     }
     p.splits = splits;
+    p.cluster = 0;
     CUtensorMap tmap;
     memset(&tmap, 0, sizeof(tmap));
     if (TMA) {
@@ -447,6 +521,34 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
         if (st) return st;
         p.status = ctx->tma_status_dev;
     }
+    const int64_t grid = tiles * splits;
+    if (grid > 0x7fffffffLL) return -1;
+    const unsigned threads = TMA ? 288 : 256;
+    if (splits > 1 && splits <= 8) {
+        // one launch: the parts of a tile as a thread-block cluster that adds itself up through shared memory
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(unsigned(grid));
+        cfg.blockDim = dim3(threads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = unsigned(splits);
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int active = 0;
+        if (cudaOccupancyMaxActiveClusters(&active, nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, &cfg) == cudaSuccess && active >= 1) {
+            p.cluster = 1;
+            T* none = nullptr;
+            cudaError_t e = cudaLaunchKernelEx(&cfg, nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, out, none, I, K, p, tmap);
+            if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaLaunchKernelEx(nk_conv_tiled_kernel, cluster)");
+            return nk_after_launch(ctx, TMA ? "nk_conv_tiled_kernel<tma,cluster>" : "nk_conv_tiled_kernel<ldgsts,cluster>");
+        }
+        cudaGetLastError();   // clusters of this size do not fit: two passes instead
+    }
     T* partial = nullptr;
     if (splits > 1) {
         void* scratch = nullptr;
@@ -455,9 +557,7 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
         if (st) return st;
         partial = reinterpret_cast<T*>(scratch);
     }
-    const int64_t grid = tiles * splits;
-    if (grid > 0x7fffffffLL) return -1;
-    nk_conv_tiled_kernel<T, KH, KW, RH, TMA><<<unsigned(grid), TMA ? 288 : 256, smem, ctx->stream>>>(out, partial, I, K, p, tmap);
+    nk_conv_tiled_kernel<T, KH, KW, RH, TMA><<<unsigned(grid), threads, smem, ctx->stream>>>(out, partial, I, K, p, tmap);
     int st = nk_after_launch(ctx, TMA ? "nk_conv_tiled_kernel<tma>" : "nk_conv_tiled_kernel<ldgsts>");
     if (st || splits == 1) return st;
     const int64_t plane = p.NP * int64_t(p.OH) * p.OW;

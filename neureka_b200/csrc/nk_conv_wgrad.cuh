@@ -189,15 +189,21 @@ __global__ void __launch_bounds__(256) nk_conv_wgrad_kernel(T* __restrict__ part
     }
 }
 
+// One warp per kernel tap: lane l adds chunks l, l+32, ... in rising order, then the 32 lane sums are folded by a
+// fixed shuffle tree, so the result does not depend on scheduling (run-to-run deterministic).
 template <class T>
-__global__ void nk_conv_wgrad_finish_kernel(T* __restrict__ out, const T* __restrict__ partial, WgradPlan p, int KH, int KW) {
-    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+__global__ void __launch_bounds__(128) nk_conv_wgrad_finish_kernel(T* __restrict__ out, const T* __restrict__ partial, WgradPlan p, int KH, int KW) {
+    const int64_t i = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
     const int win = KH * KW;
-    if (i >= p.NP * win) return;
+    if (i >= p.NP * win) return;   // warp-uniform
     const int64_t pflat = i / win;
     const int t = int(i % win);
     T total = 0;
-    for (int c = 0; c < p.chunks; c++) total += partial[(pflat * p.chunks + c) * int64_t(win) + t];
+    for (int c = lane; c < p.chunks; c += 32) total += partial[(pflat * p.chunks + c) * int64_t(win) + t];
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) total += __shfl_down_sync(0xffffffffu, total, s);
+    if (lane) return;
     int64_t o = p.bD + (t / KW) * p.sDy + (t % KW) * p.sDx;
     int64_t rem = pflat;
     for (int k = p.n_outer - 1; k >= 0; k--) { o += (rem % p.oext[k]) * p.os[k]; rem /= p.oext[k]; }
@@ -212,7 +218,14 @@ int nk_launch_wgrad(nk_ctx* ctx, T* out, WgradPlan& p, const TmaImage& imgA, con
     p.tilesX = (p.EW + C::TW - 1) / C::TW;
     p.tilesY = p.has_y ? (p.EH + C::TH - 1) / C::TH : 1;
     p.units = p.NQ * int64_t(p.tilesY) * p.tilesX;
-    int64_t chunks = (int64_t(ctx->prop.multiProcessorCount) * 4 + p.NP - 1) / p.NP;
+    cudaError_t e = cudaFuncSetAttribute(nk_conv_wgrad_kernel<T, KH, KW>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_wgrad_kernel)");
+    // as many CTAs as are resident at once (KH*KW accumulators per thread decide that), so that the grid is one wave
+    int per_sm = 1;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nk_conv_wgrad_kernel<T, KH, KW>, 256, smem);
+    if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaOccupancyMaxActiveBlocksPerMultiprocessor(nk_conv_wgrad_kernel)");
+    if (per_sm < 1) per_sm = 1;
+    int64_t chunks = int64_t(ctx->prop.multiProcessorCount) * per_sm / p.NP;
     if (chunks > p.units) chunks = p.units;
     if (chunks > 4096) chunks = 4096;
     if (chunks < 1) chunks = 1;
@@ -228,12 +241,10 @@ int nk_launch_wgrad(nk_ctx* ctx, T* out, WgradPlan& p, const TmaImage& imgA, con
     st = nk_scratch(ctx, size_t(p.NP) * size_t(chunks) * KH * KW * sizeof(T), &scratch);
     if (st) return st;
     p.status = ctx->tma_status_dev;
-    cudaError_t e = cudaFuncSetAttribute(nk_conv_wgrad_kernel<T, KH, KW>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_wgrad_kernel)");
     nk_conv_wgrad_kernel<T, KH, KW><<<unsigned(p.NP * chunks), 256, smem, ctx->stream>>>(reinterpret_cast<T*>(scratch), p, mapA, mapE);
     st = nk_after_launch(ctx, "nk_conv_wgrad_kernel");
     if (st) return st;
     const int64_t n = p.NP * KH * KW;
-    nk_conv_wgrad_finish_kernel<T><<<unsigned((n + 127) / 128), 128, 0, ctx->stream>>>(out, reinterpret_cast<const T*>(scratch), p, KH, KW);
+    nk_conv_wgrad_finish_kernel<T><<<unsigned((n + 3) / 4), 128, 0, ctx->stream>>>(out, reinterpret_cast<const T*>(scratch), p, KH, KW);
     return nk_after_launch(ctx, "nk_conv_wgrad_finish_kernel");
 }

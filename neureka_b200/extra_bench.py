@@ -121,6 +121,39 @@ def run_extra(dev, hbm_peak_gbs: float) -> dict:
     out["cfg3_broadcast_tanh_2048x1024x1024"] = r
     for bb in (a, b, t1, t2, y, ga, gb): bb.free()
 
+    # ---- cfg3 at its full size: 2^33 outputs, op by op in the reference's order ------------------------------------------
+    # 4096*2048*1024 elements overflow Java's int sizes, so the reference itself cannot hold this tensor; here every
+    # intermediate is one 32 GiB buffer (64-bit offsets throughout). Needs ~100 GiB free.
+    try:
+        if dev.props.total_mem_bytes >= 150 * (1 << 30):
+            n, m, kk = 4096, 2048, 1024
+            N = n * m * kk
+            a = _Buf(dev, np.float32, n * kk, _rand(np.float32, n * kk, 0, 3, -2.0, 2.0))
+            b = _Buf(dev, np.float32, m * kk, _rand(np.float32, m * kk, 0, 4, -2.0, 2.0))
+            t2, y, g = (_Buf(dev, np.float32, N) for _ in range(3))
+            ca, pa = _cfg([n, 1, kk]); cb, pb = _cfg([1, m, kk]); co, po = _cfg([n, m, kk])
+            ga, gb = _Buf(dev, np.float32, n * kk), _Buf(dev, np.float32, m * kk)
+            steps = [
+                ("mul_broadcast", lambda i: L.lib.nk_broadcast(ctx, L.NK_OP_MUL, L.NK_F32, 3, t2.buf, po, a.buf, pa, b.buf, pb, -1), 4.0 * (N + n * kk + m * kk)),
+                ("add_broadcast_in_place", lambda i: L.lib.nk_broadcast(ctx, L.NK_OP_ADD, L.NK_F32, 3, y.buf, po, t2.buf, po, b.buf, pb, -1), 4.0 * (2 * N + m * kk)),
+                ("tanh", lambda i: L.lib.nk_unary(ctx, L.FUN["tanh"], L.NK_F32, 3, g.buf, po, y.buf, po, -1), 8.0 * N),
+                ("tanh_derivative", lambda i: L.lib.nk_unary(ctx, L.FUN["tanh"], L.NK_F32, 3, g.buf, po, y.buf, po, 0), 8.0 * N),
+                ("grad_a_reduce", lambda i: L.lib.nk_broadcast(ctx, L.NK_OP_MUL_BOTH, L.NK_F32, 3, ga.buf, pa, b.buf, pb, g.buf, po, 0), 4.0 * (N + n * kk + m * kk)),
+                ("grad_b_reduce_mul", lambda i: L.lib.nk_broadcast(ctx, L.NK_OP_MUL_BOTH, L.NK_F32, 3, gb.buf, pb, a.buf, pa, g.buf, po, 0), 4.0 * (N + n * kk + m * kk)),
+            ]
+            r = {}
+            total_ms = 0.0
+            for name, fn, nbytes in steps:
+                ms = _time(dev, lambda i, fn=fn: L.check(fn(i), ctx), 1, 2)
+                total_ms += ms
+                r[name] = {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / hbm_peak_gbs, "kernel": dev.last_kernel()}
+            r["forward_plus_backward_ms"] = total_ms
+            r["note"] = "2^33 F32 outputs per intermediate (32 GiB each); beyond the reference's int-sized tensors"
+            out["cfg3_full_size_4096x2048x1024"] = r
+            for bb in (a, b, t2, y, g, ga, gb): bb.free()
+    except Exception as e:   # a side measurement must not take the others down
+        out["cfg3_full_size_4096x2048x1024"] = {"error": repr(e)}
+
     # ---- cfg4 -----------------------------------------------------------------------------------------------------
     v = _Buf(dev, np.float64, 128 ** 3, _rand(np.float64, 128 ** 3, 1, 11, 0.0, 1.0))
     k = _Buf(dev, np.float64, 343, _rand(np.float64, 343, 1, 12, 0.0, 0.1))
@@ -141,3 +174,16 @@ def run_extra(dev, hbm_peak_gbs: float) -> dict:
     out["cfg4_conv3d_f64_128_k7"] = r
     for bb in (v, k, yb, gv, gk): bb.free()
     return out
+
+
+if __name__ == "__main__":
+    # python -m neureka_b200.extra_bench : the side measurements alone, as JSON (also the command ncu is pointed at)
+    import json
+    import os
+    from .device import CudaDevice
+    peak = 6558.7
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peak = float(json.load(f)["hbm_gbs"])
+    print(json.dumps(run_extra(CudaDevice.get(0), peak), indent=1))

@@ -124,3 +124,67 @@ def test_config5_full_size_on_one_gpu(device, oracle):
     L.lib.nk_free(device.ctx, buf)
     for b in (A, K, K2, KD):
         b.free()
+
+
+def test_config3_full_size_beyond_java_int(device, oracle):
+    """BASELINE config 3 at its real size: y = tanh(a*b + b) with a [4096,1,1024], b [1,2048,1024] -> 2^33 outputs
+    (32 GiB per tensor, more elements than a Java int can count, so the reference cannot even allocate it). The three
+    kernels run op by op like the reference would; sampled windows of the result are compared with the oracle's
+    scalar functions (<= 1 ulp), and the reduced gradients of sum(y) with float64 sums over the sampled columns."""
+    import ctypes as C
+    if device.props.total_mem_bytes < 150 * (1 << 30):
+        pytest.skip("needs ~100 GiB of device memory")
+    n, m, k = 4096, 2048, 1024
+    N = n * m * k
+    a_h = _rand(np.float32, n * k, 0, 3, -2.0, 2.0)
+    b_h = _rand(np.float32, m * k, 0, 4, -2.0, 2.0)
+    A, B = DevArray(device, a_h), DevArray(device, b_h)
+    bufs = []
+    for _ in range(2):
+        p = C.c_void_p()
+        L.check(L.lib.nk_alloc(device.ctx, L.NK_F32, N, C.byref(p)), device.ctx)
+        bufs.append(p)
+    t, y = bufs
+    ka, pa = cfgp(ND.of_shape([n, 1, k])); kb, pb = cfgp(ND.of_shape([1, m, k])); ko, po = cfgp(ND.of_shape([n, m, k]))
+    ctx = device.ctx
+    L.check(L.lib.nk_broadcast(ctx, L.NK_OP_MUL, L.NK_F32, 3, t, po, A.buf, pa, B.buf, pb, -1), ctx)
+    L.check(L.lib.nk_broadcast(ctx, L.NK_OP_ADD, L.NK_F32, 3, y, po, t, po, B.buf, pb, -1), ctx)      # y = a*b + b
+    L.check(L.lib.nk_unary(ctx, L.FUN["tanh"], L.NK_F32, 3, t, po, y, po, -1), ctx)                    # t = tanh(y)
+    rng = np.random.default_rng(33)
+    a3, b3 = a_h.reshape(n, 1, k), b_h.reshape(1, m, k)
+    win = 4096
+    starts = [0, N - win, (1 << 32) - 100, (1 << 31) + 12345] + [int(s) for s in rng.integers(0, N - win, size=6)]
+    for s0 in starts:
+        got = np.empty(win, dtype=np.float32)
+        L.check(L.lib.nk_read(ctx, t, got.ctypes.data_as(C.c_void_p), s0, win), ctx)
+        idx = np.arange(s0, s0 + win, dtype=np.int64)
+        i, j, kk = idx // (m * k), (idx // k) % m, idx % k
+        u = (a_h[i * k + kk] * b_h[j * k + kk]).astype(np.float32) + b_h[j * k + kk]
+        want = np.zeros(win, dtype=np.float32)
+        cw = ND.of_shape([win]).as_inline_array()
+        oracle.unary("tanh", want, cw, np.ascontiguousarray(u, dtype=np.float32), cw)
+        d = np.abs(got.view(np.int32).astype(np.int64) - want.view(np.int32).astype(np.int64))
+        assert d.max() <= 1, (s0, d.max())
+    # g = tanh'(y) in place of y's consumer buffer, then the reduced gradients of sum(tanh(...))
+    L.check(L.lib.nk_unary(ctx, L.FUN["tanh"], L.NK_F32, 3, t, po, y, po, 0), ctx)
+    GA, GB = DevArray(device, np.zeros(n * k, dtype=np.float32)), DevArray(device, np.zeros(m * k, dtype=np.float32))
+    L.check(L.lib.nk_broadcast(ctx, L.NK_OP_MUL_BOTH, L.NK_F32, 3, GA.buf, pa, B.buf, pb, t, po, 0), ctx)   # da = sum_j g*b
+    L.check(L.lib.nk_broadcast(ctx, L.NK_OP_MUL_BOTH, L.NK_F32, 3, GB.buf, pb, A.buf, pa, t, po, 0), ctx)   # sum_i g*a
+    ga, gb = GA.read().reshape(n, k), GB.read().reshape(m, k)
+    # reference values for a few (i, :) rows of da and (j, :) rows of db: need g over a whole line of the big tensor
+    for i in (0, 1777, n - 1):
+        row = np.empty(m * k, dtype=np.float32)
+        L.check(L.lib.nk_read(ctx, t, row.ctypes.data_as(C.c_void_p), i * m * k, m * k), ctx)
+        want = (row.reshape(m, k).astype(np.float64) * b_h.reshape(m, k)).sum(axis=0)
+        np.testing.assert_allclose(ga[i], want, rtol=2e-5, atol=2e-4)
+    for j in (0, 999, m - 1):
+        col = np.empty((n, k), dtype=np.float32)
+        # db[j, :] = sum_i g[i, j, :] * a[i, :]; read g[:, j, :] row by row (4096 reads of 4 KB)
+        for i in range(n):
+            L.check(L.lib.nk_read(ctx, t, col[i].ctypes.data_as(C.c_void_p), (i * m + j) * k, k), ctx)
+        want = (col.astype(np.float64) * a_h.reshape(n, k)).sum(axis=0)
+        np.testing.assert_allclose(gb[j], want, rtol=2e-5, atol=2e-4)
+    for p in bufs:
+        L.lib.nk_free(ctx, p)
+    for x in (A, B, GA, GB):
+        x.free()

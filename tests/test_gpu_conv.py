@@ -189,6 +189,30 @@ def test_stencil_shapes_all_kernel_families(device, oracle, dt, case):
 
 @pytest.mark.parametrize("dt", [np.float32, np.float64])
 @pytest.mark.parametrize("case", [
+    ([32, 64, 256], [32, 3, 3], 8), ([16, 70, 132], [16, 5, 5], 4), ([24, 50, 260], [24, 3, 3], 6),
+    ([2, 16, 40, 128], [1, 16, 3, 3], 4), ([64, 40, 256], [64, 3, 3], 16),
+])
+def test_channel_split_adds_up_inside_a_cluster(device, oracle, dt, case):
+    """Few tiles, many channels: the channel range is split over CTAs. Up to 8 parts form one thread-block cluster
+    that adds its partial tiles through distributed shared memory (one launch); more parts take the two-pass path.
+    Both must agree with the oracle, and with each other bit for bit (same summation order)."""
+    rng = np.random.default_rng(23)
+    sa, sb, parts = case
+    so = [abs(x - y) + 1 for x, y in zip(sa, sb)]
+    a = rng.standard_normal(int(np.prod(sa))).astype(dt)
+    b = rng.standard_normal(int(np.prod(sb))).astype(dt)
+    c0, c1, c2 = ND.of_shape(so), ND.of_shape(sa), ND.of_shape(sb)
+    for path in (L.NK_CONV_TMA, L.NK_CONV_TILED):
+        check_conv(device, oracle, dt, c0, c0.size, a, c1, b, c2, d=-1, path=path)
+        kernel = device.last_kernel()
+        if parts <= 8:
+            assert kernel.endswith("cluster>"), kernel
+        else:
+            assert kernel == "nk_conv_tiled_finish_kernel", kernel
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("case", [
     ([96, 200], [5, 5]), ([3, 70, 150], [1, 3, 3]), ([6, 40, 300], [6, 3, 3]), ([2, 5, 64, 130], [1, 5, 5, 5]),
     ([20, 33, 140], [3, 7, 7]), ([1, 260], [1, 9]), ([40, 256], [40, 3]), ([2, 3, 34, 40, 70], [1, 3, 3, 3, 3]), ([16, 24, 72], [7, 7, 7]),
 ])
