@@ -332,6 +332,7 @@ int nk_conv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_
     }
     p.vec = vec ? 1 : 0;
     p.vec_out = vec_out ? 1 : 0;
+    p.remote_out = drn->ipc ? 1 : 0;
 
     // ---- can a tensor map describe the image view? (<= 5 dims, base and strides 16-byte aligned, positive) ----------
     TmaImage img;
@@ -376,7 +377,9 @@ int nk_conv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_
         const int64_t tiles4 = int64_t((p.OW + tw - 1) / tw) * ((p.OH + 31) / 32) * p.NP;
         const double cost8 = double((tiles8 + slots - 1) / slots) * 2.0;
         const double cost4 = double((tiles4 + slots - 1) / slots) * 1.1;
-        const bool tall = p.OH >= 128 && cost8 <= cost4;
+        // a drain on another GPU: results leave over NVLink as tiles finish, and the owner's link is the bottleneck of
+        // an assemble -- short-lived tiles start that stream early and keep it steady
+        const bool tall = p.OH >= 128 && cost8 <= cost4 && !p.remote_out;
         if (tall) st = f32 ? nk_tiled_dispatch_f32_tma8(ctx, int(KH), int(KW), of, If, Kf, p, &img) : nk_tiled_dispatch_f64_tma8(ctx, int(KH), int(KW), od, Id, Kd, p, &img);
         if (st == -1) st = f32 ? nk_tiled_dispatch_f32_tma4(ctx, int(KH), int(KW), of, If, Kf, p, &img) : nk_tiled_dispatch_f64_tma4(ctx, int(KH), int(KW), od, Id, Kd, p, &img);
         if (st != -1) family = NK_CONV_TMA;

@@ -37,6 +37,9 @@ struct TiledPlan {
     int64_t sIy, sKy, sKx, sOy;
     int64_t bI, bK, bO;
     int tilesX, tilesY, splits;
+    int remote_out;   // the drain lives on another GPU (stores cross NVLink)
+    int persist;      // TMA family: the grid is one resident wave and every CTA walks tiles blockIdx.x, +gridDim.x, ...
+    int64_t tiles_total;
     int cluster;   // channel-split CTAs of a tile form one thread-block cluster and add their tiles through shared memory
     int vec;       // LDGSTS: 16-byte global->shared copies are legal for every chunk
     int vec_out;   // 16-byte stores to the drain are legal
@@ -152,23 +155,30 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     // ---- which tile / outer coordinate / channel range ----------------------------------------------------------
-    int64_t bid = blockIdx.x;
-    const int split = int(bid % p.splits); bid /= p.splits;   // fastest: the parts of one tile are neighbours (one cluster)
-    const int tx = int(bid % p.tilesX); bid /= p.tilesX;
-    const int ty = int(bid % p.tilesY); bid /= p.tilesY;
-    const int64_t pflat = bid;
-    int64_t baseI = p.bI, baseK = p.bK, baseO = p.bO;
+    // One tile per CTA (the parts of a channel split are neighbours: one cluster), or -- persistent -- a walk over
+    // tiles blockIdx.x, blockIdx.x + gridDim.x, ... with the load pipeline running on across tile boundaries.
+    const int split = p.persist ? 0 : int(blockIdx.x % unsigned(p.splits));
+    const int64_t tile_first = p.persist ? int64_t(blockIdx.x) : int64_t(blockIdx.x / unsigned(p.splits));
+    const int64_t tile_step = gridDim.x;
+    int64_t baseI, baseK, baseO;
     int pidx[NK_TILED_MAX_OUTER];
-    {
-        int64_t rem = pflat;
+    int x0, y0;
+    auto decode_tile = [&](int64_t tile) {
+        const int tx = int(tile % p.tilesX); tile /= p.tilesX;
+        const int ty = int(tile % p.tilesY); tile /= p.tilesY;
+        baseI = p.bI; baseK = p.bK; baseO = p.bO;
+        int64_t rem = tile;
         for (int k = p.n_outer - 1; k >= 0; k--) {
             int64_t idx = rem % p.oext[k];
             rem /= p.oext[k];
             baseI += idx * p.pI[k]; baseK += idx * p.pK[k]; baseO += idx * p.os[k];
             pidx[k] = p.pI[k] != 0 ? int(idx) : 0;   // the image index follows the output index only where pI != 0
         }
-    }
-    const int x0 = tx * TW - p.xoff, y0 = ty * TH;
+        x0 = tx * TW - p.xoff;
+        y0 = ty * TH;
+    };
+    decode_tile(tile_first);
+    const int64_t pflat = tile_first / (int64_t(p.tilesX) * p.tilesY);   // used by the two-pass split path (one tile per CTA)
     const int cper = (p.NQ + p.splits - 1) / p.splits;
     const int c_begin = split * cper;
     const int c_end = (c_begin + cper < p.NQ) ? c_begin + cper : p.NQ;
@@ -180,18 +190,29 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     volatile int* abort_word = reinterpret_cast<volatile int*>(mbar + 2 * STAGES);
     const int n_it = c_end - c_begin;
     int issued = 0;                            // tiles requested so far (producer thread)
-    // Tensor-map coordinates 1..4 of channel c's tile (coordinate 0 is x0 - padX for every channel).
-    auto tma_coords = [&](int c, int* cc) {
+    // Tensor-map coordinates 1..4 of a tile load (coordinate 0 is x0 - padX): a part that depends on the channel only
+    // (kept in the channel table) plus a part that depends on the output tile only.
+    auto chan_coords = [&](int c, int* cc) {
         cc[0] = cc[1] = cc[2] = cc[3] = 0;
         int n = 0;
-        if (p.has_y) cc[n++] = y0 - p.padY;
+        if (p.has_y) cc[n++] = -p.padY;
         int rem = c;
         for (int k = p.n_outer - 1; k >= 0; k--) {
             const int q = rem % int(p.qext[k]);
             rem /= int(p.qext[k]);
-            if (n < 4) cc[n] = pidx[k] + q - p.padO[k];
+            if (n < 4) cc[n] = q - p.padO[k];
             n++;
         }
+    };
+    auto tile_coords = [&]() -> int4 {   // of the tile decode_tile() was last called for, by this thread
+        int b[4] = {0, 0, 0, 0};
+        int n = 0;
+        if (p.has_y) b[n++] = y0;
+        for (int k = p.n_outer - 1; k >= 0; k--) {
+            if (n < 4) b[n] = pidx[k];
+            n++;
+        }
+        return make_int4(b[0], b[1], b[2], b[3]);
     };
     auto tma_fire = [&](int stage, int c1, int c2, int c3, int c4) {
         // without a row dim in the map the box is a single row; the other tile rows are never stored from
@@ -206,10 +227,11 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         *abort_word = 0;
         nk_fence_barrier_init();
         nk_fence_proxy_async();
+        const int4 tb = tile_coords();
         for (int it = 0; it < STAGES && it < n_it; it++) {
             int cc[4];
-            tma_coords(c_begin + it, cc);
-            tma_fire(it, cc[0], cc[1], cc[2], cc[3]);
+            chan_coords(c_begin + it, cc);
+            tma_fire(it, cc[0] + tb.x, cc[1] + tb.y, cc[2] + tb.z, cc[3] + tb.w);
         }
     }
 
@@ -225,7 +247,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         ctab[c * 4 + 0] = oi;
         ctab[c * 4 + 1] = ok;
         int cc[4];
-        tma_coords(c, cc);
+        chan_coords(c, cc);
         *reinterpret_cast<int4*>(&ctab[c * 4 + 2]) = make_int4(cc[0], cc[1], cc[2], cc[3]);
     }
     __syncthreads();
@@ -317,10 +339,38 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         }
     };
 
+    // Stores this thread's RH x CW results of the tile decode_tile() was last called for: into the drain, or -- two-pass
+    // channel split -- into this part's plane of the scratch buffer.
+    auto store_tile = [&]() {
+        const int ox = x0 + lane * CW;
+#pragma unroll
+        for (int i = 0; i < RH; i++) {
+            const int oy = y0 + warp * RH + i;
+            if (oy >= p.OH || ox >= p.OW || ox + CW <= 0) continue;
+            T* dst;
+            bool vec_ok;
+            if (p.splits == 1) {
+                dst = out + baseO + int64_t(oy) * p.sOy + ox;
+                vec_ok = p.vec_out != 0;
+            } else {
+                dst = partial + ((int64_t(split) * p.NP + pflat) * p.OH + oy) * int64_t(p.OW) + ox;
+                vec_ok = (p.OW % CW) == 0;
+            }
+            if (vec_ok && ox >= 0 && ox + CW <= p.OW) {
+                if (sizeof(T) == 4) *reinterpret_cast<float4*>(dst) = *reinterpret_cast<float4*>(&acc[i][0]);
+                else *reinterpret_cast<double2*>(dst) = *reinterpret_cast<double2*>(&acc[i][0]);
+            } else {
+#pragma unroll
+                for (int x = 0; x < CW; x++)
+                    if (ox + x >= 0 && ox + x < p.OW) dst[x] = acc[i][x];
+            }
+        }
+    };
+
     bool aborted = false;
     if (TMA) {
         // Every wait below is bounded; whoever runs out raises the CTA's abort word (and the host-visible status),
-        // everybody else notices it while polling, and the CTA leaves without storing anything.
+        // everybody else notices it while polling, and the CTA leaves without storing anything more.
         auto wait_or_abort = [&](uint64_t* bar, unsigned parity) -> bool {
             unsigned spins = 0;
             while (!nk_mbar_try_wait(bar, parity)) {
@@ -336,12 +386,24 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         };
         if (warp == 8) {
             if (lane == 0) {
+                // `issued` counts tile loads over the CTA's whole life: load g uses stage g % STAGES in round g / STAGES
                 bool ok = true;
-                for (int it = STAGES; it < n_it && ok; it++) {   // the first STAGES tiles were requested in the prologue
-                    const int stage = it % STAGES;
-                    const int4 cc = *reinterpret_cast<const int4*>(&ctab[(c_begin + it) * 4 + 2]);
-                    ok = wait_or_abort(&empty_bar[stage], unsigned(it / STAGES - 1) & 1u);
-                    if (ok) tma_fire(stage, cc.x, cc.y, cc.z, cc.w);
+                int64_t tile = tile_first;
+                int c = c_begin + issued;   // the first loads of the first tile were requested in the prologue
+                int4 tb = tile_coords();
+                while (ok) {
+                    if (c >= c_end) {
+                        tile += tile_step;
+                        if (!p.persist || tile >= p.tiles_total) break;
+                        decode_tile(tile);
+                        tb = tile_coords();
+                        c = c_begin;
+                    }
+                    const int stage = issued % STAGES;
+                    const int4 cc = *reinterpret_cast<const int4*>(&ctab[c * 4 + 2]);
+                    if (issued >= STAGES) ok = wait_or_abort(&empty_bar[stage], unsigned(issued / STAGES - 1) & 1u);
+                    if (ok) tma_fire(stage, cc.x + tb.x, cc.y + tb.y, cc.z + tb.z, cc.w + tb.w);
+                    c++;
                 }
                 if (!ok || *abort_word) {
                     // requested copies may still be landing in this CTA's shared memory: wait for the last ones (bounded)
@@ -353,15 +415,30 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                 }
             }
         } else {
-            for (int it = 0; it < n_it; it++) {
-                const int stage = it % STAGES;
-                if (!wait_or_abort(&full_bar[stage], unsigned(it / STAGES) & 1u)) break;
-                consume(stage, c_begin + it);
-                __syncwarp();
-                if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
+            int g = 0;   // loads consumed so far, same numbering as the producer's
+            bool ok = true;
+            int64_t tile = tile_first;
+            while (true) {
+                for (int c = c_begin; c < c_end; c++, g++) {
+                    const int stage = g % STAGES;
+                    if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; break; }
+                    consume(stage, c);
+                    __syncwarp();
+                    if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
+                }
+                if (!ok || !p.persist) break;   // one tile per CTA: its epilogue follows below
+                store_tile();
+#pragma unroll
+                for (int i = 0; i < RH; i++)
+#pragma unroll
+                    for (int x = 0; x < CW; x++) acc[i][x] = T(0);
+                tile += tile_step;
+                if (tile >= p.tiles_total) break;
+                decode_tile(tile);
             }
         }
         __syncthreads();
+        if (p.persist) return;   // every tile was stored on the way
         if (*abort_word) {
             if (!p.cluster) return;
             aborted = true;   // the cluster's barriers below still have to be met; the host reports the time-out
@@ -384,7 +461,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         nk_cp_async_wait<0>();
     }
 
-    // ---- epilogue -----------------------------------------------------------------------------------------------
+    // ---- epilogue of a one-tile CTA ---------------------------------------------------------------------------------
     if (p.cluster) {
         // The p.splits CTAs of this tile are one cluster (rank == split). Each leaves its partial tile in its own
         // shared memory; then CTA r adds slice r of the tile over all ranks, in rank order (the same order as the
@@ -403,17 +480,24 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         constexpr int VPR = TW / CW, NV = TH * VPR;
         const int per = (NV + p.splits - 1) / p.splits;
         const int v_end = ((split + 1) * per < NV) ? (split + 1) * per : NV;
+        const T* peer[8];
+#pragma unroll
+        for (int s = 0; s < 8; s++) peer[s] = cl.map_shared_rank(red, s < p.splits ? s : 0);
         for (int v = split * per + tid; v < v_end && !aborted; v += blockDim.x) {
+            // all parts are fetched before the first addition: the remote reads overlap instead of queueing up
+            T part[8][CW];
+#pragma unroll
+            for (int s = 0; s < 8; s++)
+                if (s < p.splits) *reinterpret_cast<V*>(part[s]) = *reinterpret_cast<const V*>(peer[s] + size_t(v) * CW);
             T sum[CW];
 #pragma unroll
             for (int x = 0; x < CW; x++) sum[x] = T(0);
-            for (int s = 0; s < p.splits; s++) {
-                const T* peer = cl.map_shared_rank(red, s);
-                T part[CW];
-                *reinterpret_cast<V*>(part) = *reinterpret_cast<const V*>(peer + size_t(v) * CW);
 #pragma unroll
-                for (int x = 0; x < CW; x++) sum[x] += part[x];
-            }
+            for (int s = 0; s < 8; s++)
+                if (s < p.splits) {
+#pragma unroll
+                    for (int x = 0; x < CW; x++) sum[x] += part[s][x];
+                }
             const int oy = y0 + v / VPR, ox = x0 + (v % VPR) * CW;
             if (oy >= p.OH || ox >= p.OW || ox + CW <= 0) continue;
             T* dst = out + baseO + int64_t(oy) * p.sOy + ox;
@@ -428,29 +512,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         cl.sync();   // nobody leaves while a peer may still be reading its tile
         return;
     }
-    const int ox = x0 + lane * CW;
-#pragma unroll
-    for (int i = 0; i < RH; i++) {
-        const int oy = y0 + warp * RH + i;
-        if (oy >= p.OH || ox >= p.OW || ox + CW <= 0) continue;
-        T* dst;
-        bool vec_ok;
-        if (p.splits == 1) {
-            dst = out + baseO + int64_t(oy) * p.sOy + ox;
-            vec_ok = p.vec_out != 0;
-        } else {
-            dst = partial + ((int64_t(split) * p.NP + pflat) * p.OH + oy) * int64_t(p.OW) + ox;
-            vec_ok = (p.OW % CW) == 0;
-        }
-        if (vec_ok && ox >= 0 && ox + CW <= p.OW) {
-            if (sizeof(T) == 4) *reinterpret_cast<float4*>(dst) = *reinterpret_cast<float4*>(&acc[i][0]);
-            else *reinterpret_cast<double2*>(dst) = *reinterpret_cast<double2*>(&acc[i][0]);
-        } else {
-#pragma unroll
-            for (int x = 0; x < CW; x++)
-                if (ox + x >= 0 && ox + x < p.OW) dst[x] = acc[i][x];
-        }
-    }
+    store_tile();
 }
 
 // Adds the partial planes of a channel-split launch in split order (deterministic) and scatters into the drain.
@@ -521,8 +583,24 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
         if (st) return st;
         p.status = ctx->tma_status_dev;
     }
-    const int64_t grid = tiles * splits;
+    int64_t grid = tiles * splits;
     if (grid > 0x7fffffffLL) return -1;
+    // Many more tiles than resident CTAs: one resident wave of CTAs walks the tiles, so that weights, table and
+    // barriers are set up once per CTA and the load pipeline never drains between tiles. Needs the same weights for
+    // every tile (the kernel operand does not move with the outer output index). With only a few tiles per CTA the
+    // fixed tile-to-CTA assignment loses more to imbalance (up to one tile in tiles/slots) than the set-up costs,
+    // and the hardware's own CTA scheduling does better (measured on 3.3 and 5.2 tiles per CTA: 3 % and 15 % slower).
+    p.persist = 0;
+    p.tiles_total = tiles;
+    if (TMA && splits == 1 && tiles >= 8 * slots) {
+        bool fixed_weights = true;
+        for (int k = 0; k < p.n_outer; k++)
+            if (p.pK[k] != 0) fixed_weights = false;
+        if (fixed_weights) {
+            p.persist = 1;
+            grid = slots;
+        }
+    }
     const unsigned threads = TMA ? 288 : 256;
     if (splits > 1 && splits <= 8) {
         // one launch: the parts of a tile as a thread-block cluster that adds itself up through shared memory
