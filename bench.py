@@ -1,14 +1,18 @@
 #!/usr/bin/env python
 """Benchmark of the convolution hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl cuda|reference] [--assemble peer|nccl] [--scale S]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl cuda|reference] [--assemble copy|peer|nccl] [--scale S]
 
 Workload (config.workload): BASELINE config 5 -- the 4-D F32 convolution a[8,32,2048,2048] (uniform [0,1], seed 5)
 x k[1,32,5,5] (N(0,0.2), seed 6) -> [8,1,2044,2044], 53.48 GFLOP and 4.43 GB of algorithmic traffic per pass; it is the
 largest single-GPU configuration and the one that shards. With N > 1 (one process per GPU, launched by torchrun)
-the output rows (dim 2) are halo-split over the ranks; each rank holds its input slab (+4 halo rows) and, in the
-default `peer` mode, stores its results straight into rank 0's output buffer over NVLink (the assemble is the conv
-kernel's own epilogue); `nccl` keeps a local slab and gathers with NCCL. Total work is fixed => "scaling": "strong".
+the output rows (dim 2) are halo-split over the ranks; each rank holds its input slab (+4 halo rows). The result is
+assembled in rank 0's memory in one of three ways: `copy` (default) -- every rank computes into a local slab and a
+second stream pushes the finished slab into rank 0's output with device-to-device copies over NVLink while the next
+step's convolution already runs (two local slabs and two output buffers in rotation; the timed region ends only when
+the last copy has landed); `peer` -- the rank's kernel stores straight into rank 0's buffer (the assemble is the
+kernel's own epilogue; its stores then wait on rank 0's link); `nccl` -- a local slab gathered with NCCL on the same
+stream. Total work is fixed => "scaling": "strong".
 
 A step = one full pass. `value` = GFLOP/s with slabs resident in HBM; `e2e` = the same pass from pinned host buffers
 (H2D of the slab, conv, D2H of the result slab inside the timed region). One JSON line on stdout (rank 0).
@@ -156,11 +160,17 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
-    ap.add_argument("--assemble", default="peer", choices=["peer", "nccl"])
+    ap.add_argument("--assemble", default="copy", choices=["copy", "peer", "nccl"])
     ap.add_argument("--scale", type=int, default=1)
     ap.add_argument("--conv-path", type=int, default=0, help="0 auto, 1 generic, 2 tiled, 3 tma")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-extra", action="store_true")
+    ap.add_argument("--verify-assemble", action="store_true",
+                    help="diagnostic (N > 1): rank 0 recomputes the whole convolution alone and compares the assembled "
+                         "result bit for bit (adds 'assembled_equals_single_gpu' to the JSON line)")
+    ap.add_argument("--probe-assemble", action="store_true",
+                    help="diagnostic (N > 1, peer mode): time only the movement of the finished slabs into rank 0's "
+                         "output (device-to-device copies over NVLink), i.e. the floor the owner's link sets for a step")
     args = ap.parse_args()
     steps, warmup = max(1, args.steps), max(0, args.warmup)
 
@@ -224,8 +234,12 @@ def main():
     ctx = dev.ctx
     dev.set_conv_path(args.conv_path)
 
+    ctx_copy = None   # second context (= second stream) of the `copy` assemble mode
+
     def barrier():
         dev.sync()
+        if ctx_copy is not None:
+            L.check(L.lib.nk_sync(ctx_copy), ctx_copy)
         if dist is not None:
             dist.barrier()
 
@@ -273,6 +287,32 @@ def main():
     torch_full = torch_local = None
     if world == 1:
         d_full = d_out_local  # the slab is the whole output
+    elif args.assemble == "copy":
+        ctx_copy = C.c_void_p()
+        L.check(L.lib.nk_device_open(local_rank, C.byref(ctx_copy)))
+        handles = [(C.c_uint8 * L.NK_IPC_HANDLE_BYTES)() for _ in range(2)]
+        d_fulls = []
+        if rank == 0:
+            for h in handles:
+                d_fulls.append(alloc(n_out_full))
+                L.check(L.lib.nk_ipc_export(ctx, d_fulls[-1], h), ctx)
+        box = [[bytes(h) for h in handles]]
+        dist.broadcast_object_list(box, src=0)
+        if rank != 0:
+            for raw in box[0]:
+                h = (C.c_uint8 * L.NK_IPC_HANDLE_BYTES).from_buffer_copy(raw)
+                b = C.c_void_p()
+                L.check(L.lib.nk_ipc_open(ctx, h, L.NK_F32, n_out_full, C.byref(b)), ctx)
+                d_fulls.append(b)
+        d_full = d_fulls[0]
+        d_locals = [d_out_local, alloc(max(n_out_local, 1))]
+        ev_conv, ev_copy = [], []
+        for _ in range(2):
+            for lst in (ev_conv, ev_copy):
+                e = C.c_void_p()
+                L.check(L.lib.nk_event_create(ctx, C.byref(e)), ctx)
+                lst.append(e)
+        step_no = [0]
     elif args.assemble == "peer":
         handle = (C.c_uint8 * L.NK_IPC_HANDLE_BYTES)()
         if rank == 0:
@@ -304,11 +344,35 @@ def main():
             return
         if world == 1:
             L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, d_out_local, pi(cfg_out_local), d_in, pi(cfg_in), d_k, pi(cfg_k), -1), ctx)
+        elif args.assemble == "copy":
+            j = step_no[0] % 2
+            step_no[0] += 1
+            if rank == 0:   # the owner computes straight into place
+                L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, d_fulls[j], pi(cfg_out_in_full), d_in, pi(cfg_in), d_k, pi(cfg_k), -1), ctx)
+                return
+            L.check(L.lib.nk_stream_wait_event(ctx, ev_copy[j]), ctx)        # the push that last read this local slab is done
+            L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, d_locals[j], pi(cfg_out_local), d_in, pi(cfg_in), d_k, pi(cfg_k), -1), ctx)
+            L.check(L.lib.nk_event_record(ctx, ev_conv[j]), ctx)
+            L.check(L.lib.nk_stream_wait_event(ctx_copy, ev_conv[j]), ctx_copy)
+            rows = local_out_shape[2] * local_out_shape[3]
+            full_rows = o_shape[2] * o_shape[3]
+            for b in range(o_shape[0] * o_shape[1]):
+                L.check(L.lib.nk_copy(ctx_copy, d_fulls[j], b * full_rows + slab.out_lo * o_shape[3], d_locals[j], b * rows, rows), ctx_copy)
+            L.check(L.lib.nk_event_record(ctx_copy, ev_copy[j]), ctx_copy)
         elif args.assemble == "peer":
             L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, d_full, pi(cfg_out_in_full), d_in, pi(cfg_in), d_k, pi(cfg_k), -1), ctx)
         else:
             L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, d_out_nccl, pi(cfg_out_local), d_in, pi(cfg_in), d_k, pi(cfg_k), -1), ctx)
             dist.gather(torch_local, gather_list, dst=0)
+
+    def assemble_only_step():
+        """Copies of this rank's finished slab into its place in rank 0's output, one per outer index (contiguous rows)."""
+        if n_out_local == 0 or rank == 0:
+            return
+        rows = local_out_shape[2] * local_out_shape[3]
+        full_rows = o_shape[2] * o_shape[3]
+        for b in range(o_shape[0] * o_shape[1]):
+            L.check(L.lib.nk_copy(ctx, d_full, b * full_rows + slab.out_lo * o_shape[3], d_out_local, b * rows, rows), ctx)
 
     def conv_step_e2e():
         """The same pass from host buffers: H2D of the slab, conv, D2H of the rank's result slab."""
@@ -329,6 +393,9 @@ def main():
         L.check(L.lib.nk_timer_begin(ctx), ctx)
         for _ in range(n_steps):
             fn()
+        if world > 1 and args.assemble == "copy" and rank != 0:
+            for e in ev_copy:   # the timed region ends when the last pushes have landed in rank 0's memory
+                L.check(L.lib.nk_stream_wait_event(ctx, e), ctx)
         ms = C.c_float(0)
         L.check(L.lib.nk_timer_end(ctx, C.byref(ms)), ctx)   # records the end event and synchronises on it
         barrier()
@@ -342,6 +409,17 @@ def main():
             m = float(t.item())
         return m, t0, t1, n1 - n0
 
+    if args.probe_assemble:
+        if world == 1 or args.assemble == "nccl":
+            raise SystemExit("--probe-assemble needs N > 1 and --assemble copy or peer")
+        ms_total, _, _, _ = timed(assemble_only_step, max(warmup, 3), steps)
+        if rank == 0:
+            moved = (n_out_full - n_out_local) * 4
+            print(json.dumps({"probe": "assemble_only", "n_gpus": world, "ms_per_step": ms_total / steps, "bytes_into_rank0": moved,
+                              "gbs_into_rank0": moved / (ms_total / steps * 1e-3) / 1e9}))
+        barrier()
+        dist.destroy_process_group()
+        return
     sampler = ClockSampler(local_rank) if rank == 0 else None
     ms_total, t0, t1, launches = timed(conv_step_resident, max(warmup, 3), steps)
     clocks = sampler.stop(t0, t1) if sampler else None
@@ -360,6 +438,35 @@ def main():
         t = torch.tensor([h2d, d2h, launches], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         h2d, d2h, launches = int(t[0].item()), int(t[1].item()), int(t[2].item())
+
+    assembled_ok = None
+    if args.verify_assemble and world > 1:
+        barrier()
+        if rank == 0:
+            n_full_in = int(np.prod(a_shape))
+            full_host = np.empty(n_full_in, dtype=np.float32)
+            L.lib.nk_jrand_fill(L.NK_F32, 0, 5, 0.0, 1.0, full_host.ctypes.data_as(C.c_void_p), n_full_in)
+            d_a, d_ref = alloc(n_full_in), alloc(n_out_full)
+            L.check(L.lib.nk_write(ctx, d_a, full_host.ctypes.data_as(C.c_void_p), 0, 0, n_full_in), ctx)
+            cfg_a, cfg_o = ND.of_shape(a_shape).as_inline_array(), ND.of_shape(o_shape).as_inline_array()
+            L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, d_ref, pi(cfg_o), d_a, pi(cfg_a), d_k, pi(cfg_k), -1), ctx)
+            want = np.empty(n_out_full, dtype=np.float32)
+            L.check(L.lib.nk_read(ctx, d_ref, want.ctypes.data_as(C.c_void_p), 0, n_out_full), ctx)
+            got = np.empty(n_out_full, dtype=np.float32)
+            assembled_ok = True
+            if args.assemble == "nccl":
+                sl = plan_slabs(o_shape[SPLIT_DIM], world, halo)
+                w4 = want.reshape(o_shape)
+                for g, t in enumerate(gather_list):
+                    sh = list(o_shape); sh[SPLIT_DIM] = sl[g].out_len
+                    part = t[: int(np.prod(sh))].cpu().numpy().reshape(sh)
+                    assembled_ok = assembled_ok and bool(np.array_equal(part, w4[:, :, sl[g].out_lo:sl[g].out_hi, :]))
+            else:
+                for buf in (d_fulls if args.assemble == "copy" else [d_full]):
+                    L.check(L.lib.nk_read(ctx, buf, got.ctypes.data_as(C.c_void_p), 0, n_out_full), ctx)
+                    assembled_ok = assembled_ok and bool(np.array_equal(got, want))
+            L.lib.nk_free(ctx, d_a); L.lib.nk_free(ctx, d_ref)
+        barrier()
 
     if rank == 0:
         peak, peak_kind = read_peaks()
@@ -396,6 +503,8 @@ def main():
                     roofline["fp32_fma"]["frac_of_measured"] = roofline["fp32_fma"]["achieved_tflops"] / fp32
                 except Exception as e:  # the headline line must survive a failing side measurement
                     line["extra"] = {"error": repr(e)}
+        if assembled_ok is not None:
+            line["assembled_equals_single_gpu"] = assembled_ok
         print(json.dumps(line))
         sys.stdout.flush()
 

@@ -176,6 +176,16 @@ int nk_timer_end(nk_ctx* ctx, float* out_ms);            /* second event + synch
  * denominator for the FMA-bound kernels (F32 stencil, F64 convolution, double-evaluated activations). */
 int nk_measure_fma_peak(nk_ctx* ctx, int32_t dtype, double* out_tflops);
 
+/* ---- ordering between contexts (no reference counterpart: OpenCLDevice owns a single in-order queue) ----
+ * A second nk_ctx on the same device is a second stream. An event recorded on one context's stream can be waited
+ * for by another's, e.g. to let copies of finished results run beside the next computation. Waiting for an event
+ * that was never recorded does not block. */
+typedef struct nk_event nk_event;
+int nk_event_create(nk_ctx* ctx, nk_event** out);
+int nk_event_record(nk_ctx* ctx, nk_event* ev);          /* on ctx's stream, after the work queued so far */
+int nk_stream_wait_event(nk_ctx* ctx, nk_event* ev);     /* work queued on ctx's stream from now on waits for ev */
+int nk_event_free(nk_event* ev);
+
 /* ---- multi-GPU (no reference counterpart: the reference has no multi-device execution) ----
  * One process per GPU. A rank exports a buffer; peers open it and use it as the drain of nk_conv, so a
  * slab's results are stored straight into the owner's memory over NVLink (plain stores). */

@@ -67,6 +67,10 @@ SIGNATURES = {
     "nk_write": (C.c_int, [_vp, _vp, _vp, _i64, _i64, _i64]),
     "nk_read": (C.c_int, [_vp, _vp, _vp, _i64, _i64]),
     "nk_copy": (C.c_int, [_vp, _vp, _i64, _vp, _i64, _i64]),
+    "nk_event_create": (C.c_int, [_vp, C.POINTER(_vp)]),
+    "nk_event_record": (C.c_int, [_vp, _vp]),
+    "nk_stream_wait_event": (C.c_int, [_vp, _vp]),
+    "nk_event_free": (C.c_int, [_vp]),
     "nk_host_alloc": (C.c_int, [C.c_size_t, C.POINTER(_vp)]),
     "nk_host_free": (C.c_int, [_vp]),
     "nk_write_async": (C.c_int, [_vp, _vp, _vp, _i64, _i64, _i64]),

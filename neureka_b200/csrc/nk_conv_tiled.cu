@@ -379,7 +379,9 @@ int nk_conv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_
         const double cost4 = double((tiles4 + slots - 1) / slots) * 1.1;
         // a drain on another GPU: results leave over NVLink as tiles finish, and the owner's link is the bottleneck of
         // an assemble -- short-lived tiles start that stream early and keep it steady
-        const bool tall = p.OH >= 128 && cost8 <= cost4 && !p.remote_out;
+        // (only a short launch -- under two waves of tall tiles -- is dominated by that start-up; measured with 7 peers
+        // storing into one owner: 0.198 ms against 0.227 ms; with more waves the tall tiles' efficiency wins again)
+        const bool tall = p.OH >= 128 && cost8 <= cost4 && !(p.remote_out && tiles8 < 2 * slots);
         if (tall) st = f32 ? nk_tiled_dispatch_f32_tma8(ctx, int(KH), int(KW), of, If, Kf, p, &img) : nk_tiled_dispatch_f64_tma8(ctx, int(KH), int(KW), od, Id, Kd, p, &img);
         if (st == -1) st = f32 ? nk_tiled_dispatch_f32_tma4(ctx, int(KH), int(KW), of, If, Kf, p, &img) : nk_tiled_dispatch_f64_tma4(ctx, int(KH), int(KW), od, Id, Kd, p, &img);
         if (st != -1) family = NK_CONV_TMA;

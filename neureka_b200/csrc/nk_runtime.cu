@@ -447,6 +447,52 @@ extern "C" int nk_timer_end(nk_ctx* ctx, float* out_ms) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// events: ordering between the streams of two contexts on one device
+// ------------------------------------------------------------------------------------------------
+struct nk_event {
+    cudaEvent_t ev = nullptr;
+    int device = 0;
+    uint32_t magic = 0x4e4b4556;  // 'NKEV'
+};
+
+extern "C" int nk_event_create(nk_ctx* ctx, nk_event** out) {
+    NK_CHECK_CTX(ctx);
+    if (!out) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_event_create: out pointer is null");
+    *out = nullptr;
+    nk_event* e = new (std::nothrow) nk_event();
+    if (!e) return nk_fail(ctx, NK_ERR_OOM, "nk_event_create: out of host memory");
+    cudaError_t err = cudaEventCreateWithFlags(&e->ev, cudaEventDisableTiming);
+    if (err != cudaSuccess) { delete e; return nk_cuda_fail(ctx, err, "cudaEventCreateWithFlags"); }
+    e->device = ctx->device;
+    *out = e;
+    return NK_OK;
+}
+
+extern "C" int nk_event_record(nk_ctx* ctx, nk_event* ev) {
+    NK_CHECK_CTX(ctx);
+    if (!ev || ev->magic != 0x4e4b4556) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_event_record: not an event");
+    if (ev->device != ctx->device) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_event_record: event of device %d on a context of device %d", ev->device, ctx->device);
+    NK_CUDA(ctx, cudaEventRecord(ev->ev, ctx->stream));
+    return NK_OK;
+}
+
+extern "C" int nk_stream_wait_event(nk_ctx* ctx, nk_event* ev) {
+    NK_CHECK_CTX(ctx);
+    if (!ev || ev->magic != 0x4e4b4556) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_stream_wait_event: not an event");
+    NK_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ev->ev, 0));
+    return NK_OK;
+}
+
+extern "C" int nk_event_free(nk_event* ev) {
+    if (!ev || ev->magic != 0x4e4b4556) return NK_ERR_BAD_ARG;
+    cudaSetDevice(ev->device);
+    cudaEventDestroy(ev->ev);
+    ev->magic = 0;
+    delete ev;
+    return NK_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
 // IPC: share one rank's buffer with the other single-GPU processes of the box
 // ------------------------------------------------------------------------------------------------
 static_assert(sizeof(cudaIpcMemHandle_t) <= NK_IPC_HANDLE_BYTES, "IPC handle does not fit");

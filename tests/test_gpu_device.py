@@ -105,3 +105,45 @@ def test_out_of_memory_is_reported(device):
     t = Tensor.of(np.float32, [2], [1, 2]).to(device)
     assert t.items.tolist() == [1, 2]
     device.restore(t)
+
+
+def test_events_order_two_contexts_on_one_device(device):
+    """A second context on the same device is a second stream; an event recorded on the first makes the second wait.
+    The producer stream fills and squares a buffer many times over (long enough to still be running when the copy is
+    queued); the copy on the other stream, ordered by the event, must see the final values."""
+    import ctypes as C
+    import numpy as np
+    from neureka_b200 import _lib as L
+    from neureka_b200.ndconf import NDConfiguration as ND
+
+    ctx_a = device.ctx
+    ctx_b = C.c_void_p()
+    L.check(L.lib.nk_device_open(getattr(device, "ordinal", 0), C.byref(ctx_b)))
+    try:
+        n = 1 << 24
+        src, dst = C.c_void_p(), C.c_void_p()
+        L.check(L.lib.nk_alloc(ctx_a, L.NK_F32, n, C.byref(src)), ctx_a)
+        L.check(L.lib.nk_alloc(ctx_a, L.NK_F32, n, C.byref(dst)), ctx_a)
+        L.check(L.lib.nk_fill(ctx_a, dst, C.c_double(-1.0), 0, n), ctx_a)
+        L.check(L.lib.nk_sync(ctx_a), ctx_a)
+        ev = C.c_void_p()
+        L.check(L.lib.nk_event_create(ctx_a, C.byref(ev)), ctx_a)
+        L.check(L.lib.nk_stream_wait_event(ctx_b, ev), ctx_b)          # never recorded: must not block
+        cfg = ND.of_shape([n]).as_inline_array()
+        pc = cfg.ctypes.data_as(C.POINTER(C.c_int32))
+        L.check(L.lib.nk_fill(ctx_a, src, C.c_double(1.0), 0, n), ctx_a)
+        for _ in range(40):                                            # src = src + src, 40 times: 2^40
+            L.check(L.lib.nk_binary(ctx_a, L.NK_OP_ADD, L.NK_F32, 1, src, pc, src, pc, src, pc, -1), ctx_a)
+        L.check(L.lib.nk_event_record(ctx_a, ev), ctx_a)
+        L.check(L.lib.nk_stream_wait_event(ctx_b, ev), ctx_b)
+        L.check(L.lib.nk_copy(ctx_b, dst, 0, src, 0, n), ctx_b)
+        L.check(L.lib.nk_sync(ctx_b), ctx_b)
+        got = np.empty(n, dtype=np.float32)
+        L.check(L.lib.nk_read(ctx_b, dst, got.ctypes.data_as(C.c_void_p), 0, n), ctx_b)
+        assert np.all(got == np.float32(2.0 ** 40))
+        assert L.lib.nk_event_free(ev) == L.NK_OK
+        assert L.lib.nk_event_record(ctx_a, None) == L.NK_ERR_BAD_ARG
+        L.lib.nk_free(ctx_a, src)
+        L.lib.nk_free(ctx_a, dst)
+    finally:
+        L.lib.nk_device_close(ctx_b)
