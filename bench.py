@@ -475,9 +475,9 @@ def main():
         alg_flops = 2.0 * n_out_local * k_shape[1] * k_shape[2] * k_shape[3]
         kernel_ms = ms_step  # one conv kernel per step on this rank (peer mode / 1 GPU)
         achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
-        # DRAM bytes of one full-size single-GPU launch, from an ncu capture scaled by the units processed
-        # (profiles/nk_conv_tiled_kernel_tma_cfg5_scale4_full_set.md); unknown for other sizes / slabs
-        traffic = 4.4326e9 if (world == 1 and args.scale == 1) else None
+        # DRAM bytes (read + write) of one full-size single-GPU launch, from an ncu capture of exactly this launch
+        # (profiles/nk_conv_tiled_kernel_tma_persistent_cfg5_full_size.md); unknown for other sizes / slabs
+        traffic = 4.5677e9 if (world == 1 and args.scale == 1) else None
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
                     "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
                     "kernel": last_kernel, "kernel_ms": kernel_ms, "algorithmic_bytes_per_launch": alg_bytes,
