@@ -29,6 +29,7 @@ SOURCES = [
     ("nk_elementwise.cu", ["-fmad=false"]),
     ("nk_ew_unary.cu", ["-fmad=false"]),
     ("nk_conv.cu", []),
+    ("nk_conv_gemm.cu", []),
     ("nk_conv_tiled.cu", []),
     ("nk_conv_tiled_inst_f32_ldgsts.cu", []),
     ("nk_conv_tiled_inst_f32_tma4.cu", []),

@@ -4,6 +4,8 @@
 
 #include "nk_conv_plan.h"
 
+int nk_conv_gemm_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_buf* s1, const NkView& v1, nk_buf* s2, const NkView& v2,
+                     int d, bool* handled);
 int nk_conv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_buf* s1, const NkView& v1,
                       nk_buf* s2, const NkView& v2, int d, bool force, bool* handled);
 
@@ -166,6 +168,13 @@ extern "C" int nk_conv(nk_ctx* ctx, int32_t dtype, int32_t rank,
     if ((st = nk_view_parse(ctx, "nk_conv(src2)", src2, cfg2, rank, dtype, &v2))) return st;
 
     const int path = ctx->conv_path;
+    if (path == NK_CONV_AUTO || path == NK_CONV_GEMM) {
+        bool handled = false;
+        st = nk_conv_gemm_try(ctx, dtype, drn, v0, src1, v1, src2, v2, d, &handled);
+        if (st) return st;
+        if (handled) { ctx->last_conv_path = NK_CONV_GEMM; return NK_OK; }
+        if (path == NK_CONV_GEMM) return nk_fail(ctx, NK_ERR_UNSUPPORTED, "nk_conv: the forced kernel family %d does not apply to these views", path);
+    }
     if (path != NK_CONV_GENERIC) {
         bool handled = false;
         st = nk_conv_tiled_try(ctx, dtype, drn, v0, src1, v1, src2, v2, d, path != NK_CONV_AUTO, &handled);

@@ -154,6 +154,30 @@ def run_extra(dev, hbm_peak_gbs: float) -> dict:
     except Exception as e:   # a side measurement must not take the others down
         out["cfg3_full_size_4096x2048x1024"] = {"error": repr(e)}
 
+    # ---- contraction-shaped `x` (Tensor.convDot: [M,K,1] x [1,K,N]) ------------------------------------------------------
+    try:
+        r = {}
+        for name, dt, npdt, n, fma_peak in (("f32_4096", L.NK_F32, np.float32, 4096, "fp32"), ("f64_2048", L.NK_F64, np.float64, 2048, "fp64"),
+                                            ("f32_1024", L.NK_F32, np.float32, 1024, "fp32")):
+            rng = np.random.default_rng(5)
+            A = _Buf(dev, npdt, n * n, rng.standard_normal(n * n).astype(npdt))
+            B = _Buf(dev, npdt, n * n, rng.standard_normal(n * n).astype(npdt))
+            O = _Buf(dev, npdt, n * n)
+            c1, p1 = _cfg([n, n, 1]); c2, p2 = _cfg([1, n, n]); c0, p0 = _cfg([n, 1, n])
+            flops = 2.0 * n * n * n
+            ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, dt, 3, O.buf, p0, A.buf, p1, B.buf, p2, -1), ctx), 2, 5)
+            r[name] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "kernel": dev.last_kernel(),
+                       "frac_of_measured_fma_peak": flops / (ms * 1e-3) / 1e12 / out["measured_fma_peak_tflops"][fma_peak]}
+            if n == 1024:   # the gather family on the same call, for scale
+                dev.set_conv_path(L.NK_CONV_GENERIC)
+                ms_g = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, dt, 3, O.buf, p0, A.buf, p1, B.buf, p2, -1), ctx), 1, 3)
+                dev.set_conv_path(L.NK_CONV_AUTO)
+                r[name]["gather_family_ms"] = ms_g
+            for bb in (A, B, O): bb.free()
+        out["contraction_MxKx1_x_1xKxN"] = r
+    except Exception as e:
+        out["contraction_MxKx1_x_1xKxN"] = {"error": repr(e)}
+
     # ---- cfg4 -----------------------------------------------------------------------------------------------------
     v = _Buf(dev, np.float64, 128 ** 3, _rand(np.float64, 128 ** 3, 1, 11, 0.0, 1.0))
     k = _Buf(dev, np.float64, 343, _rand(np.float64, 343, 1, 12, 0.0, 0.1))

@@ -265,6 +265,59 @@ def test_kernel_gradient_reduction(device, oracle, dt, case):
     assert np.abs(auto - generic).max() <= (1e-5 if dt == np.float32 else 1e-12) * scale * 16
 
 
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("case", [
+    ([200, 300, 1], [1, 300, 200]),            # CrossDeviceSystemTest.java:95-103, Tensor.convDot
+    ([260, 70, 1], [1, 70, 197]),              # ragged tile edges
+    ([1, 64, 300], [180, 64, 1]),              # roles swapped: the output rows come from the second operand
+    ([4, 40, 50, 1, 9], [1, 1, 50, 33, 9]),    # several dims per index group: M = 160, N = 33, K = 450
+    ([64, 40, 1], [1, 40, 64]),                # under 2^21 multiply-adds: not worth the tables -> gather family
+    ([257, 33], [1, 33]),                      # N = 1: not a matrix product worth tiling -> stays on the gather family
+])
+def test_contractions_take_the_gemm_family(device, oracle, dt, case):
+    """Calls in which every dim is summed away or spanned by one operand only are dense contractions
+    O[m,n] = sum_k A[m,k] B[k,n]; AUTO routes the large ones to the register-tiled GEMM kernel, which must agree with the
+    oracle's state machine and with the gather family."""
+    rng = np.random.default_rng(31)
+    sa, sb = case
+    so = [abs(x - y) + 1 for x, y in zip(sa, sb)]
+    a = rng.standard_normal(int(np.prod(sa))).astype(dt)
+    b = rng.standard_normal(int(np.prod(sb))).astype(dt)
+    c0, c1, c2 = ND.of_shape(so), ND.of_shape(sa), ND.of_shape(sb)
+    auto = check_conv(device, oracle, dt, c0, c0.size, a, c1, b, c2, d=-1)
+    family = device.last_conv_path()
+    m = int(np.prod([x for x, y in zip(sa, sb) if y == 1 and x > 1] or [1]))
+    n = int(np.prod([y for x, y in zip(sa, sb) if x == 1 and y > 1] or [1]))
+    k = int(np.prod([x for x, y in zip(sa, sb) if x == y] or [1]))
+    big = min(m, n) >= 32 and k >= 16 and m * n * k >= (1 << 21)
+    assert (family == L.NK_CONV_GEMM) == bool(big), family
+    if big:
+        assert device.last_kernel() == "nk_conv_gemm_kernel"
+    generic = gpu_conv(device, np.zeros(c0.size, dtype=dt), c0, a, c1, b, c2, d=-1, path=L.NK_CONV_GENERIC)
+    tol = 1e-5 if dt == np.float32 else 1e-12
+    assert np.abs(auto - generic).max() <= tol * np.abs(generic).max() * 8
+
+
+def test_gemm_family_on_permuted_and_sliced_views(device, oracle):
+    """The contraction kernel gathers through offset tables, so column-major operands, a strided slice and a drain
+    that is a window of a larger buffer must give the same numbers as the dense case."""
+    rng = np.random.default_rng(32)
+    M, K, N = 192, 160, 144
+    a_full = rng.standard_normal(M * 2 * K).astype(np.float32)             # parent [M, 2K, 1]; every second k is used
+    b = rng.standard_normal(K * N).astype(np.float32)
+    c1 = ND.of_shape([M, 2 * K, 1]).sliced([M, K, 1], [0, 1, 0], [1, 2, 1])
+    c2 = ND.of_shape([N, K, 1]).reshaped([2, 1, 0])                        # B stored as [N, K]: column-major view [1, K, N]
+    parent_o = ND.of_shape([M + 3, 1, N + 5])
+    c0 = parent_o.sliced([M, 1, N], [2, 0, 4], [1, 1, 1])
+    got = check_conv(device, oracle, np.float32, c0, parent_o.size, a_full, c1, b, c2, d=-1)
+    assert device.last_conv_path() == L.NK_CONV_GEMM
+    a2 = a_full.reshape(M, 2 * K)[:, 1::2].astype(np.float64)
+    b2 = b.reshape(N, K).T.astype(np.float64)
+    want = a2 @ b2
+    view = got.reshape(M + 3, N + 5)[2:2 + M, 4:4 + N]
+    assert np.abs(view - want).max() <= 1e-5 * np.abs(a2).max() * np.abs(b2).max() * K
+
+
 def test_tiled_family_on_views(device, oracle):
     """Sliced image with an offset (unaligned rows), a drain that is a slice of a larger output (the multi-GPU
     assemble writes that way) and a column-major kernel."""
