@@ -468,6 +468,11 @@ def main():
             L.lib.nk_free(ctx, d_a); L.lib.nk_free(ctx, d_ref)
         barrier()
 
+    sharded = None
+    if world > 1 and not args.no_extra:   # collectives inside: every rank takes part
+        from neureka_b200.sharded_extra import run_sharded_extra
+        sharded = run_sharded_extra(dev, dist, rank, world, local_rank, read_peaks()[0])
+
     if rank == 0:
         peak, peak_kind = read_peaks()
         # algorithmic bytes of rank 0's launch: its input slab + the kernel + its output slab, each touched once
@@ -505,6 +510,8 @@ def main():
                     line["extra"] = {"error": repr(e)}
         if assembled_ok is not None:
             line["assembled_equals_single_gpu"] = assembled_ok
+        if sharded is not None:
+            line["extra"] = {"sharded": sharded}
         print(json.dumps(line))
         sys.stdout.flush()
 

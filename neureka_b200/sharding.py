@@ -48,6 +48,53 @@ def plan_slabs(out_extent: int, world: int, halo: int) -> List[Slab]:
     return slabs
 
 
+@dataclass(frozen=True)
+class GradSlab:
+    """A rank's share of the image gradient `D[r] = sum_t k[t] * e[r - t]` along the split dim."""
+    rank: int
+    lo: int              # first image-gradient index owned
+    hi: int              # one past the last
+    err_lo: int          # first error index the rank must hold (= lo - halo, clipped)
+    err_hi: int          # one past the last error index (= hi, clipped to the error's extent)
+    halo: int            # kernel extent - 1
+
+    @property
+    def err_len(self) -> int:
+        return self.err_hi - self.err_lo
+
+    @property
+    def local_extent(self) -> int:
+        """Extent of the local deconvolution's drain: error rows held + halo."""
+        return self.err_len + (self.halo if self.hi > self.lo else 0)
+
+    @property
+    def first_owned_local(self) -> int:
+        """Index, inside the local drain, of gradient index `lo` (local index p stands for global err_lo + p)."""
+        return self.lo - self.err_lo
+
+
+
+def plan_image_grad_slabs(image_extent: int, world: int, halo: int) -> List[GradSlab]:
+    """Split of the image gradient of a convolution along a dim where the image (extent a) is larger than the kernel
+    (extent b = halo + 1; the error has extent a - halo). Gradient index r needs the error indices r - halo .. r that
+    exist, so the halo sits on the error side, *before* the slab. A rank runs the ordinary deconvolution on the error
+    rows [err_lo, err_hi) into a local drain of err_len + halo rows; rows [first_owned_local, +hi-lo) of it are
+    exact, the other (at most 2 * halo) rows are partial sums that belong to the neighbours and are dropped."""
+    if image_extent < 1 or world < 1 or halo < 0 or image_extent - halo < 1:
+        raise ValueError("image_extent, world must be positive and the error extent image_extent - halo at least 1")
+    err_extent = image_extent - halo
+    out = []
+    for s in plan_slabs(image_extent, world, 0):
+        if s.out_len == 0:
+            out.append(GradSlab(s.rank, s.out_lo, s.out_lo, 0, 0, halo))
+            continue
+        e_lo, e_hi = max(s.out_lo - halo, 0), min(s.out_hi, err_extent)
+        if e_hi <= e_lo:   # rows past the error's end that only see its last rows: hold those
+            e_lo, e_hi = max(err_extent - 1 - halo, 0), err_extent
+        out.append(GradSlab(s.rank, s.out_lo, s.out_hi, e_lo, e_hi, halo))
+    return out
+
+
 def split_dim_for(a_shape: Sequence[int], b_shape: Sequence[int], requested: int = -1) -> int:
     """A dim is splittable when the image is larger than the kernel there (halo b-1; no halo for b == 1). Summed
     dims (a == b) would need a cross-GPU reduction and are refused."""

@@ -7,7 +7,7 @@ import sys
 import numpy as np
 import pytest
 
-from neureka_b200.sharding import plan_slabs, slab_views, split_dim_for
+from neureka_b200.sharding import plan_image_grad_slabs, plan_slabs, slab_views, split_dim_for
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -86,3 +86,76 @@ def test_two_rank_halo_split_matches_unsharded(tmp_path):
                         "--master-port", "29713", str(script), ROOT], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "SHARDED_OK" in r.stdout
+
+
+def test_image_gradient_slabs_put_the_halo_on_the_error_side():
+    for extent, world, halo in [(2048, 8, 4), (9, 8, 4), (40, 3, 2), (12, 2, 0), (7, 1, 6)]:
+        gs = plan_image_grad_slabs(extent, world, halo)
+        assert gs[0].lo == 0 and gs[-1].hi == extent
+        for g, h in zip(gs, gs[1:]):
+            assert g.hi == h.lo
+        for g in gs:
+            if g.hi == g.lo:
+                continue
+            assert 0 <= g.err_lo < g.err_hi <= extent - halo
+            # every error index a gradient index of the slab needs and that exists is held
+            for r in (g.lo, g.hi - 1):
+                need = [q for q in range(r - halo, r + 1) if 0 <= q < extent - halo]
+                assert all(g.err_lo <= q < g.err_hi for q in need)
+            assert g.first_owned_local + (g.hi - g.lo) <= g.local_extent
+
+
+GRAD_WORKER = r'''
+import sys
+sys.path.insert(0, sys.argv[1])
+import numpy as np
+import torch, torch.distributed as dist
+from neureka_b200.sharding import plan_image_grad_slabs, plan_slabs
+from neureka_b200.ndconf import NDConfiguration as ND
+from oracle import oracle as O
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+B, Cn, H, W, KH, KW = 2, 3, 23, 17, 4, 3
+OH, OW = H - KH + 1, W - KW + 1
+rng = np.random.default_rng(9)
+img = rng.standard_normal((B, Cn, H, W)).astype(np.float64)
+ker = rng.standard_normal((1, Cn, KH, KW)).astype(np.float64)
+err = rng.standard_normal((B, 1, OH, OW)).astype(np.float64)
+cf = lambda shape: ND.of_shape(list(shape)).as_inline_array()
+# ---- image gradient: rows of the gradient are split, the halo is on the error side --------------------------------------
+g = plan_image_grad_slabs(H, world, KH - 1)[rank]
+e_loc = np.ascontiguousarray(err[:, :, g.err_lo:g.err_hi, :])
+d_loc = np.zeros((B, Cn, g.local_extent, W))
+O.conv(d_loc.reshape(-1), cf(d_loc.shape), ker.reshape(-1), cf(ker.shape), e_loc.reshape(-1), cf(e_loc.shape), d=0)
+mine = d_loc[:, :, g.first_owned_local:g.first_owned_local + (g.hi - g.lo), :]
+# ---- kernel gradient: the forward split; partial sums meet in an all-reduce ------------------------------------------------
+f = plan_slabs(OH, world, KH - 1)[rank]
+i_loc = np.ascontiguousarray(img[:, :, f.in_lo:f.in_hi, :])
+ef_loc = np.ascontiguousarray(err[:, :, f.out_lo:f.out_hi, :])
+gk = np.zeros((1, Cn, KH, KW))
+O.conv(gk.reshape(-1), cf(gk.shape), i_loc.reshape(-1), cf(i_loc.shape), ef_loc.reshape(-1), cf(ef_loc.shape), d=0)
+gk_t = torch.from_numpy(gk)
+dist.all_reduce(gk_t)
+parts = [None] * world
+dist.all_gather_object(parts, mine)
+if rank == 0:
+    full = np.zeros((B, Cn, H, W))
+    O.conv(full.reshape(-1), cf(full.shape), ker.reshape(-1), cf(ker.shape), err.reshape(-1), cf(err.shape), d=0)
+    assert np.array_equal(np.concatenate(parts, axis=2), full), "sharded image gradient differs"
+    ref_k = np.zeros((1, Cn, KH, KW))
+    O.conv(ref_k.reshape(-1), cf(ref_k.shape), img.reshape(-1), cf(img.shape), err.reshape(-1), cf(err.shape), d=0)
+    assert np.abs(gk_t.numpy() - ref_k).max() <= 1e-12 * np.abs(ref_k).max()
+    print("GRAD_SHARDED_OK")
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_gradients_match_unsharded(tmp_path, world):
+    script = tmp_path / "grad_worker.py"
+    script.write_text(GRAD_WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                        "--master-port", str(29720 + world), str(script), ROOT], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "GRAD_SHARDED_OK" in r.stdout
