@@ -40,6 +40,7 @@ struct TiledPlan {
     int remote_out;   // the drain lives on another GPU (stores cross NVLink)
     int persist;      // TMA family: the grid is one resident wave and every CTA walks tiles blockIdx.x, +gridDim.x, ...
     int64_t tiles_total;
+    int wsets;        // persistent walk over tiles whose weights differ: weight sets staged at once (1 = same weights everywhere)
     int cluster;   // channel-split CTAs of a tile form one thread-block cluster and add their tiles through shared memory
     int vec;       // LDGSTS: 16-byte global->shared copies are legal for every chunk
     int vec_out;   // 16-byte stores to the drain are legal
@@ -131,13 +132,16 @@ struct TiledCfg {
     static constexpr bool WREG = KH * KW * int(sizeof(T)) <= 400;   // weights of one channel live in registers
     static constexpr int CPR = SW / CW;                       // LDGSTS chunks per row
     static constexpr int NIT = (SH * CPR + 255) / 256;        // LDGSTS chunks per thread
-    static size_t smem_bytes(int NQ) {
-        // [stages | mbarriers + abort word (128 B) | weights | channel table (32 bytes per channel)]
-        return size_t(STAGES) * STAGE_BYTES + 128 + size_t(NQ) * WPAD * sizeof(T) + 16 + size_t(NQ) * 4 * sizeof(int64_t);
+    static size_t smem_bytes(int NQ, int wsets = 1) {
+        // [stages | mbarriers + abort word (128 B) | tile-info ring (256 B) | weights | channel table (32 B per channel)]
+        return size_t(STAGES) * STAGE_BYTES + 384 + size_t(wsets) * NQ * WPAD * sizeof(T) + 16 + size_t(NQ) * 4 * sizeof(int64_t);
     }
 };
 
-template <class T, int KH, int KW, int RH, bool TMA>
+// RING (persistent walk over short tiles only): the compute warps take each tile's position from a ring the producer
+// thread fills instead of decoding the tile index themselves. A compile-time switch: with the ring code merely present
+// the long-tile launches measured 3 % slower (register allocation of the main loop), so they get a kernel without it.
+template <class T, int KH, int KW, int RH, bool TMA, bool RING = false>
 __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __restrict__ out, T* __restrict__ partial,
                                                             const T* __restrict__ I, const T* __restrict__ K,
                                                             const TiledPlan p, const __grid_constant__ CUtensorMap tmap) {
@@ -146,11 +150,14 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     extern __shared__ __align__(128) unsigned char nk_smem[];
     unsigned char* stage_base = nk_smem;
     uint64_t* mbar = reinterpret_cast<uint64_t*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES);
-    T* wsm = reinterpret_cast<T*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES + 128);
+    // persistent walk: the producer thread publishes where each tile lives (x0, y0, weight set, drain base), 32 bytes
+    // per tile in a ring of STAGES + 1 entries; the compute warps pick an entry up after the tile's first load landed
+    int4* tinfo = reinterpret_cast<int4*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES + 128);
+    T* wsm = reinterpret_cast<T*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES + 384);
     // channel table, 32 bytes per channel: image offset, kernel offset, then the tile's tensor-map coordinates 1..4
     // (everything but x) ready for the producer thread -- it runs on the same issue port as two compute warps per
     // CTA, and every instruction it spends per tile is taken from them
-    int64_t* ctab = reinterpret_cast<int64_t*>((reinterpret_cast<uintptr_t>(wsm + size_t(p.NQ) * WPAD) + 15) & ~uintptr_t(15));
+    int64_t* ctab = reinterpret_cast<int64_t*>((reinterpret_cast<uintptr_t>(wsm + size_t(p.wsets) * p.NQ * WPAD) + 15) & ~uintptr_t(15));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -163,21 +170,26 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     int64_t baseI, baseK, baseO;
     int pidx[NK_TILED_MAX_OUTER];
     int x0, y0;
-    auto decode_tile = [&](int64_t tile) {
+    int wset = 0;   // which of the staged weight sets the current tile uses (outer output dims that move the kernel)
+    // Takes a tile index apart with divisions (once per thread; the producer thread of a persistent CTA steps on digit by digit, see below).
+    auto tile_set = [&](int64_t tile) {
         const int tx = int(tile % p.tilesX); tile /= p.tilesX;
         const int ty = int(tile % p.tilesY); tile /= p.tilesY;
         baseI = p.bI; baseK = p.bK; baseO = p.bO;
         int64_t rem = tile;
+        int ws = 0, wm = 1;
         for (int k = p.n_outer - 1; k >= 0; k--) {
-            int64_t idx = rem % p.oext[k];
+            const int idx = int(rem % p.oext[k]);
             rem /= p.oext[k];
             baseI += idx * p.pI[k]; baseK += idx * p.pK[k]; baseO += idx * p.os[k];
-            pidx[k] = p.pI[k] != 0 ? int(idx) : 0;   // the image index follows the output index only where pI != 0
+            pidx[k] = p.pI[k] != 0 ? idx : 0;   // the image index follows the output index only where pI != 0
+            if (p.pK[k] != 0) { ws += idx * wm; wm *= int(p.oext[k]); }
         }
+        wset = p.wsets > 1 ? ws : 0;
         x0 = tx * TW - p.xoff;
         y0 = ty * TH;
     };
-    decode_tile(tile_first);
+    tile_set(tile_first);
     const int64_t pflat = tile_first / (int64_t(p.tilesX) * p.tilesY);   // used by the two-pass split path (one tile per CTA)
     const int cper = (p.NQ + p.splits - 1) / p.splits;
     const int c_begin = split * cper;
@@ -204,7 +216,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             n++;
         }
     };
-    auto tile_coords = [&]() -> int4 {   // of the tile decode_tile() was last called for, by this thread
+    auto tile_coords = [&]() -> int4 {   // of the tile this thread currently stands on
         int b[4] = {0, 0, 0, 0};
         int n = 0;
         if (p.has_y) b[n++] = y0;
@@ -251,11 +263,20 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         *reinterpret_cast<int4*>(&ctab[c * 4 + 2]) = make_int4(cc[0], cc[1], cc[2], cc[3]);
     }
     __syncthreads();
-    for (int e = tid; e < (c_end - c_begin) * WPAD; e += blockDim.x) {
-        const int c = c_begin + e / WPAD, t = e % WPAD;
+    for (int e = tid; e < p.wsets * (c_end - c_begin) * WPAD; e += blockDim.x) {
+        const int per_set = (c_end - c_begin) * WPAD;
+        const int ws = e / per_set, r = e - ws * per_set;
+        const int c = c_begin + r / WPAD, t = r % WPAD;
+        int64_t kb = baseK;   // one set: the weights of this CTA's (only, or every) tile
+        if (p.wsets > 1) {    // several: set ws belongs to the outer output indices that tile_set() folds into ws
+            kb = p.bK;
+            int rem = ws;
+            for (int k = p.n_outer - 1; k >= 0; k--)
+                if (p.pK[k] != 0) { kb += int64_t(rem % int(p.oext[k])) * p.pK[k]; rem /= int(p.oext[k]); }
+        }
         T v = 0;
-        if (t < KH * KW) v = K[baseK + ctab[c * 4 + 1] + (t / KW) * p.sKy + (t % KW) * p.sKx];
-        wsm[size_t(c) * WPAD + t] = v;
+        if (t < KH * KW) v = K[kb + ctab[c * 4 + 1] + (t / KW) * p.sKy + (t % KW) * p.sKx];
+        wsm[(size_t(ws) * p.NQ + c) * WPAD + t] = v;
     }
 
     // ---- loaders ------------------------------------------------------------------------------------------------
@@ -307,7 +328,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     // One channel's worth of multiply-adds for this thread (tile rows warp*RH .. +RH, columns lane*CW .. +CW).
     auto consume = [&](int stage, int c) {
         const T* tile = reinterpret_cast<const T*>(stage_base + size_t(stage) * C::STAGE_BYTES) + (warp * RH) * SW + lane * CW;
-        const T* wc = wsm + size_t(c) * WPAD;
+        const T* wc = wsm + (size_t(wset) * p.NQ + c) * WPAD;
         T w[C::WREG ? WPAD : CW];
         if (C::WREG) {
 #pragma unroll
@@ -339,7 +360,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         }
     };
 
-    // Stores this thread's RH x CW results of the tile decode_tile() was last called for: into the drain, or -- two-pass
+    // Stores this thread's RH x CW results of the tile the thread currently stands on: into the drain, or -- two-pass
     // channel split -- into this part's plane of the scratch buffer.
     auto store_tile = [&]() {
         const int ox = x0 + lane * CW;
@@ -386,23 +407,65 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         };
         if (warp == 8) {
             if (lane == 0) {
-                // `issued` counts tile loads over the CTA's whole life: load g uses stage g % STAGES in round g / STAGES
+                // `issued` counts tile loads over the CTA's whole life: load g uses stage g % STAGES in round g / STAGES.
+                // A tile index is a mixed-radix number (tx | ty | outer output indices, last outer dim fastest); the
+                // walk adds gridDim.x to it digit by digit with carry -- a few adds and compares per tile, no division.
+                constexpr int NDIG = 2 + NK_TILED_MAX_OUTER;
+                int dg[NDIG], sg[NDIG], rx[NDIG];
+                if (p.persist) {
+                    int64_t t = tile_first, st = tile_step;
+                    for (int i = 0; i < NDIG; i++) {
+                        rx[i] = i == 0 ? p.tilesX : i == 1 ? p.tilesY : ((i - 2) < p.n_outer ? int(p.oext[p.n_outer - 1 - (i - 2)]) : 1);
+                        dg[i] = int(t % rx[i]); t /= rx[i];
+                        sg[i] = int(st % rx[i]); st /= rx[i];
+                    }
+                }
                 bool ok = true;
                 int64_t tile = tile_first;
+                int tile_no = 0;
+                bool announce = false;      // a new tile's info still has to go into the ring (after the stage came free)
                 int c = c_begin + issued;   // the first loads of the first tile were requested in the prologue
                 int4 tb = tile_coords();
                 while (ok) {
                     if (c >= c_end) {
                         tile += tile_step;
                         if (!p.persist || tile >= p.tiles_total) break;
-                        decode_tile(tile);
+                        int carry = 0;
+                        for (int i = 0; i < NDIG; i++) {
+                            const int v = dg[i] + sg[i] + carry;
+                            carry = v >= rx[i] ? 1 : 0;
+                            dg[i] = v - (carry ? rx[i] : 0);
+                        }
+                        baseO = p.bO;
+                        int ws = 0, wm = 1;
+                        for (int j = 0; j < p.n_outer; j++) {
+                            const int k = p.n_outer - 1 - j, idx = dg[2 + j];
+                            baseO += idx * p.os[k];
+                            pidx[k] = p.pI[k] != 0 ? idx : 0;
+                            if (p.pK[k] != 0) { ws += idx * wm; wm *= int(p.oext[k]); }
+                        }
+                        wset = p.wsets > 1 ? ws : 0;
+                        x0 = dg[0] * TW - p.xoff;
+                        y0 = dg[1] * TH;
                         tb = tile_coords();
                         c = c_begin;
+                        tile_no++;
+                        announce = true;
                     }
                     const int stage = issued % STAGES;
                     const int4 cc = *reinterpret_cast<const int4*>(&ctab[c * 4 + 2]);
                     if (issued >= STAGES) ok = wait_or_abort(&empty_bar[stage], unsigned(issued / STAGES - 1) & 1u);
-                    if (ok) tma_fire(stage, cc.x + tb.x, cc.y + tb.y, cc.z + tb.z, cc.w + tb.w);
+                    if (ok) {
+                        if (RING && announce) {
+                            // every compute warp is past the tile whose entry this overwrites (ring of STAGES + 1, at least
+                            // one load per tile, and the wait above); the arrive inside tma_fire publishes the stores
+                            int4* e = tinfo + 2 * (tile_no % (STAGES + 1));
+                            e[0] = make_int4(x0, y0, wset, 0);
+                            *reinterpret_cast<int64_t*>(e + 1) = baseO;
+                            announce = false;
+                        }
+                        tma_fire(stage, cc.x + tb.x, cc.y + tb.y, cc.z + tb.z, cc.w + tb.w);
+                    }
                     c++;
                 }
                 if (!ok || *abort_word) {
@@ -418,7 +481,18 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             int g = 0;   // loads consumed so far, same numbering as the producer's
             bool ok = true;
             int64_t tile = tile_first;
+            int tile_no = 0;
             while (true) {
+                if (!RING && tile_no > 0) tile_set(tile);   // long tiles: a dozen divisions per tile do not matter
+                if (RING && tile_no > 0) {
+                    // where this tile lives: published by the producer before the tile's first load, so wait for that
+                    // load (the loop below finds it complete) and pick the entry up
+                    if (!wait_or_abort(&full_bar[g % STAGES], unsigned(g / STAGES) & 1u)) { ok = false; break; }
+                    const int4* e = tinfo + 2 * (tile_no % (STAGES + 1));
+                    const int4 a = e[0];
+                    x0 = a.x; y0 = a.y; wset = a.z;
+                    baseO = *reinterpret_cast<const int64_t*>(e + 1);
+                }
                 for (int c = c_begin; c < c_end; c++, g++) {
                     const int stage = g % STAGES;
                     if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; break; }
@@ -434,7 +508,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                     for (int x = 0; x < CW; x++) acc[i][x] = T(0);
                 tile += tile_step;
                 if (tile >= p.tiles_total) break;
-                decode_tile(tile);
+                tile_no++;
             }
         }
         __syncthreads();
@@ -548,30 +622,48 @@ int nk_tma_encode(nk_ctx* ctx, int dtype, const TmaImage& img, int box_w, int bo
 template <class T, int KH, int KW, int RH, bool TMA>
 int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, const TmaImage* img) {
     using C = TiledCfg<T, KH, KW, RH>;
-    const size_t smem = C::smem_bytes(p.NQ);
-    if (smem > size_t(ctx->prop.sharedMemPerBlockOptin)) return -1;   // caller falls back to another family
     p.tilesX = (p.OW + p.xoff + C::TW - 1) / C::TW;
     p.tilesY = (p.OH + C::TH - 1) / C::TH;
     const int64_t tiles = int64_t(p.tilesX) * p.tilesY * p.NP;
-    {
+    // Outer output dims that move the kernel operand (each output channel of an image gradient has its own weights):
+    // a persistent walk needs all those weight sets in shared memory at once -- fine while they are small.
+    int64_t wsets = 1;
+    for (int k = 0; k < p.n_outer; k++)
+        if (p.pK[k] != 0) wsets *= p.oext[k];
+    const bool sets_fit = wsets == 1 || (TMA && wsets * int64_t(p.NQ) * C::WPAD * int64_t(sizeof(T)) <= 16384);
+    size_t smem = 0;
+    int64_t slots = 0;
+    int splits = 1;
+    // shared memory, occupancy and channel split for a launch that stages `w` weight sets
+    auto configure = [&](int w) -> int {
+        smem = C::smem_bytes(p.NQ, w);
+        if (smem > size_t(ctx->prop.sharedMemPerBlockOptin)) return -1;   // caller falls back to another family
         cudaError_t e = cudaFuncSetAttribute(nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel)");
+        int per_sm = 1;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, TMA ? 288 : 256, smem) != cudaSuccess || per_sm < 1) {
+            cudaGetLastError();
+            per_sm = 1;
+        }
+        slots = int64_t(ctx->prop.multiProcessorCount) * per_sm;
+        // channel split: only when the tiles alone cannot fill the machine and each part keeps >= 4 channels; the
+        // CTA count stays within one resident wave (a second, nearly empty wave would double the time)
+        splits = 1;
+        if (tiles < slots && p.NQ >= 8) {
+            splits = int(slots / tiles);
+            if (splits > p.NQ / 4) splits = p.NQ / 4;
+            if (splits > 32) splits = 32;
+            if (splits < 1) splits = 1;
+        }
+        return 0;
+    };
+    p.wsets = (sets_fit && wsets > 1) ? int(wsets) : 1;
+    int cst = configure(p.wsets);
+    if (cst == 0 && p.wsets > 1 && !(splits == 1 && tiles >= 8 * slots)) {   // no persistent walk after all: one set per CTA
+        p.wsets = 1;
+        cst = configure(1);
     }
-    // channel split: only when the tiles alone cannot fill the machine and each part keeps >= 4 channels; the
-    // CTA count stays within one resident wave (a second, nearly empty wave would double the time)
-    int per_sm = 1;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, TMA ? 288 : 256, smem) != cudaSuccess || per_sm < 1) {
-        cudaGetLastError();
-        per_sm = 1;
-    }
-    const int64_t slots = int64_t(ctx->prop.multiProcessorCount) * per_sm;
-    int splits = 1;
-    if (tiles < slots && p.NQ >= 8) {
-        splits = int(slots / tiles);
-        if (splits > p.NQ / 4) splits = p.NQ / 4;
-        if (splits > 32) splits = 32;
-        if (splits < 1) splits = 1;
-    }
+    if (cst) return cst;
     p.splits = splits;
     p.cluster = 0;
     CUtensorMap tmap;
@@ -587,19 +679,16 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     if (grid > 0x7fffffffLL) return -1;
     // Many more tiles than resident CTAs: one resident wave of CTAs walks the tiles, so that weights, table and
     // barriers are set up once per CTA and the load pipeline never drains between tiles. Needs the same weights for
-    // every tile (the kernel operand does not move with the outer output index). With only a few tiles per CTA the
+    // every tile, or for all its weight sets to fit in shared memory together. With only a few tiles per CTA the
     // fixed tile-to-CTA assignment loses more to imbalance (up to one tile in tiles/slots) than the set-up costs,
     // and the hardware's own CTA scheduling does better (measured on 3.3 and 5.2 tiles per CTA: 3 % and 15 % slower).
     p.persist = 0;
     p.tiles_total = tiles;
-    if (TMA && splits == 1 && tiles >= 8 * slots) {
-        bool fixed_weights = true;
-        for (int k = 0; k < p.n_outer; k++)
-            if (p.pK[k] != 0) fixed_weights = false;
-        if (fixed_weights) {
-            p.persist = 1;
-            grid = slots;
-        }
+    bool ring = false;
+    if (TMA && splits == 1 && tiles >= 8 * slots && (wsets == 1 || p.wsets > 1)) {
+        p.persist = 1;
+        ring = p.NQ < 8;   // short tiles: decoding would cost as much as the tile's arithmetic
+        grid = slots;
     }
     const unsigned threads = TMA ? 288 : 256;
     if (splits > 1 && splits <= 8) {
@@ -634,6 +723,14 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
         int st = nk_scratch(ctx, need, &scratch);
         if (st) return st;
         partial = reinterpret_cast<T*>(scratch);
+    }
+    if constexpr (TMA) {
+        if (ring) {
+            cudaError_t e = cudaFuncSetAttribute(nk_conv_tiled_kernel<T, KH, KW, RH, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+            if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel, ring)");
+            nk_conv_tiled_kernel<T, KH, KW, RH, true, true><<<unsigned(grid), threads, smem, ctx->stream>>>(out, partial, I, K, p, tmap);
+            return nk_after_launch(ctx, "nk_conv_tiled_kernel<tma,ring>");
+        }
     }
     nk_conv_tiled_kernel<T, KH, KW, RH, TMA><<<unsigned(grid), threads, smem, ctx->stream>>>(out, partial, I, K, p, tmap);
     int st = nk_after_launch(ctx, TMA ? "nk_conv_tiled_kernel<tma>" : "nk_conv_tiled_kernel<ldgsts>");

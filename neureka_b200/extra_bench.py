@@ -178,6 +178,31 @@ def run_extra(dev, hbm_peak_gbs: float) -> dict:
     except Exception as e:
         out["contraction_MxKx1_x_1xKxN"] = {"error": repr(e)}
 
+    # ---- gradients of cfg5's convolution (error seeded, uniform [-1,1]) ---------------------------------------------------
+    try:
+        Bn, Cn, H, W, KH = 8, 32, 2048, 2048, 5
+        OH, OW = H - KH + 1, W - KH + 1
+        img = _Buf(dev, np.float32, Bn * Cn * H * W)
+        L.check(L.lib.nk_fill(ctx, img.buf, C.c_double(0.5), 0, Bn * Cn * H * W), ctx)
+        err = _Buf(dev, np.float32, Bn * OH * OW, _rand(np.float32, Bn * OH * OW, 0, 9, -1.0, 1.0))
+        ker = _Buf(dev, np.float32, Cn * KH * KH, _rand(np.float32, Cn * KH * KH, 1, 6, 0.0, 0.2))
+        gimg, gker = _Buf(dev, np.float32, Bn * Cn * H * W), _Buf(dev, np.float32, Cn * KH * KH)
+        ci, pi_ = _cfg([Bn, Cn, H, W]); ce, pe = _cfg([Bn, 1, OH, OW]); ckk, pkk = _cfg([1, Cn, KH, KH])
+        flops = 2.0 * Bn * OH * OW * Cn * KH * KH
+        r = {}
+        ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, gimg.buf, pi_, ker.buf, pkk, err.buf, pe, 0), ctx), 2, 5)
+        nbytes = 4.0 * (Bn * Cn * H * W + Bn * OH * OW + Cn * KH * KH)
+        r["grad_image"] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                           "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / hbm_peak_gbs, "kernel": dev.last_kernel(),
+                           "note": "write-bound: 4.29 GB of gradient written, 0.13 GB of error read"}
+        ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, gker.buf, pkk, img.buf, pi_, err.buf, pe, 0), ctx), 2, 5)
+        r["grad_kernel"] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                            "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / hbm_peak_gbs, "kernel": dev.last_kernel()}
+        out["cfg5_gradients"] = r
+        for bb in (img, err, ker, gimg, gker): bb.free()
+    except Exception as e:
+        out["cfg5_gradients"] = {"error": repr(e)}
+
     # ---- cfg4 -----------------------------------------------------------------------------------------------------
     v = _Buf(dev, np.float64, 128 ** 3, _rand(np.float64, 128 ** 3, 1, 11, 0.0, 1.0))
     k = _Buf(dev, np.float64, 343, _rand(np.float64, 343, 1, 12, 0.0, 0.1))
