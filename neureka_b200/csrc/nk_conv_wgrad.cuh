@@ -5,7 +5,8 @@
 // One CTA walks a list of work units; a unit is one TH x TW tile of T2 (the error) for one outer reduction index,
 // together with the (TH+KH-1) x (TW+KW-1) tile of T1 (the image) at the same position. Both tiles arrive by TMA
 // (zero fill outside the tensors: a missing term contributes 0, exactly like the reference's range check) into a
-// two-stage shared-memory ring. A thread owns RH x CW positions of the error tile and keeps all KH x KW partial
+// three-stage shared-memory ring fed by a producer warp (full/empty mbarriers, every wait bounded; the eight compute
+// warps never meet a CTA-wide barrier inside the loop). A thread owns RH x CW positions of the error tile and keeps all KH x KW partial
 // sums in registers; every image row segment it loads feeds up to KH taps rows. After its last unit the CTA reduces
 // the partial sums (warp shuffles, then the eight warp results in order) and writes one partial window to scratch;
 // a second kernel adds the CTAs' windows in CTA order, so the result does not depend on scheduling.
@@ -40,12 +41,14 @@ struct WgradCfg {
     static constexpr int NS = CW + HALO_W;
     static constexpr int A_BYTES = ((SH * SW * int(sizeof(T)) + 127) / 128) * 128;
     static constexpr int E_BYTES = ((TH * TW * int(sizeof(T)) + 127) / 128) * 128;
-    static constexpr int STAGES = 2;
+    static constexpr int STAGES = 3;
     static size_t smem_bytes() { return size_t(STAGES) * (A_BYTES + E_BYTES) + 128 + size_t(8) * KH * KW * sizeof(T); }
 };
 
+// 288 threads: warps 0..7 multiply, warp 8 feeds the ring. full[s] completes when both tiles of a unit have landed
+// (one arrival + their bytes), empty[s] when all eight compute warps are done with stage s. Every wait is bounded.
 template <class T, int KH, int KW>
-__global__ void __launch_bounds__(256) nk_conv_wgrad_kernel(T* __restrict__ partial, const WgradPlan p,
+__global__ void __launch_bounds__(288) nk_conv_wgrad_kernel(T* __restrict__ partial, const WgradPlan p,
                                                             const __grid_constant__ CUtensorMap mapA,
                                                             const __grid_constant__ CUtensorMap mapE) {
     using C = WgradCfg<T, KH, KW>;
@@ -54,50 +57,37 @@ __global__ void __launch_bounds__(256) nk_conv_wgrad_kernel(T* __restrict__ part
     unsigned char* a_base = nk_smem;
     unsigned char* e_base = nk_smem + size_t(STAGES) * C::A_BYTES;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(nk_smem + size_t(STAGES) * (C::A_BYTES + C::E_BYTES));
-    volatile int* abort_word = reinterpret_cast<volatile int*>(full_bar + STAGES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    volatile int* abort_word = reinterpret_cast<volatile int*>(full_bar + 2 * STAGES);
     T* red = reinterpret_cast<T*>(nk_smem + size_t(STAGES) * (C::A_BYTES + C::E_BYTES) + 128);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t pflat = blockIdx.x / p.chunks;
     const int chunk = int(blockIdx.x % p.chunks);
-    int pidx[NK_TILED_MAX_OUTER];
-    {
-        int64_t rem = pflat;
-        for (int k = p.n_outer - 1; k >= 0; k--) { pidx[k] = int(rem % p.oext[k]); rem /= p.oext[k]; }
-    }
     const int64_t per = (p.units + p.chunks - 1) / p.chunks;
     const int64_t u_begin = per * chunk;
     const int64_t u_end = (u_begin + per < p.units) ? u_begin + per : p.units;
-    const int64_t n_it = u_end - u_begin;
+    const int64_t n_it = u_end > u_begin ? u_end - u_begin : 0;
 
-    if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) nk_mbar_init(&full_bar[s], 1);
+    if (tid == 256) {
+        for (int s = 0; s < STAGES; s++) { nk_mbar_init(&full_bar[s], 1); nk_mbar_init(&empty_bar[s], 8); }
         *abort_word = 0;
         nk_fence_barrier_init();
     }
     __syncthreads();
 
-    int64_t last_issued = -1;
-    auto issue = [&](int stage, int64_t u) {   // thread 0
-        last_issued = u - u_begin;
-        int64_t rem = u;
-        const int tx = int(rem % p.tilesX); rem /= p.tilesX;
-        const int ty = int(rem % p.tilesY); rem /= p.tilesY;
-        int ca[5], ce[5];
-        ca[0] = ce[0] = tx * TW;
-        int n = 1;
-        if (p.has_y) { ca[n] = ce[n] = ty * TH; n++; }
-        for (int k = p.n_outer - 1; k >= 0; k--) {
-            const int q = int(rem % p.qext[k]);
-            rem /= p.qext[k];
-            ce[n] = q;
-            ca[n] = pidx[k] + q;
-            n++;
+    auto wait_or_abort = [&](uint64_t* bar, unsigned parity) -> bool {
+        unsigned spins = 0;
+        while (!nk_mbar_try_wait(bar, parity)) {
+            ++spins;
+            if ((spins & 1023u) == 0 && *abort_word) return false;
+            if (spins > NK_TMA_SPIN_LIMIT) {
+                *abort_word = 1;
+                if (p.status) atomicExch(p.status, 1);
+                return false;
+            }
         }
-        const unsigned bytes = unsigned(((p.has_y ? SH : 1) * SW + (p.has_y ? TH : 1) * TW) * sizeof(T));
-        nk_mbar_expect_tx(&full_bar[stage], bytes);
-        nk_tma_load(a_base + size_t(stage) * C::A_BYTES, &mapA, &full_bar[stage], p.nd, ca);
-        nk_tma_load(e_base + size_t(stage) * C::E_BYTES, &mapE, &full_bar[stage], p.nd, ce);
+        return true;
     };
 
     T acc[KH][KW];
@@ -106,81 +96,117 @@ __global__ void __launch_bounds__(256) nk_conv_wgrad_kernel(T* __restrict__ part
 #pragma unroll
         for (int b = 0; b < KW; b++) acc[a][b] = T(0);
 
-    if (tid == 0) {
-        nk_fence_proxy_async();
-        if (n_it > 0) issue(0, u_begin);
-    }
-    bool gave_up = false;
-    for (int64_t it = 0; it < n_it; it++) {
-        const int stage = int(it % STAGES);
-        unsigned spins = 0;
-        while (!nk_mbar_try_wait(&full_bar[stage], unsigned(it / STAGES) & 1u)) {
-            if (++spins > NK_TMA_SPIN_LIMIT) { gave_up = true; break; }
-        }
-        if (gave_up && p.status) atomicExch(p.status, 1);
-        // everyone has finished reading the other stage (previous unit) before it is refilled; uniform give-up vote
-        gave_up = __syncthreads_or(gave_up) != 0;
-        if (gave_up) break;
-        if (tid == 0 && it + 1 < n_it) issue(int((it + 1) % STAGES), u_begin + it + 1);
-
-        const T* at = reinterpret_cast<const T*>(a_base + size_t(stage) * C::A_BYTES) + (warp * RH) * SW + lane * CW;
-        const T* et = reinterpret_cast<const T*>(e_base + size_t(stage) * C::E_BYTES) + (warp * RH) * TW + lane * CW;
-        // when the maps have no row dim only row 0 of each tile is real: rows beyond it must not contribute
-        const int rows = p.has_y ? RH : (warp == 0 ? 1 : 0);
-        if (rows == 0) continue;   // nothing real in this warp's tile rows (and they were never written)
-        T ev[RH][CW];
-#pragma unroll
-        for (int i = 0; i < RH; i++) {
-            if (i < rows) {
-                if (sizeof(T) == 4) *reinterpret_cast<float4*>(ev[i]) = *reinterpret_cast<const float4*>(et + i * TW);
-                else *reinterpret_cast<double2*>(ev[i]) = *reinterpret_cast<const double2*>(et + i * TW);
-            } else {
-#pragma unroll
-                for (int x = 0; x < CW; x++) ev[i][x] = T(0);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < RH + KH - 1; j++) {
-            if (!p.has_y && j > 0) break;
-            T seg[NS];
-#pragma unroll
-            for (int v = 0; v < NS / CW; v++) {
-                if (sizeof(T) == 4) *reinterpret_cast<float4*>(&seg[v * CW]) = *reinterpret_cast<const float4*>(at + j * SW + v * CW);
-                else *reinterpret_cast<double2*>(&seg[v * CW]) = *reinterpret_cast<const double2*>(at + j * SW + v * CW);
-            }
-#pragma unroll
-            for (int ky = 0; ky < KH; ky++) {
-                const int i = j - ky;   // error row that meets image row j at tap row ky
-                if (i >= 0 && i < RH) {
-#pragma unroll
-                    for (int kx = 0; kx < KW; kx++)
-#pragma unroll
-                        for (int x = 0; x < CW; x++) acc[ky][kx] = fma(seg[kx + x], ev[i][x], acc[ky][kx]);
+    if (warp == 8) {
+        if (lane == 0 && n_it > 0) {
+            // The unit index is a mixed-radix number (tile x | tile y | outer reduction indices, last dim fastest): taken
+            // apart once, then counted up -- the producer shares an issue port with compute warps, so no division per unit.
+            int pidx[NK_TILED_MAX_OUTER], q[NK_TILED_MAX_OUTER];
+            {
+                int64_t rem = pflat;
+                for (int k = p.n_outer - 1; k >= 0; k--) { pidx[k] = int(rem % p.oext[k]); rem /= p.oext[k]; }
+                rem = u_begin;
+                const int tx0 = int(rem % p.tilesX); rem /= p.tilesX;
+                const int ty0 = int(rem % p.tilesY); rem /= p.tilesY;
+                for (int k = p.n_outer - 1; k >= 0; k--) { q[k] = int(rem % p.qext[k]); rem /= p.qext[k]; }
+                int tx = tx0, ty = ty0;
+                const unsigned bytes = unsigned(((p.has_y ? SH : 1) * SW + (p.has_y ? TH : 1) * TW) * sizeof(T));
+                nk_fence_proxy_async();
+                bool ok = true;
+                int64_t issued = 0;
+                for (int64_t it = 0; it < n_it && ok; it++) {
+                    const int stage = int(it % STAGES);
+                    int ca[5], ce[5];
+                    ca[0] = ce[0] = tx * TW;
+                    int n = 1;
+                    if (p.has_y) { ca[n] = ce[n] = ty * TH; n++; }
+                    for (int k = p.n_outer - 1; k >= 0; k--) { ce[n] = q[k]; ca[n] = pidx[k] + q[k]; n++; }
+                    if (it >= STAGES) ok = wait_or_abort(&empty_bar[stage], unsigned(it / STAGES - 1) & 1u);
+                    if (!ok) break;
+                    nk_mbar_expect_tx(&full_bar[stage], bytes);
+                    nk_tma_load(a_base + size_t(stage) * C::A_BYTES, &mapA, &full_bar[stage], p.nd, ca);
+                    nk_tma_load(e_base + size_t(stage) * C::E_BYTES, &mapE, &full_bar[stage], p.nd, ce);
+                    issued++;
+                    if (++tx == p.tilesX) {
+                        tx = 0;
+                        if (++ty == p.tilesY) {
+                            ty = 0;
+                            for (int k = p.n_outer - 1; k >= 0; k--) {
+                                if (++q[k] < int(p.qext[k])) break;
+                                q[k] = 0;
+                            }
+                        }
+                    }
+                }
+                if (!ok || *abort_word) {
+                    // requested copies may still be landing in this CTA's shared memory: wait for the last ones (bounded)
+                    for (int64_t j = (issued > STAGES ? issued - STAGES : 0); j < issued; j++) {
+                        unsigned spins = 0;
+                        while (!nk_mbar_try_wait(&full_bar[j % STAGES], unsigned(j / STAGES) & 1u))
+                            if (++spins > NK_TMA_SPIN_LIMIT) break;
+                    }
                 }
             }
         }
-    }
-    if (gave_up) {
-        // the request for the next unit may still be landing: wait for it (bounded) before leaving
-        if (tid == 0 && last_issued >= 0) {
-            unsigned spins = 0;
-            while (!nk_mbar_try_wait(&full_bar[last_issued % STAGES], unsigned(last_issued / STAGES) & 1u))
-                if (++spins > NK_TMA_SPIN_LIMIT) break;
+    } else {
+        // when the maps have no row dim only row 0 of each tile is real: rows beyond it must not contribute
+        const int rows = p.has_y ? RH : (warp == 0 ? 1 : 0);
+        for (int64_t it = 0; it < n_it; it++) {
+            const int stage = int(it % STAGES);
+            if (!wait_or_abort(&full_bar[stage], unsigned(it / STAGES) & 1u)) break;
+            if (rows > 0) {
+                const T* at = reinterpret_cast<const T*>(a_base + size_t(stage) * C::A_BYTES) + (warp * RH) * SW + lane * CW;
+                const T* et = reinterpret_cast<const T*>(e_base + size_t(stage) * C::E_BYTES) + (warp * RH) * TW + lane * CW;
+                T ev[RH][CW];
+#pragma unroll
+                for (int i = 0; i < RH; i++) {
+                    if (i < rows) {
+                        if (sizeof(T) == 4) *reinterpret_cast<float4*>(ev[i]) = *reinterpret_cast<const float4*>(et + i * TW);
+                        else *reinterpret_cast<double2*>(ev[i]) = *reinterpret_cast<const double2*>(et + i * TW);
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < CW; x++) ev[i][x] = T(0);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < RH + KH - 1; j++) {
+                    if (!p.has_y && j > 0) break;
+                    T seg[NS];
+#pragma unroll
+                    for (int v = 0; v < NS / CW; v++) {
+                        if (sizeof(T) == 4) *reinterpret_cast<float4*>(&seg[v * CW]) = *reinterpret_cast<const float4*>(at + j * SW + v * CW);
+                        else *reinterpret_cast<double2*>(&seg[v * CW]) = *reinterpret_cast<const double2*>(at + j * SW + v * CW);
+                    }
+#pragma unroll
+                    for (int ky = 0; ky < KH; ky++) {
+                        const int i = j - ky;   // error row that meets image row j at tap row ky
+                        if (i >= 0 && i < RH) {
+#pragma unroll
+                            for (int kx = 0; kx < KW; kx++)
+#pragma unroll
+                                for (int x = 0; x < CW; x++) acc[ky][kx] = fma(seg[kx + x], ev[i][x], acc[ky][kx]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
         }
-        __syncthreads();
-        return;
     }
+    __syncthreads();
+    if (*abort_word) return;
 
     // ---- CTA reduction: lanes by shuffle (fixed tree), then the 8 warps in order ----------------------------------
+    if (warp < 8) {
 #pragma unroll
-    for (int a = 0; a < KH; a++)
+        for (int a = 0; a < KH; a++)
 #pragma unroll
-        for (int b = 0; b < KW; b++) {
-            T v = acc[a][b];
+            for (int b = 0; b < KW; b++) {
+                T v = acc[a][b];
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
-            if (lane == 0) red[warp * KH * KW + a * KW + b] = v;
-        }
+                for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
+                if (lane == 0) red[warp * KH * KW + a * KW + b] = v;
+            }
+    }
     __syncthreads();
     if (tid < KH * KW) {
         T total = 0;
@@ -222,7 +248,7 @@ int nk_launch_wgrad(nk_ctx* ctx, T* out, WgradPlan& p, const TmaImage& imgA, con
     if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_wgrad_kernel)");
     // as many CTAs as are resident at once (KH*KW accumulators per thread decide that), so that the grid is one wave
     int per_sm = 1;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nk_conv_wgrad_kernel<T, KH, KW>, 256, smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nk_conv_wgrad_kernel<T, KH, KW>, 288, smem);
     if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaOccupancyMaxActiveBlocksPerMultiprocessor(nk_conv_wgrad_kernel)");
     if (per_sm < 1) per_sm = 1;
     int64_t chunks = int64_t(ctx->prop.multiProcessorCount) * per_sm / p.NP;
@@ -241,7 +267,7 @@ int nk_launch_wgrad(nk_ctx* ctx, T* out, WgradPlan& p, const TmaImage& imgA, con
     st = nk_scratch(ctx, size_t(p.NP) * size_t(chunks) * KH * KW * sizeof(T), &scratch);
     if (st) return st;
     p.status = ctx->tma_status_dev;
-    nk_conv_wgrad_kernel<T, KH, KW><<<unsigned(p.NP * chunks), 256, smem, ctx->stream>>>(reinterpret_cast<T*>(scratch), p, mapA, mapE);
+    nk_conv_wgrad_kernel<T, KH, KW><<<unsigned(p.NP * chunks), 288, smem, ctx->stream>>>(reinterpret_cast<T*>(scratch), p, mapA, mapE);
     st = nk_after_launch(ctx, "nk_conv_wgrad_kernel");
     if (st) return st;
     const int64_t n = p.NP * KH * KW;
