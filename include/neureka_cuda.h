@@ -176,6 +176,23 @@ int nk_timer_end(nk_ctx* ctx, float* out_ms);            /* second event + synch
  * denominator for the FMA-bound kernels (F32 stencil, F64 convolution, double-evaluated activations). */
 int nk_measure_fma_peak(nk_ctx* ctx, int32_t dtype, double* out_tflops);
 
+/* ---- fused elementwise expressions, compiled at run time ----
+ * Counterpart of the kernels the reference generates for Device.optimizedOperationOf(Function, name)
+ * (src/main/java/neureka/devices/Device.java:216-241; model: backend/ocl/utility/CLFunctionCompiler.java:47-196), plus
+ * broadcasting, which the reference's compiler does not do. `expr` is one C expression of type T over x0 .. x5 built from
+ *   op_add(a,b) op_sub op_mul op_div op_mod op_pow      the six Operator ops, forward
+ *   f_<id>(a), df_<id>(a)                               the 23 functions of nk_fun and their derivatives (f_tanh, df_relu ...)
+ *   T(<number>)                                         a constant in the tensor's type
+ * e.g. "f_tanh(op_add(op_mul(x0,x1),x1))". Every operator rounds to the tensor's type and the scalar functions are the
+ * ones the separate kernels use, so the result equals the op-by-op evaluation bit for bit. Operand extents must equal the
+ * drain's or be 1 (broadcast). Needs libnvrtc.so.12 at run time (NK_ERR_UNSUPPORTED if absent); a malformed expression
+ * gives NK_ERR_BAD_ARG with the compiler's log in nk_last_error. */
+typedef struct nk_fused nk_fused;
+int nk_fused_compile(nk_ctx* ctx, int32_t dtype, int32_t n_inputs, const char* expr, nk_fused** out);
+int nk_fused_run(nk_ctx* ctx, nk_fused* f, int32_t rank, nk_buf* drn, const int32_t* cfg0,
+                 nk_buf* const* srcs, const int32_t* const* cfgs);
+int nk_fused_free(nk_fused* f);
+
 /* ---- ordering between contexts (no reference counterpart: OpenCLDevice owns a single in-order queue) ----
  * A second nk_ctx on the same device is a second stream. An event recorded on one context's stream can be waited
  * for by another's, e.g. to let copies of finished results run beside the next computation. Waiting for an event

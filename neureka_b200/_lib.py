@@ -67,6 +67,9 @@ SIGNATURES = {
     "nk_write": (C.c_int, [_vp, _vp, _vp, _i64, _i64, _i64]),
     "nk_read": (C.c_int, [_vp, _vp, _vp, _i64, _i64]),
     "nk_copy": (C.c_int, [_vp, _vp, _i64, _vp, _i64, _i64]),
+    "nk_fused_compile": (C.c_int, [_vp, _i32, _i32, C.c_char_p, C.POINTER(_vp)]),
+    "nk_fused_run": (C.c_int, [_vp, _vp, _i32, _vp, _cfg, C.POINTER(_vp), C.POINTER(_cfg)]),
+    "nk_fused_free": (C.c_int, [_vp]),
     "nk_event_create": (C.c_int, [_vp, C.POINTER(_vp)]),
     "nk_event_record": (C.c_int, [_vp, _vp]),
     "nk_stream_wait_event": (C.c_int, [_vp, _vp]),

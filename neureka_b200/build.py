@@ -39,6 +39,7 @@ SOURCES = [
     ("nk_conv_tiled_inst_f64_tma8.cu", []),
     ("nk_conv_wgrad_inst_f32.cu", []),
     ("nk_conv_wgrad_inst_f64.cu", []),
+    ("nk_fused.cu", ["-I", OBJDIR]),
     ("nk_probe.cu", []),
     ("nk_sum_static.cu", ["-fmad=false"]),
     ("nk_jrand.cpp", ["-Xcompiler", "-ffp-contract=off"]),
@@ -61,9 +62,36 @@ def _headers_mtime() -> float:
     return max(t, os.path.getmtime(os.path.abspath(__file__)))
 
 
+def _write_fused_prelude() -> None:
+    """The run-time compiled (NVRTC) fused kernels must use the very scalar functions the precompiled kernels use:
+    nk_scalarfun.cuh and the operator / function ids of the public header go into one C++ raw string literal that
+    nk_fused.cu includes. Rewritten only when its content changes, so that it does not force a rebuild."""
+    import re
+    with open(os.path.join(HERE, "..", "include", "neureka_cuda.h")) as f:
+        pub = f.read()
+    enums = []
+    for name in ("nk_op", "nk_fun"):
+        m = re.search(r"typedef enum \{[^}]*\} " + name + ";", pub, re.S)
+        if not m:
+            raise RuntimeError(f"enum {name} not found in include/neureka_cuda.h")
+        enums.append(re.sub(r"/\*.*?\*/", "", m.group(0), flags=re.S))
+    with open(os.path.join(CSRC, "nk_scalarfun.cuh")) as f:
+        body = "".join(line for line in f if not line.startswith("#include") and not line.startswith("#pragma once"))
+    text = 'R"NKPRE(\n' + "\n".join(enums) + "\n" + body + '\n)NKPRE"\n'
+    path = os.path.join(OBJDIR, "nk_fused_prelude.inc")
+    old = None
+    if os.path.exists(path):
+        with open(path) as f:
+            old = f.read()
+    if old != text:
+        with open(path, "w") as f:
+            f.write(text)
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(LIBDIR, exist_ok=True)
     os.makedirs(OBJDIR, exist_ok=True)
+    _write_fused_prelude()
     nvcc = _nvcc()
     hdr_t = _headers_mtime()
     jobs = []

@@ -285,8 +285,11 @@ class CudaDevice:
         return self
 
     def optimized_operation_of(self, function, name):
-        """Device.optimizedOperationOf (Device.java:216): no fused-expression compiler yet."""
-        raise NotImplementedError("CudaDevice does not compile fused operations yet")
+        """Device.optimizedOperationOf (Device.java:216-241): one run-time compiled kernel for a whole elementwise
+        Function (operators + - * / % **, the scalar functions, constants), operands broadcasting against each other.
+        Raises ValueError for functions that contain anything else (convolutions, sums)."""
+        from .functions import FusedOperation
+        return FusedOperation(self, function, name)
 
     # ---- misc ----------------------------------------------------------------------------------------
     def sync(self) -> None:

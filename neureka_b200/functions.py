@@ -18,6 +18,7 @@ There is no CPU execution in this package: a call needs at least one operand on 
 """
 from __future__ import annotations
 
+import ctypes as C
 import re
 from typing import List, Optional, Sequence, Tuple
 
@@ -295,6 +296,95 @@ def assign(dst: Tensor, src: Tensor) -> Tensor:
         return _execute_on_common_device(call, be.implementation_for(B.ASSIGN_LEFT, B.BI_SCALAR_BROADCAST))
     call = ExecutionCall([dst, src], B.ASSIGN_LEFT, dev, -1)
     return _execute_on_common_device(call, be.implementation_for(B.ASSIGN_LEFT, B.ELEMENTWISE))
+
+
+# ---------------------------------------------------------------------------------------------------
+# fused elementwise expressions (Device.optimizedOperationOf)
+# ---------------------------------------------------------------------------------------------------
+_FUSED_OPS = {"+": "op_add", "-": "op_sub", "*": "op_mul", "/": "op_div", "%": "op_mod", "**": "op_pow"}
+
+
+def fused_expression_of(root: Node) -> Tuple[str, int]:
+    """The expression string nk_fused_compile takes for an AST made of inputs, constants, the six elementwise
+    operators and the scalar functions, and the number of inputs it reads. n-ary chains nest to the left like the
+    reference's pairwise reduction (operator/Addition.java `reducePairwise`). Raises for nodes that are not
+    elementwise (convolutions, sumItems)."""
+    highest = [-1]
+
+    def walk(n: Node) -> str:
+        if n.kind == "input":
+            highest[0] = max(highest[0], int(n.value))
+            return f"x{int(n.value)}"
+        if n.kind == "const":
+            return f"T({float(n.value)!r})"
+        if n.kind == "fun":
+            if n.value not in L.FUN_IDS:
+                raise ValueError(f"'{n.value}' is not an elementwise function and cannot be fused")
+            return f"f_{n.value}({walk(n.children[0])})"
+        if n.kind == "op":
+            if n.value not in _FUSED_OPS:
+                raise ValueError(f"operator '{n.value}' is not elementwise and cannot be fused")
+            acc = walk(n.children[0])
+            for c in n.children[1:]:
+                acc = f"{_FUSED_OPS[n.value]}({acc}, {walk(c)})"
+            return acc
+        raise ValueError(f"cannot fuse node kind {n.kind}")
+
+    expr = walk(root)
+    if highest[0] < 0:
+        raise ValueError("a fused operation needs at least one input")
+    return expr, highest[0] + 1
+
+
+class FusedOperation:
+    """What CudaDevice.optimized_operation_of returns: one kernel for a whole elementwise Function, compiled per
+    item type on first use. Calling it allocates the (broadcast-shaped) output on the device and launches once."""
+
+    def __init__(self, device: CudaDevice, function: "Function", name: str):
+        self.device, self.function, self.name = device, function, name
+        self.expr, self.n_inputs = fused_expression_of(function.root)
+        self._handles = {}
+
+    def _handle(self, dt: int):
+        h = self._handles.get(dt)
+        if h is None:
+            h = C.c_void_p()
+            L.check(L.lib.nk_fused_compile(self.device.ctx, dt, self.n_inputs, self.expr.encode(), C.byref(h)), self.device.ctx)
+            self._handles[dt] = h
+        return h
+
+    def __call__(self, *inputs: Tensor) -> Tensor:
+        if len(inputs) != self.n_inputs:
+            raise ValueError(f"{self.name} takes {self.n_inputs} inputs, got {len(inputs)}")
+        dev = self.device
+        tensors = make_fit(list(inputs)) if len({t.rank for t in inputs}) > 1 else list(inputs)
+        rank = tensors[0].rank
+        shape = []
+        for k in range(rank):
+            ext = {t.shape[k] for t in tensors} - {1}
+            if len(ext) > 1:
+                raise ValueError(f"shapes {[t.shape for t in tensors]} cannot be broadcast")
+            shape.append(ext.pop() if ext else 1)
+        dt = B.nk_dtype(tensors[0].dtype)
+        for t in tensors:
+            if t.dtype != tensors[0].dtype:
+                raise ValueError("all tensors of a call must have the same item type")
+            t.set_is_virtual(False)
+            if not dev.has(t):
+                raise ValueError("every input of a fused operation must be stored on its device")
+        out = _new_output(tensors[0].dtype, tuple(shape), dev)
+        cfgs = [t.ndconf.as_inline_array() for t in tensors]
+        cfg_ptrs = (C.POINTER(C.c_int32) * len(tensors))(*[c.ctypes.data_as(C.POINTER(C.c_int32)) for c in cfgs])
+        bufs = (C.c_void_p * len(tensors))(*[t._data.buf for t in tensors])
+        c0 = out.ndconf.as_inline_array()
+        L.check(L.lib.nk_fused_run(dev.ctx, self._handle(dt), rank, out._data.buf, c0.ctypes.data_as(C.POINTER(C.c_int32)), bufs, cfg_ptrs), dev.ctx)
+        out.version += 1
+        return out
+
+    def close(self) -> None:
+        for h in self._handles.values():
+            L.lib.nk_fused_free(h)
+        self._handles.clear()
 
 
 # ---------------------------------------------------------------------------------------------------
