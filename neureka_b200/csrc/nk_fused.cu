@@ -31,9 +31,10 @@ struct FusedPlan {
     int vec;                      // elements per work item along the innermost dim (4 or 1)
     int n_in;
     int wide;                     // unit index needs 64 bits
-    long long units;              // outer rows * chunks per row
+    long long units;              // row groups * chunks per row
     long long chunks;             // work-item groups per row
     long long inner;              // innermost extent
+    long long rows;               // product of the outer extents
     long long ext[NK_MAX_RANK];
     long long s0[NK_MAX_RANK];
     long long s[NK_FUSED_MAX_IN][NK_MAX_RANK];
@@ -104,7 +105,7 @@ const char* const k_kernel_src = R"NKSRC(
 #define NK_FUSED_MAX_IN 6
 struct FusedPlan {
     int nd, vec, n_in, wide;
-    long long units, chunks, inner;
+    long long units, chunks, inner, rows;
     long long ext[NK_MAX_RANK];
     long long s0[NK_MAX_RANK];
     long long s[NK_FUSED_MAX_IN][NK_MAX_RANK];
@@ -134,57 +135,107 @@ NK_F(softsign, NK_FUN_SOFTSIGN) NK_F(sqrt, NK_FUN_SQRT) NK_F(tanh, NK_FUN_TANH) 
 
 __device__ __forceinline__ T nk_expr(T x0, T x1, T x2, T x3, T x4, T x5) { return NK_EXPR; }
 
-// A work unit is one chunk (256 threads x VEC elements) of one row of the merged index space: the row is decoded
-// once per unit (32-bit divisions unless the problem needs more), the chunk is contiguous in the drain.
+// A work unit is one chunk (256 threads x VEC elements) of a group of NK_ROWS consecutive rows of the merged index
+// space: the first row is decoded with divisions (32-bit unless the problem needs more), the others follow by counting
+// the row index up with carry; all loads of the group are issued before the first result is computed, so a thread
+// keeps NK_ROWS x NK_NIN 128-bit loads in flight.
+#define NK_ROWS 2
 template <int VEC, class IDX>
 __device__ __forceinline__ void nk_fused_body(const FusedArgs& a) {
     const FusedPlan& p = a.p;
     T* out = reinterpret_cast<T*>(a.out);
+    const int last = p.nd - 1;
     for (IDX unit = blockIdx.x; unit < IDX(p.units); unit += gridDim.x) {
-        IDX row = unit / IDX(p.chunks);
-        const long long col = (long long)(unit - row * IDX(p.chunks)) * (256 * VEC) + threadIdx.x * VEC;
+        const IDX grp = unit / IDX(p.chunks);
+        const long long col = (long long)(unit - grp * IDX(p.chunks)) * (256 * VEC) + threadIdx.x * VEC;
         if (col >= p.inner) continue;
-        long long o0 = p.b0 + col * p.s0[p.nd - 1];
-        long long oi[NK_FUSED_MAX_IN];
+        // ---- first row of the group: digits by division ----
+        long long idx[NK_MAX_RANK - 1];
+        long long o0 = p.b0 + col * p.s0[last];
+        long long oi[NK_NIN];
 #pragma unroll
-        for (int j = 0; j < NK_FUSED_MAX_IN; j++) oi[j] = j < p.n_in ? p.b[j] + col * p.s[j][p.nd - 1] : 0;
-        for (int k = p.nd - 2; k >= 0; k--) {
-            const IDX q = row / IDX(p.ext[k]);
-            const long long idx = (long long)(row - q * IDX(p.ext[k]));
-            row = q;
-            o0 += idx * p.s0[k];
+        for (int j = 0; j < NK_NIN; j++) oi[j] = p.b[j] + col * p.s[j][last];
+        {
+            IDX row = grp * NK_ROWS;
 #pragma unroll
-            for (int j = 0; j < NK_FUSED_MAX_IN; j++)
-                if (j < p.n_in) oi[j] += idx * p.s[j][k];
-        }
-        T x[NK_FUSED_MAX_IN][VEC];
+            for (int k = NK_MAX_RANK - 2; k >= 0; k--) {
+                if (k < last) {
+                    const IDX q = row / IDX(p.ext[k]);
+                    idx[k] = (long long)(row - q * IDX(p.ext[k]));
+                    row = q;
+                    o0 += idx[k] * p.s0[k];
 #pragma unroll
-        for (int j = 0; j < NK_FUSED_MAX_IN; j++) {
-            if (j < p.n_in) {
-                const T* src = reinterpret_cast<const T*>(a.in[j]) + oi[j];
-                if (VEC == 1) {
-                    x[j][0] = src[0];
-                } else if (p.s[j][p.nd - 1] == 0) {
-                    const T v = src[0];
-#pragma unroll
-                    for (int e = 0; e < VEC; e++) x[j][e] = v;
+                    for (int j = 0; j < NK_NIN; j++) oi[j] += idx[k] * p.s[j][k];
                 } else {
-                    *reinterpret_cast<V*>(x[j]) = *reinterpret_cast<const V*>(src);
+                    idx[k] = 0;
                 }
-            } else {
-#pragma unroll
-                for (int e = 0; e < VEC; e++) x[j][e] = T(0);
             }
         }
-        T r[VEC];
+        const long long rows_left = p.rows - (long long)grp * NK_ROWS;
+        long long ro[NK_ROWS], ri[NK_ROWS][NK_NIN];
 #pragma unroll
-        for (int e = 0; e < VEC; e++) r[e] = nk_expr(x[0][e], x[1][e], x[2][e], x[3][e], x[4][e], x[5][e]);
-        if (VEC == 1) out[o0] = r[0];
-        else *reinterpret_cast<V*>(out + o0) = *reinterpret_cast<V*>(r);
+        for (int r = 0; r < NK_ROWS; r++) {
+            ro[r] = o0;
+#pragma unroll
+            for (int j = 0; j < NK_NIN; j++) ri[r][j] = oi[j];
+            // next row: count up, innermost outer dim first
+            bool carry = true;
+#pragma unroll
+            for (int k = NK_MAX_RANK - 2; k >= 0; k--) {
+                if (k < last && carry) {
+                    idx[k]++;
+                    o0 += p.s0[k];
+#pragma unroll
+                    for (int j = 0; j < NK_NIN; j++) oi[j] += p.s[j][k];
+                    if (idx[k] < p.ext[k]) {
+                        carry = false;
+                    } else {
+                        idx[k] = 0;
+                        o0 -= p.ext[k] * p.s0[k];
+#pragma unroll
+                        for (int j = 0; j < NK_NIN; j++) oi[j] -= p.ext[k] * p.s[j][k];
+                    }
+                }
+            }
+        }
+        T x[NK_ROWS][NK_NIN][VEC];
+#pragma unroll
+        for (int r = 0; r < NK_ROWS; r++) {
+            if (r < rows_left) {
+#pragma unroll
+                for (int j = 0; j < NK_NIN; j++) {
+                    const T* src = reinterpret_cast<const T*>(a.in[j]) + ri[r][j];
+                    if (VEC == 1) {
+                        x[r][j][0] = src[0];
+                    } else if (p.s[j][last] == 0) {
+                        const T v = src[0];
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) x[r][j][e] = v;
+                    } else {
+                        *reinterpret_cast<V*>(x[r][j]) = *reinterpret_cast<const V*>(src);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < NK_ROWS; r++) {
+            if (r < rows_left) {
+                T res[VEC];
+#pragma unroll
+                for (int e = 0; e < VEC; e++) {
+                    T in[6];
+#pragma unroll
+                    for (int j = 0; j < 6; j++) in[j] = j < NK_NIN ? x[r][j < NK_NIN ? j : 0][e] : T(0);
+                    res[e] = nk_expr(in[0], in[1], in[2], in[3], in[4], in[5]);
+                }
+                if (VEC == 1) out[ro[r]] = res[0];
+                else *reinterpret_cast<V*>(out + ro[r]) = *reinterpret_cast<V*>(res);
+            }
+        }
     }
 }
 
-extern "C" __global__ void __launch_bounds__(256) nk_fused_kernel(const FusedArgs a) {
+extern "C" __global__ void __launch_bounds__(256, 4) nk_fused_kernel(const FusedArgs a) {
     if (a.p.vec > 1) {
         if (a.p.wide) nk_fused_body<VECW, long long>(a); else nk_fused_body<VECW, unsigned>(a);
     } else {
@@ -207,6 +258,7 @@ extern "C" int nk_fused_compile(nk_ctx* ctx, int32_t dtype, int32_t n_inputs, co
 
     std::string src;
     src += dtype == NK_F32 ? "typedef float T;\ntypedef float4 V;\n#define VECW 4\n" : "typedef double T;\ntypedef double2 V;\n#define VECW 2\n";
+    src += "#define NK_NIN " + std::to_string(n_inputs) + "\n";
     src += "#define NK_EXPR (";
     src += expr;
     src += ")\n";
@@ -302,6 +354,15 @@ extern "C" int nk_fused_run(nk_ctx* ctx, nk_fused* f, int32_t rank, nk_buf* drn,
     p.b0 = v0.base;
     a.out = drn->ptr;
     for (int j = 0; j < f->n_in; j++) { p.b[j] = v[j].base; a.in[j] = srcs[j]->ptr; }
+    // a fully linear problem is one long row: cut it into rows of 1024 so that a thread still has several loads in flight
+    if (nd == 1 && p.ext[0] >= 8192 && p.ext[0] % 1024 == 0) {
+        p.ext[1] = 1024; p.s0[1] = p.s0[0];
+        for (int j = 0; j < f->n_in; j++) p.s[j][1] = p.s[j][0];
+        p.ext[0] /= 1024; p.s0[0] *= 1024;
+        for (int j = 0; j < f->n_in; j++) p.s[j][0] *= 1024;
+        nd = 2;
+        p.nd = 2;
+    }
     p.inner = p.ext[nd - 1];
     // 128-bit accesses along the innermost dim when everything lines up
     const int es = int(nk_dtype_size(f->dtype)), W = 16 / es;
@@ -320,7 +381,8 @@ extern "C" int nk_fused_run(nk_ctx* ctx, nk_fused* f, int32_t rank, nk_buf* drn,
     p.chunks = (p.inner + per_chunk - 1) / per_chunk;
     int64_t rows = 1;
     for (int k = 0; k < nd - 1; k++) rows *= p.ext[k];
-    p.units = rows * p.chunks;
+    p.rows = rows;
+    p.units = ((rows + 1) / 2) * p.chunks;   // groups of NK_ROWS = 2 rows
     p.wide = p.units >= (int64_t(1) << 32) ? 1 : 0;
     if (p.units == 0) return NK_OK;
     const int64_t cap = int64_t(ctx->prop.multiProcessorCount) * 16;
