@@ -203,6 +203,11 @@ int nk_event_record(nk_ctx* ctx, nk_event* ev);          /* on ctx's stream, aft
 int nk_stream_wait_event(nk_ctx* ctx, nk_event* ev);     /* work queued on ctx's stream from now on waits for ev */
 int nk_event_free(nk_event* ev);
 
+/* Failure-path check (no reference counterpart): runs the bounded mbarrier wait of the pipelined kernels on a barrier
+ * that nothing completes, with the given limit (at most 1 s). The kernel returns by itself; the expired wait is then
+ * reported by the next nk_sync / nk_read as NK_ERR_TIMEOUT, exactly as for a convolution kernel. */
+int nk_probe_wait_timeout(nk_ctx* ctx, uint64_t limit_ns, uint64_t* out_waited_ns);
+
 /* ---- multi-GPU (no reference counterpart: the reference has no multi-device execution) ----
  * One process per GPU. A rank exports a buffer; peers open it and use it as the drain of nk_conv, so a
  * slab's results are stored straight into the owner's memory over NVLink (plain stores). */

@@ -70,6 +70,7 @@ SIGNATURES = {
     "nk_fused_compile": (C.c_int, [_vp, _i32, _i32, C.c_char_p, C.POINTER(_vp)]),
     "nk_fused_run": (C.c_int, [_vp, _vp, _i32, _vp, _cfg, C.POINTER(_vp), C.POINTER(_cfg)]),
     "nk_fused_free": (C.c_int, [_vp]),
+    "nk_probe_wait_timeout": (C.c_int, [_vp, C.c_uint64, C.POINTER(C.c_uint64)]),
     "nk_event_create": (C.c_int, [_vp, C.POINTER(_vp)]),
     "nk_event_record": (C.c_int, [_vp, _vp]),
     "nk_stream_wait_event": (C.c_int, [_vp, _vp]),

@@ -24,7 +24,7 @@
 #include "nk_conv_plan.h"
 
 #define NK_TILED_MAX_OUTER 6
-#define NK_TMA_SPIN_LIMIT (1u << 24)   // bounded mbarrier wait: ~ a second, then the kernel gives up and reports
+#define NK_WAIT_LIMIT_NS 2000000000ull   // bounded mbarrier wait: two seconds by the global timer, then the kernel gives up and reports
 
 struct TiledPlan {
     int n_outer;
@@ -88,6 +88,26 @@ __device__ __forceinline__ unsigned nk_mbar_try_wait(uint64_t* bar, unsigned par
     asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
                  : "=r"(ok) : "r"(a), "r"(parity) : "memory");
     return ok;
+}
+__device__ __forceinline__ unsigned long long nk_globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    return t;
+}
+// Waits for a phase of an mbarrier, but never longer than limit_ns (nor past a raised abort word, if one is given):
+// the first poll costs nothing extra; only a blocked waiter reads the timer, once per 64 polls.
+// Returns 1 = phase complete, 0 = somebody else aborted, -1 = this wait ran out.
+__device__ __forceinline__ int nk_mbar_wait_bounded(uint64_t* bar, unsigned parity, unsigned long long limit_ns, volatile int* abort_word) {
+    if (nk_mbar_try_wait(bar, parity)) return 1;
+    const unsigned long long t0 = nk_globaltimer_ns();
+    unsigned spins = 0;
+    while (!nk_mbar_try_wait(bar, parity)) {
+        if ((++spins & 63u) == 0) {
+            if (abort_word && *abort_word) return 0;
+            if (nk_globaltimer_ns() - t0 > limit_ns) return -1;
+        }
+    }
+    return 1;
 }
 __device__ __forceinline__ void nk_fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
 __device__ __forceinline__ void nk_fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
@@ -393,31 +413,42 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         // Every wait below is bounded; whoever runs out raises the CTA's abort word (and the host-visible status),
         // everybody else notices it while polling, and the CTA leaves without storing anything more.
         auto wait_or_abort = [&](uint64_t* bar, unsigned parity) -> bool {
-            unsigned spins = 0;
-            while (!nk_mbar_try_wait(bar, parity)) {
-                ++spins;
-                if ((spins & 1023u) == 0 && *abort_word) return false;
-                if (spins > NK_TMA_SPIN_LIMIT) {
-                    *abort_word = 1;
-                    if (p.status) atomicExch(p.status, 1);
-                    return false;
-                }
+            const int r = nk_mbar_wait_bounded(bar, parity, NK_WAIT_LIMIT_NS, abort_word);
+            if (r < 0) {
+                *abort_word = 1;
+                if (p.status) atomicExch(p.status, 1);
             }
-            return true;
+            return r > 0;
         };
         if (warp == 8) {
             if (lane == 0) {
                 // `issued` counts tile loads over the CTA's whole life: load g uses stage g % STAGES in round g / STAGES.
                 // A tile index is a mixed-radix number (tx | ty | outer output indices, last outer dim fastest); the
                 // walk adds gridDim.x to it digit by digit with carry -- a few adds and compares per tile, no division.
-                constexpr int NDIG = 2 + NK_TILED_MAX_OUTER;
-                int dg[NDIG], sg[NDIG], rx[NDIG];
+                // Everything the per-tile step needs sits in registers under compile-time indices (j counts the outer
+                // dims from the last one): the step is a few dozen instructions, the producer's time per tile bounds short tiles.
+                constexpr int NO = NK_TILED_MAX_OUTER, NDIG = 2 + NO;
+                int dg[NDIG], sg[NDIG], rx[NDIG], wmj[NO];
+                long long osj[NO];
+                bool foli[NO];
                 if (p.persist) {
                     int64_t t = tile_first, st = tile_step;
+#pragma unroll
                     for (int i = 0; i < NDIG; i++) {
                         rx[i] = i == 0 ? p.tilesX : i == 1 ? p.tilesY : ((i - 2) < p.n_outer ? int(p.oext[p.n_outer - 1 - (i - 2)]) : 1);
                         dg[i] = int(t % rx[i]); t /= rx[i];
                         sg[i] = int(st % rx[i]); st /= rx[i];
+                    }
+                    int wm = 1;
+#pragma unroll
+                    for (int j = 0; j < NO; j++) {
+                        const bool on = j < p.n_outer;
+                        const int k = on ? p.n_outer - 1 - j : 0;
+                        osj[j] = on ? p.os[k] : 0;
+                        foli[j] = on && p.pI[k] != 0;
+                        const bool moves_kernel = on && p.pK[k] != 0;
+                        wmj[j] = moves_kernel ? wm : 0;
+                        if (moves_kernel) wm *= int(p.oext[k]);
                     }
                 }
                 bool ok = true;
@@ -431,23 +462,24 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                         tile += tile_step;
                         if (!p.persist || tile >= p.tiles_total) break;
                         int carry = 0;
+#pragma unroll
                         for (int i = 0; i < NDIG; i++) {
                             const int v = dg[i] + sg[i] + carry;
                             carry = v >= rx[i] ? 1 : 0;
                             dg[i] = v - (carry ? rx[i] : 0);
                         }
                         baseO = p.bO;
-                        int ws = 0, wm = 1;
-                        for (int j = 0; j < p.n_outer; j++) {
-                            const int k = p.n_outer - 1 - j, idx = dg[2 + j];
-                            baseO += idx * p.os[k];
-                            pidx[k] = p.pI[k] != 0 ? idx : 0;
-                            if (p.pK[k] != 0) { ws += idx * wm; wm *= int(p.oext[k]); }
+                        int ws = 0, P[NO];
+#pragma unroll
+                        for (int j = 0; j < NO; j++) {
+                            baseO += dg[2 + j] * osj[j];
+                            P[j] = foli[j] ? dg[2 + j] : 0;
+                            ws += dg[2 + j] * wmj[j];
                         }
                         wset = p.wsets > 1 ? ws : 0;
                         x0 = dg[0] * TW - p.xoff;
                         y0 = dg[1] * TH;
-                        tb = tile_coords();
+                        tb = p.has_y ? make_int4(y0, P[0], P[1], P[2]) : make_int4(P[0], P[1], P[2], P[3]);
                         c = c_begin;
                         tile_no++;
                         announce = true;
@@ -471,9 +503,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                 if (!ok || *abort_word) {
                     // requested copies may still be landing in this CTA's shared memory: wait for the last ones (bounded)
                     for (int j = (issued > STAGES ? issued - STAGES : 0); j < issued; j++) {
-                        unsigned spins = 0;
-                        while (!nk_mbar_try_wait(&full_bar[j % STAGES], unsigned(j / STAGES) & 1u))
-                            if (++spins > NK_TMA_SPIN_LIMIT) break;
+                        nk_mbar_wait_bounded(&full_bar[j % STAGES], unsigned(j / STAGES) & 1u, NK_WAIT_LIMIT_NS, nullptr);
                     }
                 }
             }

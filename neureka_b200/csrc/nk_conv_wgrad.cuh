@@ -77,17 +77,12 @@ __global__ void __launch_bounds__(288) nk_conv_wgrad_kernel(T* __restrict__ part
     __syncthreads();
 
     auto wait_or_abort = [&](uint64_t* bar, unsigned parity) -> bool {
-        unsigned spins = 0;
-        while (!nk_mbar_try_wait(bar, parity)) {
-            ++spins;
-            if ((spins & 1023u) == 0 && *abort_word) return false;
-            if (spins > NK_TMA_SPIN_LIMIT) {
-                *abort_word = 1;
-                if (p.status) atomicExch(p.status, 1);
-                return false;
-            }
+        const int r = nk_mbar_wait_bounded(bar, parity, NK_WAIT_LIMIT_NS, abort_word);
+        if (r < 0) {
+            *abort_word = 1;
+            if (p.status) atomicExch(p.status, 1);
         }
-        return true;
+        return r > 0;
     };
 
     T acc[KH][KW];
@@ -140,9 +135,7 @@ __global__ void __launch_bounds__(288) nk_conv_wgrad_kernel(T* __restrict__ part
                 if (!ok || *abort_word) {
                     // requested copies may still be landing in this CTA's shared memory: wait for the last ones (bounded)
                     for (int64_t j = (issued > STAGES ? issued - STAGES : 0); j < issued; j++) {
-                        unsigned spins = 0;
-                        while (!nk_mbar_try_wait(&full_bar[j % STAGES], unsigned(j / STAGES) & 1u))
-                            if (++spins > NK_TMA_SPIN_LIMIT) break;
+                        nk_mbar_wait_bounded(&full_bar[j % STAGES], unsigned(j / STAGES) & 1u, NK_WAIT_LIMIT_NS, nullptr);
                     }
                 }
             }

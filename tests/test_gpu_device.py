@@ -147,3 +147,27 @@ def test_events_order_two_contexts_on_one_device(device):
         L.lib.nk_free(ctx_a, dst)
     finally:
         L.lib.nk_device_close(ctx_b)
+
+
+def test_bounded_wait_runs_out_and_is_reported(device):
+    """The pipelined kernels wait on mbarriers with a time limit. Here the same wait runs on a barrier nothing ever
+    completes, with a 20 ms limit: the kernel returns by itself, the next synchronising call reports NK_ERR_TIMEOUT
+    and the context stays usable."""
+    import ctypes as C
+    import numpy as np
+    from neureka_b200 import _lib as L
+
+    waited = C.c_uint64(0)
+    assert L.lib.nk_probe_wait_timeout(device.ctx, 20_000_000, C.byref(waited)) == L.NK_OK
+    assert 20_000_000 <= waited.value < 500_000_000, waited.value
+    assert L.lib.nk_sync(device.ctx) == L.NK_ERR_TIMEOUT
+    assert b"gave up waiting" in L.lib.nk_last_error(device.ctx)
+    assert L.lib.nk_sync(device.ctx) == L.NK_OK                      # reported once, then clear
+    buf = C.c_void_p()
+    L.check(L.lib.nk_alloc(device.ctx, L.NK_F32, 16, C.byref(buf)), device.ctx)
+    L.check(L.lib.nk_fill(device.ctx, buf, C.c_double(3.0), 0, 16), device.ctx)
+    out = np.empty(16, dtype=np.float32)
+    L.check(L.lib.nk_read(device.ctx, buf, out.ctypes.data_as(C.c_void_p), 0, 16), device.ctx)
+    assert np.all(out == 3.0)
+    L.lib.nk_free(device.ctx, buf)
+    assert L.lib.nk_probe_wait_timeout(device.ctx, 0, None) == L.NK_ERR_BAD_ARG
