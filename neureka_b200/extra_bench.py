@@ -256,14 +256,42 @@ def run_extra(dev, hbm_peak_gbs: float) -> dict:
     return out
 
 
+def run_small_broadcast(dev, hbm_peak_gbs: float) -> dict:
+    """The broadcast / elementwise / reduction kernels of config 3 on a case small enough for a multi-pass profiler
+    capture and still far larger than L2: a [1024,1,1024], b [1,512,1024] -> 2^29 outputs (2 GiB per tensor)."""
+    ctx = dev.ctx
+    n, m, kk = 1024, 512, 1024
+    N = n * m * kk
+    a = _Buf(dev, np.float32, n * kk, _rand(np.float32, n * kk, 0, 3, -2.0, 2.0))
+    b = _Buf(dev, np.float32, m * kk, _rand(np.float32, m * kk, 0, 4, -2.0, 2.0))
+    t1, t2 = _Buf(dev, np.float32, N), _Buf(dev, np.float32, N)
+    ga = _Buf(dev, np.float32, n * kk)
+    ca, pa = _cfg([n, 1, kk]); cb, pb = _cfg([1, m, kk]); co, po = _cfg([n, m, kk])
+    out = {}
+    for name, fn, nbytes in (
+            ("mul_broadcast", lambda i: L.lib.nk_broadcast(ctx, L.NK_OP_MUL, L.NK_F32, 3, t1.buf, po, a.buf, pa, b.buf, pb, -1), 4.0 * (N + n * kk + m * kk)),
+            ("add_broadcast", lambda i: L.lib.nk_broadcast(ctx, L.NK_OP_ADD, L.NK_F32, 3, t2.buf, po, t1.buf, po, b.buf, pb, -1), 4.0 * (2 * N + m * kk)),
+            ("relu", lambda i: L.lib.nk_unary(ctx, L.FUN["relu"], L.NK_F32, 3, t1.buf, po, t2.buf, po, -1), 8.0 * N),
+            ("grad_a_reduce", lambda i: L.lib.nk_broadcast(ctx, L.NK_OP_MUL_BOTH, L.NK_F32, 3, ga.buf, pa, b.buf, pb, t1.buf, po, 0), 4.0 * (N + n * kk + m * kk))):
+        ms = _time(dev, lambda i, fn=fn: L.check(fn(i), ctx), 2, 4)
+        out[name] = {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / hbm_peak_gbs, "kernel": dev.last_kernel()}
+    for bb in (a, b, t1, t2, ga): bb.free()
+    return out
+
+
 if __name__ == "__main__":
-    # python -m neureka_b200.extra_bench : the side measurements alone, as JSON (also the command ncu is pointed at)
+    # python -m neureka_b200.extra_bench : the side measurements alone, as JSON (also the command ncu is pointed at);
+    # --small-broadcast : only a 2 GiB case of the broadcast / elementwise / reduction kernels (for full-set captures)
     import json
     import os
+    import sys
     from .device import CudaDevice
     peak = 6558.7
     path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             peak = float(json.load(f)["hbm_gbs"])
-    print(json.dumps(run_extra(CudaDevice.get(0), peak), indent=1))
+    if "--small-broadcast" in sys.argv[1:]:
+        print(json.dumps(run_small_broadcast(CudaDevice.get(0), peak), indent=1))
+    else:
+        print(json.dumps(run_extra(CudaDevice.get(0), peak), indent=1))
