@@ -56,7 +56,9 @@ template <> struct GemmTile<double> { static constexpr int BM = 128, BN = 64, BK
 
 // 256 threads as 16 x 16; thread (ty, tx) owns rows {ty*TM/2 .. +TM/2} of each half of the tile's rows and columns
 // {tx*TN/2 .. +TN/2} of each half of its columns, so that the lanes of a quarter warp read consecutive 16-byte words.
-template <class T>
+// OFF: type the per-thread gather offsets are kept in -- 32 bits when both operands are smaller than 2^31 elements (half the
+// registers of the 64-bit form, which spilled inside the main loop).
+template <class T, class OFF>
 __global__ void __launch_bounds__(256, 2) nk_conv_gemm_kernel(T* __restrict__ out, const T* __restrict__ A, const T* __restrict__ B,
                                                            const int64_t* __restrict__ tab, GemmPlan p) {
     using C = GemmTile<T>;
@@ -81,27 +83,38 @@ __global__ void __launch_bounds__(256, 2) nk_conv_gemm_kernel(T* __restrict__ ou
     //                      B by (k = tid / BN + i * (256 / BN), n = tid % BN) -- n fastest, contiguous for row-major B
     const int ak = tid % BK, am = tid / BK;
     const int bn = tid % BN, bk = tid / BN;
-    int64_t a_off[LA], b_off;
-    bool a_ok[LA];
+    // rows / columns past the edge are clamped to the last valid one (their products land in accumulators that are
+    // never stored), so the panel loads need no per-element predicate; only the K tail is guarded
+    OFF a_off[LA], b_off;
 #pragma unroll
     for (int i = 0; i < LA; i++) {
-        const int64_t m = m0 + am + i * (256 / BK);
-        a_ok[i] = m < p.M;
-        a_off[i] = a_ok[i] ? p.bA + offA_m[m] : 0;
+        int64_t m = m0 + am + i * (256 / BK);
+        if (m >= p.M) m = p.M - 1;
+        a_off[i] = OFF(p.bA + offA_m[m]);
     }
-    const bool b_ok = n0 + bn < p.N;
-    b_off = b_ok ? p.bB + offB_n[n0 + bn] : 0;
+    {
+        int64_t n = n0 + bn;
+        if (n >= p.N) n = p.N - 1;
+        b_off = OFF(p.bB + offB_n[n]);
+    }
 
     T ra[LA], rb[LB];
     auto fetch = [&](int64_t k0) {
-        const int64_t ka = k0 + ak;
-        const int64_t oka = ka < p.K ? offA_k[ka] : -1;
+        if (k0 + BK <= p.K) {
+            const OFF oka = OFF(offA_k[k0 + ak]);
 #pragma unroll
-        for (int i = 0; i < LA; i++) ra[i] = (a_ok[i] && oka >= 0) ? A[a_off[i] + oka] : T(0);
+            for (int i = 0; i < LA; i++) ra[i] = A[a_off[i] + oka];
 #pragma unroll
-        for (int i = 0; i < LB; i++) {
-            const int64_t kb = k0 + bk + i * (256 / BN);
-            rb[i] = (b_ok && kb < p.K) ? B[b_off + offB_k[kb]] : T(0);
+            for (int i = 0; i < LB; i++) rb[i] = B[b_off + OFF(offB_k[k0 + bk + i * (256 / BN)])];
+        } else {
+            const int64_t ka = k0 + ak;
+#pragma unroll
+            for (int i = 0; i < LA; i++) ra[i] = ka < p.K ? A[a_off[i] + OFF(offA_k[ka])] : T(0);
+#pragma unroll
+            for (int i = 0; i < LB; i++) {
+                const int64_t kb = k0 + bk + i * (256 / BN);
+                rb[i] = kb < p.K ? B[b_off + OFF(offB_k[kb])] : T(0);
+            }
         }
     };
     auto stash = [&](int buf) {
@@ -157,7 +170,7 @@ __global__ void __launch_bounds__(256, 2) nk_conv_gemm_kernel(T* __restrict__ ou
 }
 
 template <class T>
-int launch_gemm(nk_ctx* ctx, T* out, const T* A, const T* B, const GemmPlan& p) {
+int launch_gemm(nk_ctx* ctx, T* out, const T* A, const T* B, const GemmPlan& p, bool narrow) {
     using C = GemmTile<T>;
     void* scratch = nullptr;
     const int64_t entries = 2 * (p.M + p.N + p.K);
@@ -169,7 +182,8 @@ int launch_gemm(nk_ctx* ctx, T* out, const T* A, const T* B, const GemmPlan& p) 
     if (st) return st;
     const int64_t tiles = ((p.M + C::BM - 1) / C::BM) * ((p.N + C::BN - 1) / C::BN);
     if (tiles > 0x7fffffffLL) return -1;
-    nk_conv_gemm_kernel<T><<<unsigned(tiles), 256, 0, ctx->stream>>>(out, A, B, tab, p);
+    if (narrow) nk_conv_gemm_kernel<T, unsigned><<<unsigned(tiles), 256, 0, ctx->stream>>>(out, A, B, tab, p);
+    else nk_conv_gemm_kernel<T, int64_t><<<unsigned(tiles), 256, 0, ctx->stream>>>(out, A, B, tab, p);
     return nk_after_launch(ctx, "nk_conv_gemm_kernel");
 }
 
@@ -210,8 +224,9 @@ int nk_conv_gemm_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_b
     if (double(p.M) * double(p.N) * double(p.K) < double(1 << 21)) return NK_OK;
     p.bA = v1.base; p.bB = v2.base; p.bO = v0.base;
     int st;
-    if (dtype == NK_F32) st = launch_gemm<float>(ctx, (float*)drn->ptr, (const float*)s1->ptr, (const float*)s2->ptr, p);
-    else st = launch_gemm<double>(ctx, (double*)drn->ptr, (const double*)s1->ptr, (const double*)s2->ptr, p);
+    const bool narrow = s1->n_elems < (int64_t(1) << 31) && s2->n_elems < (int64_t(1) << 31);   // every gather offset fits 32 bits
+    if (dtype == NK_F32) st = launch_gemm<float>(ctx, (float*)drn->ptr, (const float*)s1->ptr, (const float*)s2->ptr, p, narrow);
+    else st = launch_gemm<double>(ctx, (double*)drn->ptr, (const double*)s1->ptr, (const double*)s2->ptr, p, narrow);
     if (st == -1) return NK_OK;
     if (st) return st;
     *handled = true;

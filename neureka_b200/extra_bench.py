@@ -279,9 +279,25 @@ def run_small_broadcast(dev, hbm_peak_gbs: float) -> dict:
     return out
 
 
+def run_small_contraction(dev) -> dict:
+    """[4096,4096,1] x [1,4096,4096] in F32 alone (201 MB of operands and result): the command a profiler is pointed at."""
+    ctx = dev.ctx
+    n = 4096
+    rng = np.random.default_rng(5)
+    A = _Buf(dev, np.float32, n * n, rng.standard_normal(n * n).astype(np.float32))
+    B = _Buf(dev, np.float32, n * n, rng.standard_normal(n * n).astype(np.float32))
+    O = _Buf(dev, np.float32, n * n)
+    c1, p1 = _cfg([n, n, 1]); c2, p2 = _cfg([1, n, n]); c0, p0 = _cfg([n, 1, n])
+    ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F32, 3, O.buf, p0, A.buf, p1, B.buf, p2, -1), ctx), 2, 4)
+    out = {"ms": ms, "tflops": 2.0 * n * n * n / (ms * 1e-3) / 1e12, "kernel": dev.last_kernel()}
+    for bb in (A, B, O): bb.free()
+    return out
+
+
 if __name__ == "__main__":
     # python -m neureka_b200.extra_bench : the side measurements alone, as JSON (also the command ncu is pointed at);
     # --small-broadcast : only a 2 GiB case of the broadcast / elementwise / reduction kernels (for full-set captures)
+    # --small-contraction : only the 4096^3 F32 contraction
     import json
     import os
     import sys
@@ -291,7 +307,9 @@ if __name__ == "__main__":
     if os.path.exists(path):
         with open(path) as f:
             peak = float(json.load(f)["hbm_gbs"])
-    if "--small-broadcast" in sys.argv[1:]:
+    if "--small-contraction" in sys.argv[1:]:
+        print(json.dumps(run_small_contraction(CudaDevice.get(0)), indent=1))
+    elif "--small-broadcast" in sys.argv[1:]:
         print(json.dumps(run_small_broadcast(CudaDevice.get(0), peak), indent=1))
     else:
         print(json.dumps(run_extra(CudaDevice.get(0), peak), indent=1))
