@@ -165,13 +165,15 @@ class NDConfiguration:
         return NDConfiguration.of(tuple(new_shape), self.strides, imap, new_spread, new_offset)
 
     def reshaped(self, new_form: Sequence[int]) -> "NDConfiguration":
-        """AbstractNDC._simpleReshape (AbstractNDC.java:179-204): axis permutation / padding with size-1 axes
-        (negative entries of new_form). Only defined here for simple (non-sliced) configurations; the
-        reference wraps anything else in a SimpleReshapeView."""
-        rm = Layout.ROW_MAJOR.new_strides_for(self.shape)
-        simple = self.strides == rm and self.indices_map == rm and all(o == 0 for o in self.offset) and all(s == 1 for s in self.spread)
-        if not simple:
-            raise NotImplementedError("reshaping a sliced/permuted configuration needs SimpleReshapeView semantics")
+        """AbstractNDC._simpleReshape (AbstractNDC.java:182-204): axis permutation / padding with size-1 axes
+        (negative entries of new_form). For a configuration that is already sliced or permuted the reference wraps
+        the parent in a SimpleReshapeView (config/types/views/SimpleReshapeView.java:60-107), whose five vectors are
+        these same rearranged vectors and whose index resolution -- through the parent, with the indices put back in
+        the parent's order -- gives exactly sum_i (idx_i * spread_i + offset_i) * strides_i of the rearranged vectors;
+        so one construction serves both cases (every parent axis must appear in new_form, as the view demands)."""
+        used = sorted(f for f in new_form if f >= 0)
+        if used != list(range(self.rank)):
+            raise ValueError("a reshape may only permute the axes and pad with size-1 axes: every axis must appear exactly once")
         new_shape = tuple(abs(f) if f < 0 else self.shape[f] for f in new_form)
         lay = self.layout()
         new_strides = lay.rearrange(self.strides, new_shape, new_form)

@@ -227,3 +227,30 @@ def test_large_broadcast_rows_kernel(device, oracle):
     assert device.last_kernel() == "nk_ew_rows_kernel"
     want = (a.reshape(64, 1, 1024) * b.reshape(1, 48, 1024)).reshape(-1)
     assert np.array_equal(got, want)
+
+
+def test_permuted_slices_as_operands(device, oracle):
+    """A permuted view of a strided slice (the reference's SimpleReshapeView) as operand of a broadcast, an activation
+    and a convolution: the kernels only see its inline array, the oracle resolves the same array on the CPU."""
+    from neureka_b200.tensor import Tensor
+    from neureka_b200.functions import Function
+    rng = np.random.default_rng(77)
+    parent = Tensor.of(np.float32, [10, 12, 9], rng.uniform(-2, 2, 10 * 12 * 9).astype(np.float32)).to(device)
+    view = parent[1:9:2, 2:12:2, 0:8].permute(2, 0, 1)          # [8, 4, 5]
+    assert view.shape == (8, 4, 5)
+    host = parent.numpy()[1:9:2, 2:12:2, 0:8].transpose(2, 0, 1)
+    assert np.array_equal(view.numpy(), host)
+    other = Tensor.of(np.float32, [8, 1, 5], rng.uniform(-2, 2, 40).astype(np.float32)).to(device)
+    got = Function.of("tanh(i0 * i1) + i0", False)(view, other)
+    h64 = host.astype(np.float32)
+    t = (h64 * other.numpy()).astype(np.float32)
+    want = np.array([oracle.fun32("tanh", float(v)) for v in t.reshape(-1)], dtype=np.float32).reshape(t.shape) + h64
+    assert np.abs(got.numpy() - want).max() <= 2 * np.finfo(np.float32).eps * np.abs(want).max()
+    k = Tensor.of(np.float32, [1, 3, 3], rng.standard_normal(9).astype(np.float32)).to(device)
+    y = Function.of("i0 x i1", False)(view, k)
+    ref = np.zeros((8, 2, 3), dtype=np.float32)
+    for c in range(8):
+        for i in range(2):
+            for j in range(3):
+                ref[c, i, j] = np.sum(host[c, i:i + 3, j:j + 3].astype(np.float64) * k.numpy()[0].astype(np.float64))
+    assert np.abs(y.numpy() - ref).max() <= 1e-5 * np.abs(ref).max() * 4

@@ -107,3 +107,30 @@ def test_no_cpu_fallback():
     a = Tensor.of(np.float32, [2, 2], [1, 2, 3, 4])
     with pytest.raises(L.NeurekaCudaError):
         Function.of("i0 x i1")(a, a)
+
+
+def test_reshaping_a_sliced_configuration_resolves_like_a_view_of_its_parent():
+    """SimpleReshapeView (config/types/views/SimpleReshapeView.java:96-107) resolves an index by putting the indices
+    back into the parent's axis order and asking the parent; its inline array holds the parent's vectors rearranged
+    (AbstractNDC.java:182-204). Both descriptions must name the same element for every index -- enumerated here for
+    permutations and size-1 paddings of a strided slice."""
+    import itertools
+    from neureka_b200.ndconf import NDConfiguration as ND
+
+    sl = ND.of_shape([5, 6, 7]).sliced([3, 2, 4], [1, 2, 0], [1, 2, 1])
+    for form in ([2, 0, 1], [1, 0, 2], [0, 2, 1], [2, 1, 0], [-1, 2, 0, 1], [1, -1, 0, 2]):
+        v = sl.reshaped(form)
+        through_parent = []
+        for idx in itertools.product(*[range(s) for s in v.shape]):
+            inner = [0] * sl.rank
+            for i, f in enumerate(form):
+                if f >= 0:
+                    inner[f] = idx[i]
+            through_parent.append(sum((inner[k] * sl.spread[k] + sl.offset[k]) * sl.strides[k] for k in range(sl.rank)))
+        assert list(v.element_offsets()) == through_parent, form
+        arr = v.as_inline_array()
+        r = v.rank
+        assert list(arr[:r]) == list(v.shape) and list(arr[r:2 * r]) == list(v.strides)
+    import pytest
+    with pytest.raises(ValueError):
+        sl.reshaped([0, 0, 1])
