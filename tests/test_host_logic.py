@@ -134,3 +134,20 @@ def test_reshaping_a_sliced_configuration_resolves_like_a_view_of_its_parent():
     import pytest
     with pytest.raises(ValueError):
         sl.reshaped([0, 0, 1])
+
+
+def test_fused_expression_translation():
+    """Function tree -> the expression language of nk_fused_compile: n-ary chains nest to the left like the
+    reference's pairwise reduction, unary minus is a multiplication by -1 (FunctionParser), constants are cast to the
+    tensor's type, anything that is not elementwise is refused."""
+    import pytest
+    from neureka_b200.functions import Function, fused_expression_of
+
+    assert fused_expression_of(Function.of("tanh(i0*i1+i1)").root) == ("f_tanh(op_add(op_mul(x0, x1), x1))", 2)
+    assert fused_expression_of(Function.of("i0 - i1 - i2").root) == ("op_sub(op_sub(x0, x1), x2)", 3)
+    assert fused_expression_of(Function.of("-i0").root) == ("op_mul(T(-1.0), x0)", 1)
+    assert fused_expression_of(Function.of("relu(i2) ** 2 % 3").root)[1] == 3          # highest input index + 1
+    assert "op_pow(op_pow(" not in fused_expression_of(Function.of("i0 ** 2 / i1").root)[0]
+    for bad in ("i0 x i1", "sumItems(i0)", "3 + 4"):
+        with pytest.raises(ValueError):
+            fused_expression_of(Function.of(bad).root)
