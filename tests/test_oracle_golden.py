@@ -1,5 +1,5 @@
 """Pins the CPU oracle (oracle/oracle.cpp) against the known-answer vectors transcribed from the reference's
-own tests (tests/golden/reference_kat.json): only an oracle that reproduces them may judge the CUDA path."""
+own tests (tests/golden/reference_kat.json): only an oracle that reproduces them may be used to check the CUDA path."""
 import numpy as np
 import pytest
 
