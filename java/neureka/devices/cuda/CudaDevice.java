@@ -123,8 +123,27 @@ public final class CudaDevice extends AbstractDevice<Number>
     @Override public int numberOfStored() { return _tensors.size(); }
     @Override public boolean isEmpty() { return _tensors.isEmpty(); }
     @Override public Collection<Tensor<Number>> getTensors() { return _tensors; }
+    /**
+     *  Device.optimizedOperationOf (Device.java:216-241; model: CLFunctionCompiler.java:47-196): the Function tree is
+     *  turned into the expression language of nk_fused_compile and wrapped into an Operation whose execution is a
+     *  single nk_fused_run. Operands may broadcast, which the OpenCL compiler of the reference does not support.
+     */
     @Override public Operation optimizedOperationOf( Function function, String name ) {
-        throw new IllegalStateException("CudaDevice does not compile fused operations yet");
+        final String expr = CudaKernels.fusedExpressionOf( function );
+        final int arity = function.numberOfArgs();
+        return Operation.builder()
+                .identifier( name ).operator( name ).arity( arity )
+                .isOperator( false ).isIndexer( false ).isDifferentiable( false ).isInline( false )
+                .stringifier( children -> name + "(" + String.join(", ", children) + ")" )
+                .build()
+                .setAlgorithm(
+                    neureka.backend.api.template.algorithms.FunDeviceAlgorithm.withName("generic_algorithm_for_" + name)
+                        .setIsSuitableFor( call -> neureka.backend.api.fun.SuitabilityPredicate.GOOD )
+                        .setAutogradModeFor( call -> neureka.backend.api.AutoDiffMode.NOT_SUPPORTED )
+                        .setExecution( (outerCaller, outerCall) -> neureka.backend.api.Result.of(
+                            CudaKernels.runFused( this, expr, arity, outerCall ) ) )
+                        .buildFunAlgorithm()
+                );
     }
     @Override public void dispose() {
         _tensors.clear();

@@ -5,6 +5,7 @@ import neureka.backend.api.ExecutionCall;
 
 import java.lang.foreign.Arena;
 import java.lang.foreign.MemorySegment;
+import java.lang.foreign.ValueLayout;
 import java.util.Arrays;
 import java.util.List;
 
@@ -89,6 +90,60 @@ public final class CudaKernels
         try ( Arena a = Arena.ofConfined() ) {
             NeurekaCuda.check((int) NeurekaCuda.SUM.invokeExact(dev.ctx, CudaDevice.typeOf(in.getItemType()), in.rank(),
                     dev.bufOf(in), cfg(a, in), dev.bufOf(out), 0L), dev.ctx);
+        } catch ( RuntimeException e ) { throw e; } catch ( Throwable t ) { throw new IllegalStateException(t); }
+        return out;
+    }
+
+    // ---- fused elementwise expressions (nk_fused_*) ----------------------------------------------------------------------
+
+    private static final java.util.Map<String, MemorySegment> FUSED = new java.util.concurrent.ConcurrentHashMap<>();
+
+    /** Function tree -> "f_tanh(op_add(op_mul(x0,x1),x1))"; n-ary chains nest to the left like reducePairwise. */
+    static String fusedExpressionOf( neureka.math.Function f ) {
+        if ( f instanceof neureka.math.implementations.FunctionInput ) return "x" + ((neureka.math.implementations.FunctionInput) f).index();
+        if ( f instanceof neureka.math.implementations.FunctionConstant ) return "T(" + ((neureka.math.implementations.FunctionConstant) f).value() + ")";
+        String id = f.getOperation().getIdentifier();
+        java.util.List<neureka.math.Function> subs = f.getSubFunctions();
+        String op = switch ( id ) {
+            case "add" -> "op_add"; case "subtract" -> "op_sub"; case "multiply" -> "op_mul";
+            case "divide" -> "op_div"; case "modulo" -> "op_mod"; case "power" -> "op_pow";
+            default -> null;
+        };
+        if ( op != null ) {
+            String acc = fusedExpressionOf( subs.get(0) );
+            for ( int i = 1; i < subs.size(); i++ ) acc = op + "(" + acc + ", " + fusedExpressionOf( subs.get(i) ) + ")";
+            return acc;
+        }
+        if ( subs.size() == 1 && f.getOperation() instanceof neureka.backend.main.operations.functions.AbstractActivationOperation )
+            return "f_" + id + "(" + fusedExpressionOf( subs.get(0) ) + ")";
+        throw new IllegalArgumentException("Operation '" + id + "' is not elementwise and cannot be fused");
+    }
+
+    /** Allocates the broadcast-shaped output on the device and launches the compiled kernel once. */
+    static Tensor<?> runFused( CudaDevice dev, String expr, int arity, ExecutionCall<?> call ) {
+        Tensor<?>[] in = call.inputs();
+        int rank = in[0].rank();
+        int[] shape = new int[rank];
+        for ( int k = 0; k < rank; k++ ) { shape[k] = 1; for ( Tensor<?> t : in ) if ( t.shape(k) != 1 ) shape[k] = t.shape(k); }
+        Tensor<?> out = Tensor.of( in[0].getItemType(), neureka.Shape.of(shape), 0 ).mut().setIsIntermediate(true);
+        out.mut().setIsVirtual(false);
+        dev.store( (Tensor) out );
+        int type = CudaDevice.typeOf( in[0].getItemType() );
+        try ( Arena a = Arena.ofConfined() ) {
+            MemorySegment handle = FUSED.computeIfAbsent( type + ":" + arity + ":" + expr, key -> {
+                try ( Arena b = Arena.ofConfined() ) {
+                    MemorySegment slot = b.allocate(ValueLayout.ADDRESS);
+                    NeurekaCuda.check((int) NeurekaCuda.FUSED_COMPILE.invokeExact(dev.ctx, type, arity, b.allocateFrom(expr), slot), dev.ctx);
+                    return slot.get(ValueLayout.ADDRESS, 0);
+                } catch ( RuntimeException e ) { throw e; } catch ( Throwable t ) { throw new IllegalStateException(t); }
+            });
+            MemorySegment bufs = a.allocate(ValueLayout.ADDRESS, arity), cfgs = a.allocate(ValueLayout.ADDRESS, arity);
+            for ( int j = 0; j < arity; j++ ) {
+                bufs.setAtIndex(ValueLayout.ADDRESS, j, dev.bufOf(in[j]));
+                cfgs.setAtIndex(ValueLayout.ADDRESS, j, NeurekaCuda.cfg(a, in[j].getNDConf().asInlineArray()));
+            }
+            NeurekaCuda.check((int) NeurekaCuda.FUSED_RUN.invokeExact(dev.ctx, handle, rank, dev.bufOf(out),
+                    NeurekaCuda.cfg(a, out.getNDConf().asInlineArray()), bufs, cfgs), dev.ctx);
         } catch ( RuntimeException e ) { throw e; } catch ( Throwable t ) { throw new IllegalStateException(t); }
         return out;
     }
