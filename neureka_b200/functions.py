@@ -386,6 +386,12 @@ class FusedOperation:
             L.lib.nk_fused_free(h)
         self._handles.clear()
 
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:   # interpreter shutdown: the library may already be gone
+            pass
+
 
 # ---------------------------------------------------------------------------------------------------
 # Function
