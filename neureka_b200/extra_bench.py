@@ -209,6 +209,24 @@ def run_extra(dev, hbm_peak_gbs: float) -> dict:
     except Exception as e:
         out["contraction_MxKx1_x_1xKxN"] = {"error": repr(e)}
 
+    # ---- cfg5's forward pass on the slabs a rank holds at 4 and 8 GPUs (what bounds the multi-GPU rows) ---------------------
+    try:
+        r = {}
+        for name, rows in (("one_of_8_ranks_260_rows", 260), ("one_of_4_ranks_515_rows", 515)):
+            Bn, Cn, W, KH = 8, 32, 2048, 5
+            img = _Buf(dev, np.float32, Bn * Cn * rows * W)
+            L.check(L.lib.nk_fill(ctx, img.buf, C.c_double(0.5), 0, Bn * Cn * rows * W), ctx)
+            ker = _Buf(dev, np.float32, Cn * KH * KH, _rand(np.float32, Cn * KH * KH, 1, 6, 0.0, 0.2))
+            o = _Buf(dev, np.float32, Bn * (rows - 4) * (W - 4))
+            ci, pi_ = _cfg([Bn, Cn, rows, W]); ckk, pkk = _cfg([1, Cn, KH, KH]); co_, po_ = _cfg([Bn, 1, rows - 4, W - 4])
+            ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, o.buf, po_, img.buf, pi_, ker.buf, pkk, -1), ctx), 3, 20)
+            flops = 2.0 * Bn * (rows - 4) * (W - 4) * Cn * KH * KH
+            r[name] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "kernel": dev.last_kernel()}
+            for bb in (img, ker, o): bb.free()
+        out["cfg5_forward_on_one_rank_slab"] = r
+    except Exception as e:
+        out["cfg5_forward_on_one_rank_slab"] = {"error": repr(e)}
+
     # ---- gradients of cfg5's convolution (error seeded, uniform [-1,1]) ---------------------------------------------------
     try:
         Bn, Cn, H, W, KH = 8, 32, 2048, 2048, 5
