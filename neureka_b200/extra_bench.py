@@ -297,6 +297,28 @@ def run_small_broadcast(dev, hbm_peak_gbs: float) -> dict:
     return out
 
 
+def run_small_gradients(dev, hbm_peak_gbs: float) -> dict:
+    """Both gradients of an [8,32,512,2048] x [1,32,5,5] convolution (1 GiB image): the profiler-sized case of the
+    config 5 gradient kernels."""
+    ctx = dev.ctx
+    Bn, Cn, H, W, KH = 8, 32, 512, 2048, 5
+    OH, OW = H - KH + 1, W - KH + 1
+    img = _Buf(dev, np.float32, Bn * Cn * H * W)
+    L.check(L.lib.nk_fill(ctx, img.buf, C.c_double(0.5), 0, Bn * Cn * H * W), ctx)
+    err = _Buf(dev, np.float32, Bn * OH * OW, _rand(np.float32, Bn * OH * OW, 0, 9, -1.0, 1.0))
+    ker = _Buf(dev, np.float32, Cn * KH * KH, _rand(np.float32, Cn * KH * KH, 1, 6, 0.0, 0.2))
+    gimg, gker = _Buf(dev, np.float32, Bn * Cn * H * W), _Buf(dev, np.float32, Cn * KH * KH)
+    ci, pi_ = _cfg([Bn, Cn, H, W]); ce, pe = _cfg([Bn, 1, OH, OW]); ckk, pkk = _cfg([1, Cn, KH, KH])
+    nbytes = 4.0 * (Bn * Cn * H * W + Bn * OH * OW + Cn * KH * KH)
+    out = {}
+    ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, gimg.buf, pi_, ker.buf, pkk, err.buf, pe, 0), ctx), 2, 4)
+    out["grad_image"] = {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / hbm_peak_gbs, "kernel": dev.last_kernel()}
+    ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, gker.buf, pkk, img.buf, pi_, err.buf, pe, 0), ctx), 2, 4)
+    out["grad_kernel"] = {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / hbm_peak_gbs, "kernel": dev.last_kernel()}
+    for bb in (img, err, ker, gimg, gker): bb.free()
+    return out
+
+
 def run_small_contraction(dev) -> dict:
     """[4096,4096,1] x [1,4096,4096] in F32 alone (201 MB of operands and result): the command a profiler is pointed at."""
     ctx = dev.ctx
@@ -316,6 +338,7 @@ if __name__ == "__main__":
     # python -m neureka_b200.extra_bench : the side measurements alone, as JSON (also the command ncu is pointed at);
     # --small-broadcast : only a 2 GiB case of the broadcast / elementwise / reduction kernels (for full-set captures)
     # --small-contraction : only the 4096^3 F32 contraction
+    # --small-gradients : only the two gradients of a quarter-height config 5 convolution
     import json
     import os
     import sys
@@ -325,7 +348,9 @@ if __name__ == "__main__":
     if os.path.exists(path):
         with open(path) as f:
             peak = float(json.load(f)["hbm_gbs"])
-    if "--small-contraction" in sys.argv[1:]:
+    if "--small-gradients" in sys.argv[1:]:
+        print(json.dumps(run_small_gradients(CudaDevice.get(0), peak), indent=1))
+    elif "--small-contraction" in sys.argv[1:]:
         print(json.dumps(run_small_contraction(CudaDevice.get(0)), indent=1))
     elif "--small-broadcast" in sys.argv[1:]:
         print(json.dumps(run_small_broadcast(CudaDevice.get(0), peak), indent=1))
