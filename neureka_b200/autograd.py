@@ -103,6 +103,19 @@ def _record_operator(sym: str, a: Tensor, b: Tensor, out: Tensor) -> None:
         out.graph_node = GraphNode(out, parents)
 
 
+def _record_matmul(a: Tensor, b: Tensor, out: Tensor) -> None:
+    """MatMulAlgorithm's ADAction (algorithms/MatMulAlgorithm.java:37-59): the gradient of the first operand is
+    error @ transpose(second), of the second transpose(first) @ error. The reference deep-copies the transposed
+    operand to get a simple configuration; the kernels here read the transposed view directly."""
+    parents = []
+    if _tracks(a):
+        parents.append((a, lambda err, b=b: F.run_matmul(err, b.T)))
+    if _tracks(b):
+        parents.append((b, lambda err, a=a: F.run_matmul(a.T, err)))
+    if parents:
+        out.graph_node = GraphNode(out, parents)
+
+
 def _reshape_like(g: Tensor, like: Tensor) -> Tensor:
     return g
 
@@ -149,6 +162,13 @@ def evaluate(node, inputs: List[Tensor], do_ad: bool) -> Tensor:
             raise ValueError(f"'{sym}' needs exactly three operands")
         return F.run_xconv(sym, *vals)
     acc = vals[0]
+    if sym == "@":
+        for nxt in vals[1:]:   # ((a @ b) @ c) ..., MatMul.reducePairwise (linear/MatMul.java:48-63)
+            out = F.run_matmul(acc, nxt)
+            if do_ad:
+                _record_matmul(acc, nxt, out)
+            acc = out
+        return acc
     for nxt in vals[1:]:   # pairwise, left nested
         out = F.run_conv(acc, nxt) if sym == "x" else F.run_operator(sym, acc, nxt)
         if do_ad:

@@ -33,7 +33,7 @@ from .tensor import Tensor
 # ---------------------------------------------------------------------------------------------------
 # AST + parser
 # ---------------------------------------------------------------------------------------------------
-_PRECEDENCE = ["**", "/", "*", "%", "-", "+", "x", "«x", "x»"]  # tightest first
+_PRECEDENCE = ["**", "/", "*", "%", "-", "+", "x", "«x", "x»", "@"]  # tightest first
 _FUN_ALIASES = {name: name for name in L.FUN_IDS}   # the operation identifiers are the ScalarFun ids
 _FUN_ALIASES["sumItems"] = "sumItems"
 
@@ -59,7 +59,7 @@ class Node:
         return "(" + f" {self.value} ".join(str(c) for c in self.children) + ")"
 
 
-_TOKEN = re.compile(r"\s*(?:(?P<num>\d+\.\d*|\.\d+|\d+)|(?P<inp>[iI]\[?\s*(?P<idx>\d+)\s*\]?)|(?P<op>\*\*|<<x|x>>|«x|x»|[-+*/%x()])|(?P<name>[A-Za-z_][A-Za-z_0-9]*))")
+_TOKEN = re.compile(r"\s*(?:(?P<num>\d+\.\d*|\.\d+|\d+)|(?P<inp>[iI]\[?\s*(?P<idx>\d+)\s*\]?)|(?P<op>\*\*|<<x|x>>|«x|x»|[-+*/%x()@])|(?P<name>[A-Za-z_][A-Za-z_0-9]*))")
 
 
 def _tokenize(expr: str):
@@ -236,6 +236,36 @@ def run_xconv(op: str, i0: Tensor, i1: Tensor, i2: Tensor) -> Tensor:
     if op == "x»":
         call.rearrange_inputs(2, 1, 0)
     return _execute_on_common_device(call, B.backend().implementation_for(op, B.ND_CONVOLUTION))
+
+
+def run_matmul(a: Tensor, b: Tensor) -> Tensor:
+    """Operation "@" (linear/MatMul.java:15-40, algorithms/MatMulAlgorithm.java:62-84): [M,K] @ [K,N] -> [M,N], output
+    allocated zero-filled in the operands' type. On this backend a matrix product is a convolution in which every
+    dim is summed away or spanned by one operand only -- a [M,K,1] x [1,K,N] -> [M,1,N] -- so the call is handed to the
+    convolution implementation on views that pad the three matrices with a size-1 axis (no copy; transposed and
+    sliced operands included), where large problems take the register-tiled contraction kernel."""
+    dev = _common_device([a, b])
+    if a.rank != 2 or b.rank != 2:
+        raise ValueError("matrix multiplication needs two rank-2 tensors")
+    if a.shape[1] != b.shape[0]:
+        raise ValueError(f"shapes {a.shape} and {b.shape} cannot be matrix-multiplied")
+    if a.dtype != b.dtype:
+        raise ValueError("all tensors of a call must have the same item type")
+    moved = []
+    for t in (a, b):
+        t.set_is_virtual(False)
+        if not dev.has(t):
+            dev.store(t)
+            moved.append(t)
+    out = _new_output(a.dtype, (a.shape[0], b.shape[1]), dev)
+    call = ExecutionCall([out.permute(0, -1, 1), a.permute(0, 1, -1), b.permute(-1, 0, 1)], "x", dev, -1)
+    dev.approve(call)
+    B.backend().implementation_for("x", B.ND_CONVOLUTION).run(call)
+    out.version += 1
+    for t in moved:
+        if not t.is_intermediate:
+            dev.restore(t)
+    return out
 
 
 def choose_algorithm(a: Tensor, b: Tensor) -> str:

@@ -258,6 +258,11 @@ class Tensor:
     def __mod__(self, o): return self._fn().Function.of("I[0] % I[1]").call(self, self._fn().as_tensor(o, self))
     def __pow__(self, o): return self._fn().Function.of("I[0] ** I[1]").call(self, self._fn().as_tensor(o, self))
 
+    def matmul(self, other):
+        return self._fn().Function.of("I[0] @ I[1]").call(self, other)
+
+    __matmul__ = matmul
+
     def sum(self):
         return self._fn().Function.of("sumItems(I[0])").call(self)
 

@@ -126,3 +126,35 @@ def test_scaled_config3_forward_and_reduced_gradients(device, oracle):
     db = (g3 * (a_h.reshape(n, 1, k).astype(np.float64) + 1)).sum(axis=0)
     np.testing.assert_allclose(a.gradient.items.reshape(n, k), da, rtol=1e-5, atol=1e-5)
     np.testing.assert_allclose(b.gradient.items.reshape(m, k), db, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("mkn", [(3, 4, 2), (70, 130, 50), (256, 192, 160)])
+def test_matmul_operator_forward_and_backward(device, dt, mkn):
+    """`@` (linear/MatMul.java, algorithms/MatMulAlgorithm.java:37-59) on the convolution kernels: forward against numpy in
+    float64, the gradients of sum(a @ b * w) against their closed forms; the largest case takes the contraction kernel."""
+    m, k, n = mkn
+    rng = np.random.default_rng(m * 1000 + n)
+    a_h, b_h, w_h = rng.standard_normal((m, k)), rng.standard_normal((k, n)), rng.standard_normal((m, n))
+    a = Tensor.of(dt, [m, k], a_h).set_rqs_gradient(True).to(device)
+    b = Tensor.of(dt, [k, n], b_h).set_rqs_gradient(True).to(device)
+    c = Function.of("i0 @ i1")(a, b)
+    tol = (1e-5 if dt == np.float32 else 1e-12) * k * 4
+    ref = a_h.astype(dt).astype(np.float64) @ b_h.astype(dt).astype(np.float64)
+    assert c.shape == (m, n)
+    assert np.abs(c.numpy() - ref).max() <= tol * max(1.0, np.abs(ref).max()) / k
+    if m * k * n >= (1 << 21):
+        from neureka_b200 import _lib as L
+        assert device.last_conv_path() == L.NK_CONV_GEMM
+    c.backward(Tensor.of(dt, [m, n], w_h))
+    ga = w_h.astype(dt).astype(np.float64) @ b_h.astype(dt).astype(np.float64).T
+    gb = a_h.astype(dt).astype(np.float64).T @ w_h.astype(dt).astype(np.float64)
+    assert np.abs(a.gradient.numpy() - ga).max() <= tol * max(1.0, np.abs(ga).max())
+    assert np.abs(b.gradient.numpy() - gb).max() <= tol * max(1.0, np.abs(gb).max())
+    # the operator form and a transposed view as operand
+    c2 = a @ b
+    assert np.array_equal(c2.numpy(), c.numpy())
+    c3 = Function.of("i0 @ i1", False)(b.T, a.T)
+    assert np.abs(c3.numpy() - ref.T).max() <= tol * max(1.0, np.abs(ref).max()) / k
+    with pytest.raises(ValueError):
+        Function.of("i0 @ i1", False)(a, a)
