@@ -15,8 +15,19 @@
 //            base or strides are not 16-byte aligned or whose rank exceeds what a tensor map can describe.
 // A thread owns RH x CW outputs (CW = one 128-bit vector) and slides over the tile rows so that every
 // shared-memory row segment it loads feeds up to KH output rows; the KH x KW weights of the current channel sit
-// in registers. Each input byte is fetched from HBM once per tile (+ halo); with few tiles and many channels
-// the channel range is split across CTAs and a second pass adds the partial planes in a fixed order.
+// in registers. Each input byte is fetched from HBM once per tile (+ halo).
+//
+// Launch shapes (chosen by nk_launch_tiled from the tile count and the kernel's real occupancy):
+//   * one tile per CTA, the hardware scheduling the CTAs -- a few tiles per resident CTA slot;
+//   * persistent walk -- many tiles per slot: the grid is one resident wave, CTA b takes tiles b, b + grid, ...; the
+//     producer warp keeps loading across tile boundaries; tiles with their own weights select one of the weight
+//     sets staged at once; for one-channel tiles (RING) the compute warps take tile positions from a ring the
+//     producer fills instead of decoding the tile index;
+//   * channel split -- fewer tiles than slots and many channels: up to 8 parts of a tile form a thread-block cluster
+//     and add their partial tiles through distributed shared memory; more parts go through scratch and a finish
+//     kernel. Both add in part order, so the result is deterministic and the same on either path.
+// The same kernel runs deconvolutions whose drain is the image-shaped tensor as a zero-padded, flipped correlation
+// (padX / padY / padO / xoff of the plan).
 #pragma once
 #include <cuda.h>
 #include <cooperative_groups.h>
