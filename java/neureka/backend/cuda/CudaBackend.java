@@ -26,7 +26,7 @@ import java.util.List;
 /**
  *  BackendExtension that puts a CUDA ImplementationFor on every (Operation, Algorithm) pair of the convolution /
  *  broadcast / elementwise path -- the pair list of CLBackend._load (backend/ocl/CLBackend.java:200-325) minus
- *  MatMul / DotProduct / Randomization. Install with {@code Neureka.get().backend().set(new CudaBackend())}
+ *  DotProduct / Randomization. Install with {@code Neureka.get().backend().set(new CudaBackend())}
  *  (BackendContext.java:289-321); Tensor.of(...), Function.of("i0 x i1") and backward() then run unchanged on
  *  tensors moved to a CudaDevice. The executable twin is neureka_b200/backend.py. COMPILE-UNVERIFIED.
  */
@@ -68,6 +68,9 @@ public final class CudaBackend implements BackendExtension
             receive.forOperation( conv ).set( NDConvolution.class, ctx -> (ImplementationFor<CudaDevice>) call -> CudaKernels.conv(call, d(call)) );
 
         receive.forOperation( Sum.class ).set( SumAlgorithm.class, ctx -> (ImplementationFor<CudaDevice>) CudaKernels::sum );
+        // a @ b is the convolution [M,K,1] x [1,K,N] -> [M,1,N] on padded views of the three matrices (no copy)
+        receive.forOperation( neureka.backend.main.operations.linear.MatMul.class )
+               .set( neureka.backend.main.algorithms.MatMulAlgorithm.class, ctx -> (ImplementationFor<CudaDevice>) CudaKernels::matMul );
 
         Object[][] activations = {
             { Absolute.class, ScalarFun.ABSOLUTE }, { Cosinus.class, ScalarFun.COSINUS }, { GaSU.class, ScalarFun.GASU }, { GaTU.class, ScalarFun.GATU },

@@ -147,4 +147,31 @@ public final class CudaKernels
         } catch ( RuntimeException e ) { throw e; } catch ( Throwable t ) { throw new IllegalStateException(t); }
         return out;
     }
+
+    // ---- MatMul on the convolution entry point -----------------------------------------------------------------------------
+
+    /** inline array of a rank-2 configuration with one size-1 axis inserted at position `at` (stride / indicesMap of the
+     *  new axis are irrelevant: its only index is 0). */
+    private static int[] padded( int[] c, int at ) {
+        int[] out = new int[15];
+        for ( int v = 0; v < 5; v++ ) {                       // shape | strides | indicesMap | offset | spread
+            int pad = ( v == 0 || v == 4 ) ? 1 : ( v == 3 ? 0 : 1 );
+            for ( int k = 0, j = 0; k < 3; k++ ) out[ v * 3 + k ] = ( k == at ) ? pad : c[ v * 2 + j++ ];
+        }
+        // the indicesMap of the padded view must be the row-major strides of its shape
+        out[8] = 1; out[7] = out[2]; out[6] = out[1] * out[2];
+        return out;
+    }
+
+    static Tensor<?> matMul( ExecutionCall<CudaDevice> call ) {
+        CudaDevice dev = call.getDevice();
+        Tensor<?> c = call.input(0), a = call.input(1), b = call.input(2);
+        try ( Arena arena = Arena.ofConfined() ) {
+            NeurekaCuda.check((int) NeurekaCuda.CONV.invokeExact(dev.ctx, CudaDevice.typeOf(c.getItemType()), 3,
+                    dev.bufOf(c), NeurekaCuda.cfg(arena, padded(c.getNDConf().asInlineArray(), 1)),
+                    dev.bufOf(a), NeurekaCuda.cfg(arena, padded(a.getNDConf().asInlineArray(), 2)),
+                    dev.bufOf(b), NeurekaCuda.cfg(arena, padded(b.getNDConf().asInlineArray(), 0)), -1), dev.ctx);
+        } catch ( RuntimeException e ) { throw e; } catch ( Throwable t ) { throw new IllegalStateException(t); }
+        return c;
+    }
 }
