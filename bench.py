@@ -15,15 +15,20 @@ kernel's own epilogue; its stores then wait on rank 0's link); `nccl` -- a local
 stream. Total work is fixed => "scaling": "strong".
 
 A step = one full pass. `value` = GFLOP/s with slabs resident in HBM; `e2e` = the same pass from pinned host buffers
-(H2D of the slab, conv, D2H of the result slab inside the timed region). One JSON line on stdout (rank 0).
+(H2D of the slab, conv, D2H of the result slab inside the timed region; the pass is cut along the batch dim so that the
+upload of batch b+1, the convolution of batch b and the download of batch b-1 overlap on three streams). One JSON line
+on stdout (rank 0).
+
+`--impl reference` times the CPU implementation of the same path on the host cores (the oracle port; the JVM original
+cannot run here). That arm never loads the CUDA library: inputs come from the host-only generator library.
 """
 from __future__ import annotations
 
 import argparse
 import ctypes as C
+import hashlib
 import json
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -113,18 +118,105 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(inside), "power_w_max": max(watts) if watts else None}
 
 
-def cpu_sample(a_host, k_host, a_shape, k_shape, o_shape, seconds_target: float, gpu_out=None):
+def kernel_traffic(kernel: str, workload: str):
+    """DRAM bytes (read + write) of one launch of `kernel` on `workload`, as an ncu capture measured them -- from
+    bench_traffic.json, and only while the kernel's source files still hash to what was captured (else None: a changed
+    kernel has unknown traffic until it is captured again)."""
+    path = os.path.join(ROOT, "bench_traffic.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        table = json.load(f)
+    for row in table.get("captures", []):
+        if row["workload"] == workload and kernel.startswith(row["kernel_prefix"]):
+            h = hashlib.sha256()
+            for rel in row["sources"]:
+                with open(os.path.join(ROOT, rel), "rb") as src:
+                    h.update(src.read())
+            return float(row["dram_bytes_per_launch"]) if h.hexdigest() == row["sources_sha256"] else None
+    return None
+
+
+TRAFFIC_SOURCES = ["neureka_b200/csrc/nk_conv_tiled.cuh", "neureka_b200/csrc/nk_conv_tiled.cu"]
+
+
+def record_traffic(dram_bytes: float, kernel_prefix: str, workload: str) -> None:
+    """Writes a profiler-measured DRAM byte count into bench_traffic.json together with the hash of the kernel sources it
+    was measured on (python bench.py --record-traffic BYTES, after reading dram__bytes_read.sum + dram__bytes_write.sum
+    of one launch out of the capture)."""
+    path = os.path.join(ROOT, "bench_traffic.json")
+    table = {"captures": []}
+    if os.path.exists(path):
+        with open(path) as f:
+            table = json.load(f)
+    h = hashlib.sha256()
+    for rel in TRAFFIC_SOURCES:
+        with open(os.path.join(ROOT, rel), "rb") as src:
+            h.update(src.read())
+    table["captures"] = [r for r in table["captures"] if not (r["workload"] == workload and r["kernel_prefix"] == kernel_prefix)]
+    table["captures"].append({"kernel_prefix": kernel_prefix, "workload": workload, "dram_bytes_per_launch": float(dram_bytes),
+                              "sources": TRAFFIC_SOURCES, "sources_sha256": h.hexdigest()})
+    with open(path, "w") as f:
+        json.dump(table, f, indent=1)
+        f.write("\n")
+
+
+def bind_to_gpu_numa_node(gpu_index: int):
+    """Runs this process on the CPUs of the NUMA node the GPU hangs off, so that the pinned staging buffers allocated
+    afterwards are local to the GPU's PCIe root. Returns a short description, or why nothing was done."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",")]
+            if gpu_index < len(ids) and ids[gpu_index].isdigit():
+                gpu_index = int(ids[gpu_index])
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(gpu_index)).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        bus = bus.lower()
+        if len(bus.split(":")[0]) == 8:
+            bus = bus[4:]
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return "numa node unknown (-1)"
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return f"node {node}: none of its cpus allowed"
+        os.sched_setaffinity(0, cpus)
+        return f"node {node} ({len(cpus)} cpus)"
+    except Exception as e:  # noqa: BLE001 -- placement is an optimisation, never a reason to fail
+        return "not bound: " + repr(e)
+
+
+def cpu_reference(seconds_target: float, reps: int = 1, gpu_out=None, k_shape=None, a_shape=None):
     """Times the CPU oracle (the line-faithful restatement of Neureka's CPU implementation) on a bounded sample of the
-    same workload: whole output rows of batch 0, split over all host threads like CPU.JVMExecutor splits the flat
-    output range. Returns (GFLOP/s, cores, description, max_rel_err vs gpu_out or None)."""
+    benchmark's workload: the first rows of batch 0's output, computed from batch 0's 32 input planes, the flat output
+    range split over all host threads like CPU.JVMExecutor splits it. Both arms of the benchmark call exactly this
+    (same buffers -- ordinary numpy arrays it generates itself --, same calibration, same sample), so their figures are
+    the same measurement. Returns a dict: best and mean GFLOP/s over `reps` repetitions, per-repetition values, cores,
+    the sample's description and its share of the full pass, seconds per repetition, and the largest relative error
+    of gpu_out (batch 0's output rows, if given) against the sample."""
+    import baseline_configs as B
     from neureka_b200.ndconf import NDConfiguration as ND
     from oracle import oracle as O
+    a_shape = a_shape or A_SHAPE
+    k_shape = k_shape or K_SHAPE
     cores = os.cpu_count() or 1
+    sa = [1, a_shape[1], a_shape[2], a_shape[3]]
+    so = [1, 1, a_shape[2] - k_shape[2] + 1, a_shape[3] - k_shape[3] + 1]
+    a_host = B.cfg5_image(n=int(np.prod(sa)))      # batch 0 = the first elements of the seed-5 stream
+    k_host = B.cfg5_kernel()
     macs_per_out = k_shape[1] * k_shape[2] * k_shape[3]
-    cfg_o, cfg_a, cfg_k = (ND.of_shape(s).as_inline_array() for s in (o_shape, a_shape, k_shape))
-    out = np.zeros(int(np.prod(o_shape)), dtype=np.float32)
-    # calibrate on one row per thread, then size the sample for the target time
-    row = o_shape[3]
+    cfg_o, cfg_a, cfg_k = (ND.of_shape(s).as_inline_array() for s in (so, sa, k_shape))
+    out = np.zeros(int(np.prod(so)), dtype=np.float32)
+    row = so[3]
 
     def run(n_rows):
         n = n_rows * row
@@ -142,16 +234,22 @@ def cpu_sample(a_host, k_host, a_shape, k_shape, o_shape, seconds_target: float,
             th.join()
         return time.perf_counter() - t0, n
 
-    t_cal, n_cal = run(min(cores, o_shape[2]))
-    rate = n_cal / t_cal
-    rows = int(max(cores, min(o_shape[2], seconds_target * rate / row)))
-    t, n = run(rows)
-    gflops = 2.0 * macs_per_out * n / t / 1e9
+    # calibrate on one row per thread (this also touches every page once), then size the sample for the target time
+    t_cal, n_cal = run(min(cores, so[2]))
+    rows = int(max(cores, min(so[2], seconds_target * (n_cal / t_cal) / row)))
+    vals, secs = [], []
+    for _ in range(max(1, reps)):
+        t, n = run(rows)
+        vals.append(2.0 * macs_per_out * n / t / 1e9)
+        secs.append(t)
     err = None
     if gpu_out is not None:
         ref = out[:n].astype(np.float64)
         err = float(np.abs(gpu_out[:n].astype(np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
-    return gflops, cores, f"first {rows} of {o_shape[2]} output rows of batch 0 ({n} outputs x {macs_per_out} MACs), {t:.1f} s", err
+    full_outputs = float(np.prod([a_shape[0], 1, so[2], so[3]]))
+    return {"best": float(max(vals)), "mean": float(np.mean(vals)), "per_rep": [float(v) for v in vals], "cores": cores,
+            "sample": f"first {rows} of {so[2]} output rows of batch 0 ({n} outputs x {macs_per_out} MACs)",
+            "sample_fraction": n / full_outputs, "seconds_per_rep": [float(t) for t in secs], "max_rel_err": err}
 
 
 def main():
@@ -171,7 +269,13 @@ def main():
     ap.add_argument("--probe-assemble", action="store_true",
                     help="diagnostic (N > 1, peer mode): time only the movement of the finished slabs into rank 0's "
                          "output (device-to-device copies over NVLink), i.e. the floor the owner's link sets for a step")
+    ap.add_argument("--record-traffic", type=float, default=None,
+                    help="no run: store this DRAM byte count (one full-size single-GPU launch, from a profiler capture) in "
+                         "bench_traffic.json with the hash of the kernel's sources")
     args = ap.parse_args()
+    if args.record_traffic is not None:
+        record_traffic(args.record_traffic, "nk_conv_tiled_kernel<tma", "cfg5 full size, 1 GPU")
+        return
     steps, warmup = max(1, args.steps), max(0, args.warmup)
 
     rank = int(os.environ.get("RANK", "0"))
@@ -182,39 +286,32 @@ def main():
     config = {"workload": f"cfg5: F32 a{a_shape} x k{k_shape} -> {o_shape}, halo-split on dim {SPLIT_DIM}",
               "parallelism": f"slab{world}", "l2": "inputs larger than L2 (>= 512 MiB per GPU)"}
 
-    from neureka_b200 import _lib as L
-
     # ------------------------------------------------------------------------------------------------------------
     # reference arm: the CPU implementation of the path on the host cores (the JVM original cannot run on this box;
-    # the oracle is its line-faithful restatement)
+    # the oracle is its line-faithful restatement). Nothing here loads the CUDA library.
     # ------------------------------------------------------------------------------------------------------------
     if args.impl == "reference":
         if rank != 0:
             return
-        a_rows = a_shape[2]          # one whole batch plane set: the sample is cut from its output rows
-        sa = [1, a_shape[1], a_rows, a_shape[3]]
-        so = [1, 1, a_rows - k_shape[2] + 1, o_shape[3]]
-        a_host = np.zeros(int(np.prod(sa)), dtype=np.float32)
-        k_host = np.zeros(int(np.prod(k_shape)), dtype=np.float32)
-        L.lib.nk_jrand_fill(L.NK_F32, 0, 5, 0.0, 1.0, a_host.ctypes.data_as(C.c_void_p), a_host.size)
-        L.lib.nk_jrand_fill(L.NK_F32, 1, 6, 0.0, 0.2, k_host.ctypes.data_as(C.c_void_p), k_host.size)
-        vals = []
-        per = max(1.0, min(20.0, 120.0 / (steps + warmup)))
-        for i in range(warmup + steps):
-            g, cores, sample, _ = cpu_sample(a_host, k_host, sa, k_shape, so, per)
-            if i >= warmup:
-                vals.append(g)
-        v = float(np.mean(vals))
-        ms = 1e3 * flops_total / (v * 1e9)
+        per = max(1.0, min(12.0, 150.0 / (steps + warmup)))
+        r = cpu_reference(per, reps=warmup + steps, k_shape=k_shape, a_shape=a_shape)
+        timed_vals = r["per_rep"][warmup:]
+        timed_secs = r["seconds_per_rep"][warmup:]
+        v = float(max(timed_vals))
         line = {"metric": "nd_conv_gflops", "value": v, "unit": "GFLOP/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
-                "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "impl": "reference", "config": config,
-                "cpu_baseline": {"value": v, "unit": "GFLOP/s", "cores": cores, "kind": "port",
-                                 "sample": sample + f" per step; ms_per_step extrapolates to the full {flops_total / 1e9:.2f} GFLOP pass"},
+                "ms_per_step": 1e3 * float(np.mean(timed_secs)), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic", "impl": "reference", "config": config,
+                "cpu_baseline": {"value": v, "unit": "GFLOP/s", "cores": r["cores"], "kind": "port",
+                                 "sample": r["sample"] + " per step", "sample_fraction": r["sample_fraction"],
+                                 "value_is": "best step", "mean": float(np.mean(timed_vals)), "per_step": timed_vals},
+                "ms_per_step_is": "time of the sample that was computed, not of a full pass",
+                "ms_full_pass_extrapolated": 1e3 * flops_total / (v * 1e9),
                 "e2e": {"value": v, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
         print(json.dumps(line))
         return
+
+    from neureka_b200 import _lib as L
 
     # ------------------------------------------------------------------------------------------------------------
     # CUDA arm
@@ -230,6 +327,7 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group(backend="cpu:gloo,cuda:nccl")
 
+    numa = bind_to_gpu_numa_node(local_rank)   # before any pinned allocation: staging memory local to the GPU's root
     dev = CudaDevice.get(local_rank)
     ctx = dev.ctx
     dev.set_conv_path(args.conv_path)
@@ -260,16 +358,15 @@ def main():
     out_host = np.ctypeslib.as_array(C.cast(host_out, C.POINTER(C.c_float)), shape=(max(n_out_local, 1),))
     plane = a_shape[2] * a_shape[3]
     seg = slab.in_len * a_shape[3]
+    import baseline_configs as B
     for pl in range(a_shape[0] * a_shape[1]):
-        start = pl * plane + slab.in_lo * a_shape[3]
-        ptr = C.c_void_p(host_in.value + pl * seg * 4)
-        L.lib.nk_jrand_fill_at(L.NK_F32, 0, 5, 0.0, 1.0, start, ptr, seg)
-    k_host = np.zeros(int(np.prod(k_shape)), dtype=np.float32)
-    L.lib.nk_jrand_fill(L.NK_F32, 1, 6, 0.0, 0.2, k_host.ctypes.data_as(C.c_void_p), k_host.size)
+        B.cfg5_image(a_host[pl * seg:(pl + 1) * seg], start=pl * plane + slab.in_lo * a_shape[3])
+    k_host = B.cfg5_kernel()
 
-    def alloc(n):
+    def alloc(n, shared=False):
+        """shared: from the plain allocator, so that the buffer can be exported to the other ranks"""
         b = C.c_void_p()
-        L.check(L.lib.nk_alloc(ctx, L.NK_F32, int(n), C.byref(b)), ctx)
+        L.check((L.lib.nk_alloc_shared if shared else L.lib.nk_alloc)(ctx, L.NK_F32, int(n), C.byref(b)), ctx)
         return b
 
     d_in, d_k, d_out_local = alloc(n_in), alloc(k_host.size), alloc(max(n_out_local, 1))
@@ -294,7 +391,7 @@ def main():
         d_fulls = []
         if rank == 0:
             for h in handles:
-                d_fulls.append(alloc(n_out_full))
+                d_fulls.append(alloc(n_out_full, shared=True))
                 L.check(L.lib.nk_ipc_export(ctx, d_fulls[-1], h), ctx)
         box = [[bytes(h) for h in handles]]
         dist.broadcast_object_list(box, src=0)
@@ -316,7 +413,7 @@ def main():
     elif args.assemble == "peer":
         handle = (C.c_uint8 * L.NK_IPC_HANDLE_BYTES)()
         if rank == 0:
-            d_full = alloc(n_out_full)
+            d_full = alloc(n_out_full, shared=True)
             L.check(L.lib.nk_ipc_export(ctx, d_full, handle), ctx)
         box = [bytes(handle)]
         dist.broadcast_object_list(box, src=0)
@@ -374,13 +471,52 @@ def main():
         for b in range(o_shape[0] * o_shape[1]):
             L.check(L.lib.nk_copy(ctx, d_full, b * full_rows + slab.out_lo * o_shape[3], d_out_local, b * rows, rows), ctx)
 
+    # ---- the pass from host buffers, cut along the batch dim: upload of batch b+1 | convolution of batch b | download
+    # of batch b-1 on three streams (each context owns one), ordered by events. The local slab is dense
+    # [batches, channels, rows, width], so a batch is one contiguous range on either side.
+    e2e = {}
+
+    def e2e_setup():
+        nb = local_in_shape[0]
+        e2e["nb"] = nb
+        e2e["in_per"] = n_in // nb
+        e2e["out_per"] = n_out_local // nb
+        for name in ("ctx_up", "ctx_down"):
+            c = C.c_void_p()
+            L.check(L.lib.nk_device_open(local_rank, C.byref(c)))
+            e2e[name] = c
+        for name in ("up", "conv"):
+            evs = []
+            for _ in range(nb):
+                ev = C.c_void_p()
+                L.check(L.lib.nk_event_create(ctx, C.byref(ev)), ctx)
+                evs.append(ev)
+            e2e["ev_" + name] = evs
+        ev = C.c_void_p()
+        L.check(L.lib.nk_event_create(ctx, C.byref(ev)), ctx)
+        e2e["ev_done"] = ev
+        sh_in = [1] + list(local_in_shape[1:])
+        sh_out = [1] + list(local_out_shape[1:])
+        e2e["cfg_in"] = [ND.of_shape(local_in_shape).sliced(sh_in, [b, 0, 0, 0], [1, 1, 1, 1]).as_inline_array() for b in range(nb)]
+        e2e["cfg_out"] = [ND.of_shape(local_out_shape).sliced(sh_out, [b, 0, 0, 0], [1, 1, 1, 1]).as_inline_array() for b in range(nb)]
+
     def conv_step_e2e():
-        """The same pass from host buffers: H2D of the slab, conv, D2H of the rank's result slab."""
+        """The same pass from host buffers: H2D of the slab, conv, D2H of the rank's result slab, batch by batch."""
         if n_out_local == 0:
             return
-        L.check(L.lib.nk_write_async(ctx, d_in, host_in, 0, 0, n_in), ctx)
-        L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, d_out_local, pi(cfg_out_local), d_in, pi(cfg_in), d_k, pi(cfg_k), -1), ctx)
-        L.check(L.lib.nk_read_async(ctx, d_out_local, host_out, 0, n_out_local), ctx)
+        up, down = e2e["ctx_up"], e2e["ctx_down"]
+        ip, op = e2e["in_per"], e2e["out_per"]
+        L.check(L.lib.nk_stream_wait_event(up, e2e["ev_done"]), up)        # the previous pass has read d_in completely
+        for b in range(e2e["nb"]):
+            L.check(L.lib.nk_write_async(up, d_in, host_in, b * ip, b * ip, ip), up)
+            L.check(L.lib.nk_event_record(up, e2e["ev_up"][b]), up)
+            L.check(L.lib.nk_stream_wait_event(ctx, e2e["ev_up"][b]), ctx)
+            L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, d_out_local, pi(e2e["cfg_out"][b]), d_in, pi(e2e["cfg_in"][b]), d_k, pi(cfg_k), -1), ctx)
+            L.check(L.lib.nk_event_record(ctx, e2e["ev_conv"][b]), ctx)
+            L.check(L.lib.nk_stream_wait_event(down, e2e["ev_conv"][b]), down)
+            L.check(L.lib.nk_read_async(down, d_out_local, C.c_void_p(host_out.value + b * op * 4), b * op, op), down)
+        L.check(L.lib.nk_event_record(down, e2e["ev_done"]), down)
+        L.check(L.lib.nk_stream_wait_event(ctx, e2e["ev_done"]), ctx)       # the launch stream's timer sees the whole pass
 
     def timed(fn, n_warm, n_steps):
         """W untimed steps, then exactly K steps between two events on the launch stream, bracketed by barrier +
@@ -428,11 +564,29 @@ def main():
     ms_step = ms_total / steps
     value = flops_total / (ms_step * 1e-3) / 1e9
 
-    e2e_ms_total, _, _, _ = timed(conv_step_e2e, 1, max(2, min(steps, 5)))
-    e2e_ms = e2e_ms_total / max(2, min(steps, 5))
+    # one pass alone, start to assembled result, nothing of a neighbouring pass overlapping it (median of 7)
+    single_pass_ms = None
+    if world > 1:
+        singles = []
+        for _ in range(7):
+            m, _, _, _ = timed(conv_step_resident, 0, 1)
+            singles.append(m)
+        single_pass_ms = float(np.median(singles))
+
+    e2e_setup()
+    n_e2e = max(2, min(steps, 5))
+    e2e_ms_total, _, _, _ = timed(conv_step_e2e, 1, n_e2e)
+    e2e_ms = e2e_ms_total / n_e2e
     e2e_value = flops_total / (e2e_ms * 1e-3) / 1e9
     h2d = n_in * 4
     d2h = n_out_local * 4
+    e2e_ok = None
+    if world == 1:   # the pipelined pass must leave the same result in the host buffer as the resident pass left on the device
+        L.check(L.lib.nk_sync(e2e["ctx_down"]), e2e["ctx_down"])
+        check = np.empty(n_out_local, dtype=np.float32)
+        L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, d_out_local, pi(cfg_out_local), d_in, pi(cfg_in), d_k, pi(cfg_k), -1), ctx)
+        L.check(L.lib.nk_read(ctx, d_out_local, check.ctypes.data_as(C.c_void_p), 0, n_out_local), ctx)
+        e2e_ok = bool(np.array_equal(check, out_host[:n_out_local]))
     if dist is not None:
         import torch
         t = torch.tensor([h2d, d2h, launches], dtype=torch.float64)
@@ -444,8 +598,7 @@ def main():
         barrier()
         if rank == 0:
             n_full_in = int(np.prod(a_shape))
-            full_host = np.empty(n_full_in, dtype=np.float32)
-            L.lib.nk_jrand_fill(L.NK_F32, 0, 5, 0.0, 1.0, full_host.ctypes.data_as(C.c_void_p), n_full_in)
+            full_host = B.cfg5_image(n=n_full_in)
             d_a, d_ref = alloc(n_full_in), alloc(n_out_full)
             L.check(L.lib.nk_write(ctx, d_a, full_host.ctypes.data_as(C.c_void_p), 0, 0, n_full_in), ctx)
             cfg_a, cfg_o = ND.of_shape(a_shape).as_inline_array(), ND.of_shape(o_shape).as_inline_array()
@@ -470,7 +623,7 @@ def main():
 
     sharded = None
     if world > 1 and not args.no_extra:   # collectives inside: every rank takes part
-        from neureka_b200.sharded_extra import run_sharded_extra
+        from bench_sharded import run_sharded_extra
         sharded = run_sharded_extra(dev, dist, rank, world, local_rank, read_peaks()[0])
 
     if rank == 0:
@@ -478,30 +631,41 @@ def main():
         # algorithmic bytes of rank 0's launch: its input slab + the kernel + its output slab, each touched once
         alg_bytes = (n_in + k_host.size + n_out_local) * 4.0
         alg_flops = 2.0 * n_out_local * k_shape[1] * k_shape[2] * k_shape[3]
-        kernel_ms = ms_step  # one conv kernel per step on this rank (peer mode / 1 GPU)
+        kernel_ms = ms_step  # one conv kernel per step on this rank
         achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
-        # DRAM bytes (read + write) of one full-size single-GPU launch, from an ncu capture of exactly this launch
-        # (profiles/nk_conv_tiled_kernel_tma_persistent_cfg5_full_size.md); unknown for other sizes / slabs
-        traffic = 4.5677e9 if (world == 1 and args.scale == 1) else None
+        # DRAM bytes (read + write) of one launch, from the profiler capture of this very launch shape (None when the
+        # kernel's sources changed since, or for sizes that were not captured)
+        traffic = kernel_traffic(last_kernel, "cfg5 full size, 1 GPU") if (world == 1 and args.scale == 1) else None
+        props = dev.props
+        fma_nominal = props.sm_count * 128 * 2 * props.clock_khz * 1e3 / 1e12   # FP32 lanes per SM x 2 flop x clock
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
                     "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
                     "kernel": last_kernel, "kernel_ms": kernel_ms, "algorithmic_bytes_per_launch": alg_bytes,
-                    "fp32_fma": {"achieved_tflops": alg_flops / (kernel_ms * 1e-3) / 1e12,
-                                 "nominal_peak_tflops": 148 * 128 * 2 * 1.965e9 / 1e12}}
+                    "fp32_fma": {"achieved_tflops": alg_flops / (kernel_ms * 1e-3) / 1e12, "nominal_peak_tflops": fma_nominal}}
         line = {"metric": "nd_conv_gflops", "value": value, "unit": "GFLOP/s", "n_gpus": world, "steps": steps, "warmup": max(warmup, 3),
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": dict(config, assemble=("none" if world == 1 else args.assemble), conv_family=conv_family),
-                "e2e": {"value": e2e_value, "unit": "GFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+                "config": config, "conv_family": conv_family,
+                "e2e": {"value": e2e_value, "unit": "GFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                        "pipeline": "per batch: upload | convolution | download on three streams", "staging_numa": numa,
+                        "h2d_gbs_per_gpu": (h2d / world) / (e2e_ms * 1e-3) / 1e9, "matches_resident_result": e2e_ok},
                 "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks}
+        if world > 1:
+            line["assemble"] = {"mode": args.assemble,
+                                "overlap": ("the push of pass k into rank 0's output runs on a second stream under the convolution of pass k+1; "
+                                            "ms_per_step is therefore a pipelined throughput figure, every push inside the timed region")
+                                if args.assemble == "copy" else "none: a pass is assembled when its kernel (or gather) retires",
+                                "single_pass_ms": single_pass_ms}
         if world == 1:
-            # CPU baseline on a bounded sample of the same workload, checked against the GPU result on the way
+            # CPU baseline on a bounded sample of the same workload (the routine the reference arm runs), checked against
+            # the GPU result on the way
             L.check(L.lib.nk_read(ctx, d_out_local, host_out, 0, n_out_local), ctx)
-            g, cores, sample, err = cpu_sample(a_host, k_host, local_in_shape, k_shape, local_out_shape, args.cpu_seconds, gpu_out=out_host)
-            line["cpu_baseline"] = {"value": g, "unit": "GFLOP/s", "cores": cores, "kind": "port", "sample": sample,
-                                    "gpu_vs_cpu_max_rel_err_on_sample": err}
+            r = cpu_reference(args.cpu_seconds / 2, reps=2, gpu_out=out_host, k_shape=k_shape, a_shape=a_shape)
+            line["cpu_baseline"] = {"value": r["best"], "unit": "GFLOP/s", "cores": r["cores"], "kind": "port", "sample": r["sample"],
+                                    "sample_fraction": r["sample_fraction"], "value_is": "best of 2 repetitions", "per_rep": r["per_rep"],
+                                    "gpu_vs_cpu_max_rel_err_on_sample": r["max_rel_err"]}
             if not args.no_extra:
                 try:
-                    from neureka_b200.extra_bench import run_extra
+                    from bench_extra import run_extra
                     line["extra"] = run_extra(dev, peak)
                     fp32 = line["extra"]["measured_fma_peak_tflops"]["fp32"]
                     roofline["fp32_fma"]["measured_peak_tflops"] = fp32

@@ -88,7 +88,14 @@ const char* nk_version(void);
 /* ---- memory: replaces OpenCLDevice._add/_store/free/access
  *      (OpenCLDevice.java:355-405 store, :497-524 free, :553-594 allocate*, :616-632 overwrite,
  *       :676-690 read; Device.Access J/devices/Device.java:305-407) ---- */
-int nk_alloc(nk_ctx* ctx, int32_t dtype, int64_t n_elems, nk_buf** out);    /* Device.allocate(DataType, size) */
+/* Device.allocate(DataType, size). Blocks come from the device's stream-ordered memory pool and go back to it on
+ * nk_free, in the order of ctx's stream: neither call waits for the device, and a freed block is handed out again
+ * without a trip to the driver (the reference creates and releases one cl_mem per tensor, OpenCLDevice.java:385-405,
+ * :497-524). A buffer used by a second context's stream must be ordered against ctx's stream with nk_event_*. */
+int nk_alloc(nk_ctx* ctx, int32_t dtype, int64_t n_elems, nk_buf** out);
+/* The same from the driver's plain allocator: the only kind of buffer nk_ipc_export accepts. nk_free of such a buffer
+ * waits for the device. (No reference counterpart.) */
+int nk_alloc_shared(nk_ctx* ctx, int32_t dtype, int64_t n_elems, nk_buf** out);
 int nk_wrap(nk_ctx* ctx, int32_t dtype, void* device_ptr, int64_t n_elems, nk_buf** out); /* adopt foreign device memory, not owned */
 int nk_free(nk_ctx* ctx, nk_buf* buf);                                       /* Device.free; NULL is a no-op */
 int nk_buf_info(nk_buf* buf, void** device_ptr, int64_t* n_elems, int32_t* dtype);
@@ -192,6 +199,9 @@ int nk_fused_compile(nk_ctx* ctx, int32_t dtype, int32_t n_inputs, const char* e
 int nk_fused_run(nk_ctx* ctx, nk_fused* f, int32_t rank, nk_buf* drn, const int32_t* cfg0,
                  nk_buf* const* srcs, const int32_t* const* cfgs);
 int nk_fused_free(nk_fused* f);
+/* Plan arithmetic of nk_fused_run, exposed so that it can be checked without a device: 1 when a launch of `units`
+ * work units over `rows` rows on a grid of `grid` CTAs must use 64-bit unit and row counters in the kernel. */
+int nk_fused_plan_is_wide(int64_t units, int64_t rows, int64_t grid);
 
 /* ---- ordering between contexts (no reference counterpart: OpenCLDevice owns a single in-order queue) ----
  * A second nk_ctx on the same device is a second stream. An event recorded on one context's stream can be waited

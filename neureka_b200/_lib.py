@@ -60,6 +60,7 @@ SIGNATURES = {
     "nk_last_error": (C.c_char_p, [_vp]),
     "nk_version": (C.c_char_p, []),
     "nk_alloc": (C.c_int, [_vp, _i32, _i64, C.POINTER(_vp)]),
+    "nk_alloc_shared": (C.c_int, [_vp, _i32, _i64, C.POINTER(_vp)]),
     "nk_wrap": (C.c_int, [_vp, _i32, _vp, _i64, C.POINTER(_vp)]),
     "nk_free": (C.c_int, [_vp, _vp]),
     "nk_buf_info": (C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_i64), C.POINTER(_i32)]),
@@ -70,6 +71,7 @@ SIGNATURES = {
     "nk_fused_compile": (C.c_int, [_vp, _i32, _i32, C.c_char_p, C.POINTER(_vp)]),
     "nk_fused_run": (C.c_int, [_vp, _vp, _i32, _vp, _cfg, C.POINTER(_vp), C.POINTER(_cfg)]),
     "nk_fused_free": (C.c_int, [_vp]),
+    "nk_fused_plan_is_wide": (C.c_int, [_i64, _i64, _i64]),
     "nk_probe_wait_timeout": (C.c_int, [_vp, C.c_uint64, C.POINTER(C.c_uint64)]),
     "nk_event_create": (C.c_int, [_vp, C.POINTER(_vp)]),
     "nk_event_record": (C.c_int, [_vp, _vp]),

@@ -18,6 +18,8 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 OBJDIR = os.path.join(HERE, "build")
 LIB = os.path.join(LIBDIR, "libneureka_cuda.so")
+# the input generator alone, host code only (no CUDA runtime inside): what a process that must not touch the GPU loads
+JRAND_LIB = os.path.join(LIBDIR, "libnk_jrand.so")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-O2,-fno-fast-math"]
@@ -119,7 +121,22 @@ def build(force: bool = False, verbose: bool = False) -> str:
             list(ex.map(run, jobs))
     if jobs or not os.path.exists(LIB):
         run([nvcc, *ARCH, "-shared", "-o", LIB, *objs])
+    build_jrand(force)
     return LIB
+
+
+def build_jrand(force: bool = False) -> str:
+    """libnk_jrand.so: nk_jrand.cpp compiled by the host compiler alone."""
+    os.makedirs(LIBDIR, exist_ok=True)
+    src = os.path.join(CSRC, "nk_jrand.cpp")
+    if force or not os.path.exists(JRAND_LIB) or os.path.getmtime(JRAND_LIB) < os.path.getmtime(src):
+        cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-ffp-contract=off", "-fno-fast-math", "-fPIC", "-shared",
+               "-o", JRAND_LIB, src]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+            raise RuntimeError("host compiler failed for nk_jrand.cpp")
+    return JRAND_LIB
 
 
 if __name__ == "__main__":

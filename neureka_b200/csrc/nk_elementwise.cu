@@ -359,6 +359,8 @@ extern "C" int nk_sum(nk_ctx* ctx, int32_t dtype, int32_t rank, nk_buf* src, con
     int st;
     if ((st = nk_view_parse(ctx, "nk_sum(src)", src, cfg, rank, dtype, &v))) return st;
     if (out == nullptr || out->magic != 0x4e4b4246 || out->dtype != dtype) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_sum: invalid output buffer");
+    if (out->device != ctx->device)
+        return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_sum: output buffer lives on device %d, context on device %d", out->device, ctx->device);
     if (out_index < 0 || out_index >= out->n_elems) return nk_fail(ctx, NK_ERR_BOUNDS, "nk_sum: output index %lld outside the buffer", (long long)out_index);
     EwPlan p;
     make_plan(v, nullptr, nullptr, nullptr, nullptr, &p);

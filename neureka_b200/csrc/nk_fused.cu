@@ -304,6 +304,11 @@ extern "C" int nk_fused_compile(nk_ctx* ctx, int32_t dtype, int32_t n_inputs, co
     return NK_OK;
 }
 
+static bool nk_fused_needs_wide(int64_t units, int64_t rows, int64_t grid) {
+    const int64_t lim = int64_t(1) << 32;
+    return units + grid >= lim || rows + 2 >= lim;
+}
+
 extern "C" int nk_fused_run(nk_ctx* ctx, nk_fused* f, int32_t rank, nk_buf* drn, const int32_t* cfg0, nk_buf* const* srcs, const int32_t* const* cfgs) {
     NK_CHECK_CTX(ctx);
     if (!f || f->magic != 0x4e4b4655) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_fused_run: not a fused operation");
@@ -383,14 +388,19 @@ extern "C" int nk_fused_run(nk_ctx* ctx, nk_fused* f, int32_t rank, nk_buf* drn,
     for (int k = 0; k < nd - 1; k++) rows *= p.ext[k];
     p.rows = rows;
     p.units = ((rows + 1) / 2) * p.chunks;   // groups of NK_ROWS = 2 rows
-    p.wide = p.units >= (int64_t(1) << 32) ? 1 : 0;
     if (p.units == 0) return NK_OK;
     const int64_t cap = int64_t(ctx->prop.multiProcessorCount) * 16;
+    // 32-bit unit and row arithmetic in the kernel only while neither the unit counter (it steps by the grid size) nor
+    // the row index of a group's second row can pass 2^32
+    p.wide = nk_fused_needs_wide(p.units, rows, cap) ? 1 : 0;
     const unsigned grid = unsigned(p.units < cap ? p.units : cap);
     void* params[] = {&a};
     NK_CUDA(ctx, cudaLaunchKernel(reinterpret_cast<const void*>(f->kernel), dim3(grid), dim3(256), params, 0, ctx->stream));
     return nk_after_launch(ctx, "nk_fused_kernel");
 }
+
+// Exported for the host-side test of the plan arithmetic.
+extern "C" int nk_fused_plan_is_wide(int64_t units, int64_t rows, int64_t grid) { return nk_fused_needs_wide(units, rows, grid) ? 1 : 0; }
 
 extern "C" int nk_fused_free(nk_fused* f) {
     if (!f || f->magic != 0x4e4b4655) return NK_ERR_BAD_ARG;

@@ -18,7 +18,8 @@ struct nk_buf {
     int64_t n_elems = 0;
     int32_t dtype = NK_F32;
     int32_t device = 0;
-    bool owned = true;    // cudaFree on nk_free
+    bool owned = true;    // released on nk_free
+    bool pooled = false;  // from the device's stream-ordered pool (cudaFreeAsync), else cudaFree
     bool ipc = false;     // cudaIpcCloseMemHandle on nk_free
     uint32_t magic = 0x4e4b4246;  // 'NKBF'
 };

@@ -49,17 +49,18 @@ int nk_after_launch(nk_ctx* ctx, const char* kernel_name) {
     return NK_OK;
 }
 
+// The context's scratch block grows on demand. Both the release of the old block and the new allocation are ordered on
+// the context's stream (the device's memory pool), so work already queued keeps its block and nothing waits for the
+// device: a backward pass that needs a larger block in its middle does not stall the other streams.
 int nk_scratch(nk_ctx* ctx, size_t bytes, void** out) {
     if (bytes > ctx->scratch_bytes) {
         if (ctx->scratch) {
-            // work queued on the stream may still use the old block
-            NK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-            NK_CUDA(ctx, cudaFree(ctx->scratch));
+            NK_CUDA(ctx, cudaFreeAsync(ctx->scratch, ctx->stream));
             ctx->scratch = nullptr;
             ctx->scratch_bytes = 0;
         }
         size_t want = bytes < (size_t(1) << 20) ? (size_t(1) << 20) : bytes;
-        NK_CUDA(ctx, cudaMalloc(&ctx->scratch, want));
+        NK_CUDA(ctx, cudaMallocAsync(&ctx->scratch, want, ctx->stream));
         ctx->scratch_bytes = want;
     }
     *out = ctx->scratch;
@@ -107,11 +108,15 @@ int nk_view_parse(nk_ctx* ctx, const char* who, const nk_buf* buf, const int32_t
         v->imap[k] = virtual_cfg ? vmap[k] : imap[k];
         v->estride[k] = int64_t(spread[k]) * strides[k];
         v->base += int64_t(offset[k]) * strides[k];
+        // checked before the multiplication: eight extents of 2^16 would wrap int64 to 0 and pass every later test
+        if (v->size > (int64_t(1) << 40) / shape[k])
+            return nk_fail(ctx, NK_ERR_UNSUPPORTED, "%s: view of more than 2^40 elements is too large", who);
         v->size *= shape[k];
-        int64_t reach = v->estride[k] * (shape[k] - 1);
+        int64_t reach = v->estride[k] * (shape[k] - 1);   // |spread * strides| < 2^62, extent < 2^31: no wrap
         if (reach > 0) hi += reach; else lo += reach;
+        if (hi > (int64_t(1) << 62) || lo < -(int64_t(1) << 62))
+            return nk_fail(ctx, NK_ERR_BOUNDS, "%s: view reaches beyond any buffer", who);
     }
-    if (v->size > (int64_t(1) << 40)) return nk_fail(ctx, NK_ERR_UNSUPPORTED, "%s: view of %lld elements is too large", who, (long long)v->size);
     if (v->base + lo < 0 || v->base + hi >= buf->n_elems)
         return nk_fail(ctx, NK_ERR_BOUNDS, "%s: view reaches elements [%lld, %lld] of a buffer holding %lld",
                        who, (long long)(v->base + lo), (long long)(v->base + hi), (long long)buf->n_elems);
@@ -166,6 +171,14 @@ extern "C" int nk_device_open(int32_t ordinal, nk_ctx** out_ctx) {
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev0);
     if (e == cudaSuccess) e = cudaEventCreate(&ctx->ev1);
+    if (e == cudaSuccess) {
+        // nk_alloc / nk_free go through the device's stream-ordered memory pool: freed blocks stay in the pool (no
+        // release back to the driver at synchronisation points) and are handed out again without a device-wide wait
+        cudaMemPool_t pool = nullptr;
+        e = cudaDeviceGetDefaultMemPool(&pool, ordinal);
+        uint64_t keep = UINT64_MAX;
+        if (e == cudaSuccess) e = cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
     if (e == cudaSuccess) e = cudaHostAlloc((void**)&ctx->tma_status_host, sizeof(int), cudaHostAllocMapped);
     if (e == cudaSuccess) { *ctx->tma_status_host = 0; e = cudaHostGetDevicePointer((void**)&ctx->tma_status_dev, ctx->tma_status_host, 0); }
     if (e != cudaSuccess) {
@@ -189,8 +202,8 @@ extern "C" int nk_device_open(int32_t ordinal, nk_ctx** out_ctx) {
 extern "C" int nk_device_close(nk_ctx* ctx) {
     if (ctx == nullptr) return NK_OK;
     NK_CHECK_CTX(ctx);
+    if (ctx->scratch) cudaFreeAsync(ctx->scratch, ctx->stream);
     cudaStreamSynchronize(ctx->stream);
-    if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->tma_status_host) cudaFreeHost(ctx->tma_status_host);
     cudaEventDestroy(ctx->ev0);
     cudaEventDestroy(ctx->ev1);
@@ -231,23 +244,36 @@ extern "C" void* nk_stream(nk_ctx* ctx) {
 // ------------------------------------------------------------------------------------------------
 // memory
 // ------------------------------------------------------------------------------------------------
-extern "C" int nk_alloc(nk_ctx* ctx, int32_t dtype, int64_t n_elems, nk_buf** out) {
+// Largest element count a handle may claim: keeps n_elems * sizeof(element) far from wrapping size_t.
+static const int64_t NK_MAX_ELEMS = int64_t(1) << 44;
+
+static int nk_alloc_impl(nk_ctx* ctx, int32_t dtype, int64_t n_elems, bool pooled, nk_buf** out, const char* who) {
     NK_CHECK_CTX(ctx);
-    if (!out) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_alloc: out pointer is null");
+    if (!out) return nk_fail(ctx, NK_ERR_BAD_ARG, "%s: out pointer is null", who);
     *out = nullptr;
     size_t es = nk_dtype_size(dtype);
-    if (es == 0) return nk_fail(ctx, NK_ERR_UNSUPPORTED, "nk_alloc: unknown dtype %d", dtype);
-    if (n_elems < 1) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_alloc: n_elems = %lld, must be > 0", (long long)n_elems);
+    if (es == 0) return nk_fail(ctx, NK_ERR_UNSUPPORTED, "%s: unknown dtype %d", who, dtype);
+    if (n_elems < 1) return nk_fail(ctx, NK_ERR_BAD_ARG, "%s: n_elems = %lld, must be > 0", who, (long long)n_elems);
+    if (n_elems > NK_MAX_ELEMS) return nk_fail(ctx, NK_ERR_OOM, "%s: %lld elements exceed the supported maximum of 2^44 (more memory than any device holds)", who, (long long)n_elems);
     nk_buf* b = new (std::nothrow) nk_buf();
-    if (!b) return nk_fail(ctx, NK_ERR_OOM, "nk_alloc: host allocation failed");
-    cudaError_t e = cudaMalloc(&b->ptr, size_t(n_elems) * es);
-    if (e != cudaSuccess) { delete b; return nk_cuda_fail(ctx, e, "cudaMalloc"); }
+    if (!b) return nk_fail(ctx, NK_ERR_OOM, "%s: host allocation failed", who);
+    cudaError_t e = pooled ? cudaMallocAsync(&b->ptr, size_t(n_elems) * es, ctx->stream) : cudaMalloc(&b->ptr, size_t(n_elems) * es);
+    if (e != cudaSuccess) { delete b; return nk_cuda_fail(ctx, e, pooled ? "cudaMallocAsync" : "cudaMalloc"); }
     b->n_elems = n_elems;
     b->dtype = dtype;
     b->device = ctx->device;
     b->owned = true;
+    b->pooled = pooled;
     *out = b;
     return NK_OK;
+}
+
+extern "C" int nk_alloc(nk_ctx* ctx, int32_t dtype, int64_t n_elems, nk_buf** out) {
+    return nk_alloc_impl(ctx, dtype, n_elems, true, out, "nk_alloc");
+}
+
+extern "C" int nk_alloc_shared(nk_ctx* ctx, int32_t dtype, int64_t n_elems, nk_buf** out) {
+    return nk_alloc_impl(ctx, dtype, n_elems, false, out, "nk_alloc_shared");
 }
 
 extern "C" int nk_wrap(nk_ctx* ctx, int32_t dtype, void* device_ptr, int64_t n_elems, nk_buf** out) {
@@ -256,6 +282,7 @@ extern "C" int nk_wrap(nk_ctx* ctx, int32_t dtype, void* device_ptr, int64_t n_e
     *out = nullptr;
     if (nk_dtype_size(dtype) == 0) return nk_fail(ctx, NK_ERR_UNSUPPORTED, "nk_wrap: unknown dtype %d", dtype);
     if (device_ptr == nullptr || n_elems < 1) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_wrap: null pointer or empty range");
+    if (n_elems > NK_MAX_ELEMS) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_wrap: %lld elements exceed the supported maximum of 2^44", (long long)n_elems);
     nk_buf* b = new (std::nothrow) nk_buf();
     if (!b) return nk_fail(ctx, NK_ERR_OOM, "nk_wrap: host allocation failed");
     b->ptr = device_ptr;
@@ -271,14 +298,15 @@ extern "C" int nk_free(nk_ctx* ctx, nk_buf* buf) {
     if (buf == nullptr) return NK_OK;
     NK_CHECK_CTX(ctx);
     if (buf->magic != 0x4e4b4246) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_free: invalid (or already freed) buffer handle");
-    // Kernels already queued may still touch the allocation; cudaFree synchronises the device, an IPC
-    // close does not, so wait for the stream first.
+    // Kernels already queued may still touch the allocation. A pooled block goes back to the pool in stream order
+    // (after everything this context queued so far; nothing waits); cudaFree synchronises the device; an IPC close
+    // does not, so wait for the stream first.
     cudaError_t e = cudaSuccess;
     if (buf->ipc) {
         cudaStreamSynchronize(ctx->stream);
         e = cudaIpcCloseMemHandle(buf->ptr);
     } else if (buf->owned) {
-        e = cudaFree(buf->ptr);
+        e = buf->pooled ? cudaFreeAsync(buf->ptr, ctx->stream) : cudaFree(buf->ptr);
     }
     buf->magic = 0;
     delete buf;
@@ -500,7 +528,8 @@ static_assert(sizeof(cudaIpcMemHandle_t) <= NK_IPC_HANDLE_BYTES, "IPC handle doe
 extern "C" int nk_ipc_export(nk_ctx* ctx, nk_buf* buf, uint8_t handle[NK_IPC_HANDLE_BYTES]) {
     NK_CHECK_CTX(ctx);
     if (buf == nullptr || buf->magic != 0x4e4b4246 || handle == nullptr) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_ipc_export: invalid argument");
-    if (!buf->owned) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_ipc_export: only buffers allocated by nk_alloc can be exported");
+    if (!buf->owned || buf->pooled)
+        return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_ipc_export: only buffers allocated by nk_alloc_shared can be exported (pooled memory has no IPC handle)");
     cudaIpcMemHandle_t h;
     NK_CUDA(ctx, cudaIpcGetMemHandle(&h, buf->ptr));
     memset(handle, 0, NK_IPC_HANDLE_BYTES);
@@ -512,7 +541,7 @@ extern "C" int nk_ipc_open(nk_ctx* ctx, const uint8_t handle[NK_IPC_HANDLE_BYTES
     NK_CHECK_CTX(ctx);
     if (!out || !handle) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_ipc_open: null argument");
     *out = nullptr;
-    if (nk_dtype_size(dtype) == 0 || n_elems < 1) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_ipc_open: bad dtype or size");
+    if (nk_dtype_size(dtype) == 0 || n_elems < 1 || n_elems > NK_MAX_ELEMS) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_ipc_open: bad dtype or size");
     cudaIpcMemHandle_t h;
     memcpy(&h, handle, sizeof(h));
     void* p = nullptr;

@@ -113,6 +113,8 @@ extern "C" int nk_sum_static(nk_ctx* ctx, int32_t dtype, int32_t rank, nk_buf* s
     int st;
     if ((st = nk_view_parse(ctx, "nk_sum_static(src)", src, cfg, rank, dtype, &view))) return st;
     if (out == nullptr || out->magic != 0x4e4b4246 || out->dtype != dtype) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_sum_static: invalid output buffer");
+    if (out->device != ctx->device)
+        return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_sum_static: output buffer lives on device %d, context on device %d", out->device, ctx->device);
     if (out_index < 0 || out_index >= out->n_elems) return nk_fail(ctx, NK_ERR_BOUNDS, "nk_sum_static: output index %lld outside the buffer", (long long)out_index);
     const size_t es = nk_dtype_size(dtype);
     const int64_t n = view.size, n1 = (n + 127) / 128, n2 = (n1 + 127) / 128;

@@ -192,6 +192,10 @@ def _execute_on_common_device(call: ExecutionCall, impl) -> Tensor:
     """AbstractDeviceAlgorithm.executeOnCommonDevice (:427-449) + executeDeviceAlgorithm (:127-156)."""
     dev = call.device
     moved = []
+    for t in call.inputs:   # AbstractDeviceAlgorithm.java:119-124, :130-134
+        if t is None:
+            raise ValueError("Device arguments may not be null!\n"
+                             "One or more tensor arguments within the given ExecutionCall instance is null.")
     for t in call.inputs:
         if t is not None and not dev.has(t):
             dev.store(t)
@@ -304,7 +308,7 @@ def run_function(fid: str, x: Tensor, d: int = -1) -> Tensor:
     dev = _common_device([x])
     be = B.backend()
     if fid == "sumItems":
-        call = ExecutionCall([None, x], fid, dev, d)
+        call = ExecutionCall([x], fid, dev, d)   # CLSum takes input(0), or input(1) when a null drain was put in front
         return _execute_on_common_device(call, be.implementation_for(fid, B.SUM_ALGORITHM))
     out = _new_output(x.dtype, x.shape, dev)
     if x.is_virtual:

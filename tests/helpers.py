@@ -57,6 +57,21 @@ def gpu_conv(device, drn, c0, a, c1, b, c2, d=-1, path=L.NK_CONV_AUTO):
     return out
 
 
+CONV_TOL = {np.dtype(np.float32): 1e-5, np.dtype(np.float64): 1e-12}
+
+
+def assert_conv_close(got, ref, scale, what=""):
+    """The convolution tolerance, per element and with no extra factor: |got - ref| <= tol * sum|a||b| (tol = 1e-5 for
+    F32, 1e-12 for F64; `scale` is the same sum taken over absolute values, the magnitude any summation order is
+    measured against). Returns the largest error / bound ratio seen."""
+    dt = np.dtype(got.dtype)
+    err = np.abs(got.astype(np.float64) - ref.astype(np.float64))
+    bound = CONV_TOL[dt] * np.maximum(np.abs(scale).astype(np.float64), np.finfo(dt).tiny)
+    worst = int(np.argmax(err / bound))
+    assert np.all(err <= bound), f"{what}: err {err.flat[worst]:.3e} > bound {bound.flat[worst]:.3e} at {worst}"
+    return float((err / bound).max())
+
+
 def gpu_call3(fn, device, op, drn, c0, a, c1, b, c2, d=-1):
     D, A, B = DevArray(device, drn), DevArray(device, a), DevArray(device, b)
     k0, p0 = cfgp(c0); k1, p1 = cfgp(c1); k2, p2 = cfgp(c2)

@@ -102,9 +102,8 @@ def test_scaled_config3_forward_and_reduced_gradients(device, oracle):
     from neureka_b200.ndconf import NDConfiguration as ND
     n, m, k = 24, 16, 160
     dt = np.float32
-    a_h, b_h = np.zeros(n * k, dtype=dt), np.zeros(m * k, dtype=dt)
-    L.lib.nk_jrand_fill(L.NK_F32, 0, 3, -2.0, 2.0, a_h.ctypes.data_as(C.c_void_p), a_h.size)
-    L.lib.nk_jrand_fill(L.NK_F32, 0, 3, -2.0, 2.0, b_h.ctypes.data_as(C.c_void_p), b_h.size)
+    import baseline_configs as B
+    a_h, b_h = B.cfg3_inputs(n, m, k)   # one uniform stream of seed 3: a, then b
     a = Tensor.of(dt, [n, 1, k], a_h).set_rqs_gradient(True).to(device)
     b = Tensor.of(dt, [1, m, k], b_h).set_rqs_gradient(True).to(device)
     y = Function.of("tanh(i0*i1+i1)")(a, b)
@@ -126,6 +125,63 @@ def test_scaled_config3_forward_and_reduced_gradients(device, oracle):
     db = (g3 * (a_h.reshape(n, 1, k).astype(np.float64) + 1)).sum(axis=0)
     np.testing.assert_allclose(a.gradient.items.reshape(n, k), da, rtol=1e-5, atol=1e-5)
     np.testing.assert_allclose(b.gradient.items.reshape(m, k), db, rtol=1e-5, atol=1e-5)
+
+
+def test_config3_through_the_api_at_the_largest_int_sized_variant(device, oracle):
+    """BASELINE config 3 through Function.of("tanh(i0*i1+i1)") and backward(), at 2^30 outputs: a [1024,1,1024],
+    b [1,1024,1024] -- the largest variant of the configuration whose tensors a Java int can still count (the full
+    2^33 cannot exist in the reference). Same generator and seed as the full size. Forward: sampled windows against
+    the oracle's op-by-op chain, <= 1 ulp. Backward of the sum: rows of the reduced gradients against float64 sums."""
+    import baseline_configs as B
+    from helpers import ulp_diff
+    from neureka_b200.ndconf import NDConfiguration as ND
+    if device.props.total_mem_bytes < 60 * (1 << 30):
+        pytest.skip("needs ~40 GiB of device memory")
+    n, m, k = 1024, 1024, 1024
+    dt = np.float32
+    a_h, b_h = B.cfg3_inputs(n, m, k)
+    a = Tensor.of(dt, [n, 1, k], a_h).set_rqs_gradient(True).to(device)
+    b = Tensor.of(dt, [1, m, k], b_h).set_rqs_gradient(True).to(device)
+    y = Function.of("tanh(i0*i1+i1)")(a, b)
+    assert y.shape == (n, m, k) and y.is_outsourced
+    N = n * m * k
+    win = 8192
+    rng = np.random.default_rng(31)
+    acc = device.access(y)
+    cw = ND.of_shape([win]).as_inline_array()
+    for s0 in [0, N - win, (1 << 29) - 17] + [int(x) for x in rng.integers(0, N - win, size=8)]:
+        got = acc.read_array(s0, win)
+        idx = np.arange(s0, s0 + win, dtype=np.int64)
+        i, j, kk = idx // (m * k), (idx // k) % m, idx % k
+        av, bv = a_h[i * k + kk], b_h[j * k + kk]
+        t1, t2, want = (np.zeros(win, dtype=dt) for _ in range(3))
+        oracle.bielementwise("*", t1, cw, np.ascontiguousarray(av), cw, np.ascontiguousarray(bv), cw)
+        oracle.bielementwise("+", t2, cw, t1, cw, np.ascontiguousarray(bv), cw)
+        oracle.unary("tanh", want, cw, t2, cw)
+        assert ulp_diff(got, want).max() <= 1, s0
+    s = y.sum()
+    s.backward()
+    ga = a.gradient.items.reshape(n, k)
+    gb = b.gradient.items.reshape(m, k)
+    A, Bm = a_h.reshape(n, k), b_h.reshape(m, k)
+
+    def g_of(arow, brow):   # tanh'(a*b+b) as the reference defines it for F32, evaluated in float64
+        u = (arow * brow).astype(np.float32) + brow
+        t = np.zeros(u.size, dtype=np.float32)
+        c = ND.of_shape([u.size]).as_inline_array()
+        oracle.unary("tanh", t, c, np.ascontiguousarray(u.reshape(-1)), c, d=0)
+        return t.reshape(u.shape).astype(np.float64)
+
+    for i in (0, 511, n - 1):      # da[i, :] = sum_j g[i, j, :] * b[j, :]
+        g = g_of(A[i][None, :], Bm)
+        want = (g * Bm).sum(axis=0)
+        mag = (np.abs(g) * np.abs(Bm)).sum(axis=0)
+        assert np.all(np.abs(ga[i] - want) <= 1e-5 * mag + 1e-30)
+    for j in (0, 300, m - 1):      # db[j, :] = sum_i g[i, j, :] * (a[i, :] + 1)
+        g = g_of(A, Bm[j][None, :])
+        want = (g * (A.astype(np.float64) + 1)).sum(axis=0)
+        mag = (np.abs(g) * (np.abs(A.astype(np.float64)) + 1)).sum(axis=0)
+        assert np.all(np.abs(gb[j] - want) <= 1e-5 * mag + 1e-30)
 
 
 @pytest.mark.parametrize("dt", [np.float32, np.float64])

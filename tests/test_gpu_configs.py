@@ -1,80 +1,103 @@
 """The BASELINE configurations themselves, on their seeded inputs (java.util.Random-compatible streams), against the
 CPU oracle: full output where the oracle finishes in seconds, otherwise oracle spot checks on sampled output ranges
-plus size-independent properties (linearity in the kernel, shift equivariance, gradient = adjoint identity)."""
+plus size-independent properties (linearity in the kernel, shift equivariance, gradient = adjoint identity).
+
+Every comparison of a convolution result uses the stated tolerance per element with no extra factor:
+|gpu - oracle| <= 1e-5 (F32) / 1e-12 (F64) x sum|a||b| (helpers.assert_conv_close)."""
 import ctypes as C
 
 import numpy as np
 import pytest
 
-from helpers import DevArray, cfgp, gpu_conv
+import baseline_configs as B
+from helpers import DevArray, assert_conv_close, cfgp, gpu_conv
 from neureka_b200 import _lib as L
 from neureka_b200.ndconf import NDConfiguration as ND
 
 pytestmark = pytest.mark.gpu
 
 
-def _rand(dtype, n, dist, seed, p0, p1):
-    a = np.zeros(n, dtype=dtype)
-    L.lib.nk_jrand_fill(L.NK_F32 if dtype == np.float32 else L.NK_F64, dist, seed, p0, p1, a.ctypes.data_as(C.c_void_p), n)
-    return a
-
-
 def test_config1_conv2d_matches_the_simple_cpu_convolution(device, oracle):
-    both = _rand(np.float32, 256 * 256 + 25, 0, 42, -1.0, 1.0)   # one stream of seed 42: the image, then the kernel
-    a, k = both[:256 * 256].copy(), both[256 * 256:].copy()
+    a, k = B.cfg1_inputs()   # one stream of seed 42: the image, then the kernel
     co, ca, ck = ND.of_shape([252, 252]), ND.of_shape([256, 256]), ND.of_shape([5, 5])
     ref = np.zeros(co.size, dtype=np.float32)
     assert oracle.conv(ref, co.as_inline_array(), a, ca.as_inline_array(), k, ck.as_inline_array()) == 1   # SimpleCPUConvolution path
+    scale = np.zeros(co.size, dtype=np.float32)
+    oracle.conv(scale, co.as_inline_array(), np.abs(a), ca.as_inline_array(), np.abs(k), ck.as_inline_array())
     got = gpu_conv(device, np.zeros(co.size, dtype=np.float32), co, a, ca, k, ck)
+    assert_conv_close(got, ref, scale, "config 1")
     assert np.abs(got - ref).max() <= 1e-5 * np.abs(ref).max()
 
 
 def test_config2_channel_collapsing_conv(device, oracle):
-    both = _rand(np.float32, 64 * 512 * 512 + 576, 1, 7, 0.0, 1.0)   # one N(0,1) stream of seed 7: the image, then the kernel
-    a, k = both[:64 * 512 * 512].copy(), both[64 * 512 * 512:].copy()
+    a, k = B.cfg2_inputs()   # one N(0,1) stream of seed 7: the image, then the kernel
     co, ca, ck = ND.of_shape([1, 510, 510]), ND.of_shape([64, 512, 512]), ND.of_shape([64, 3, 3])
     ref = np.zeros(co.size, dtype=np.float32)
     assert oracle.conv(ref, co.as_inline_array(), a, ca.as_inline_array(), k, ck.as_inline_array(), threads=8) == 0   # general nd path
     scale = np.zeros(co.size, dtype=np.float32)
     oracle.conv(scale, co.as_inline_array(), np.abs(a), ca.as_inline_array(), np.abs(k), ck.as_inline_array(), threads=8)
     got = gpu_conv(device, np.zeros(co.size, dtype=np.float32), co, a, ca, k, ck)
-    assert np.all(np.abs(got.astype(np.float64) - ref) <= 1e-5 * scale)
-    assert np.abs(got - ref).max() <= 1e-5 * np.abs(ref).max() * 4
+    assert_conv_close(got, ref, scale, "config 2")
+    assert np.abs(got - ref).max() <= 1e-5 * np.abs(ref).max()
 
 
 def test_config4_f64_forward_and_both_gradients(device, oracle):
-    v, k = _rand(np.float64, 128 ** 3, 1, 11, 0.0, 1.0), _rand(np.float64, 343, 1, 12, 0.0, 0.1)
+    v, k = B.cfg4_inputs()
     cv, ck, cy = ND.of_shape([128] * 3), ND.of_shape([7] * 3), ND.of_shape([122] * 3)
+    iv, ik, iy = cv.as_inline_array(), ck.as_inline_array(), cy.as_inline_array()
+    av, ak = np.abs(v), np.abs(k)
     y = gpu_conv(device, np.zeros(cy.size), cy, v, cv, k, ck)
     # forward: oracle on sampled ranges of the output (the full state machine would take minutes)
     rng = np.random.default_rng(4)
-    ref = np.zeros(cy.size)
-    for s in rng.integers(0, cy.size - 3000, size=6):
-        oracle.conv_range(ref, cy.as_inline_array(), v, cv.as_inline_array(), k, ck.as_inline_array(), -1, int(s), int(s) + 3000)
-        seg = slice(int(s), int(s) + 3000)
-        assert np.abs(y[seg] - ref[seg]).max() <= 1e-12 * max(1.0, np.abs(ref[seg]).max()) * 50
+    ref, scale = np.zeros(cy.size), np.zeros(cy.size)
+    for s in [0, cy.size - 3000] + [int(x) for x in rng.integers(0, cy.size - 3000, size=6)]:
+        oracle.conv_range(ref, iy, v, iv, k, ik, -1, s, s + 3000)
+        oracle.conv_range(scale, iy, av, iv, ak, ik, -1, s, s + 3000)
+        seg = slice(s, s + 3000)
+        assert_conv_close(y[seg], ref[seg], scale[seg], f"config 4 forward, range at {s}")
     # backward of sum(y): error = ones
     err = np.ones(cy.size)
     gk = gpu_conv(device, np.zeros(343), ck, v, cv, err, cy, d=0)             # (drain = kernel-shaped, t1 = volume, t2 = error)
     gv = gpu_conv(device, np.zeros(128 ** 3), cv, k, ck, err, cy, d=0)         # (drain = volume-shaped, t1 = kernel, t2 = error)
-    # grad wrt kernel with error = ones is a box sum of the volume: check all 343 taps in float128-free numpy
-    V = v.reshape(128, 128, 128)
-    csum = np.zeros((129, 129, 129))
-    csum[1:, 1:, 1:] = V.cumsum(0).cumsum(1).cumsum(2)
-    def box(z, yy, x):
-        z1, y1, x1 = z + 122, yy + 122, x + 122
-        return (csum[z1, y1, x1] - csum[z, y1, x1] - csum[z1, yy, x1] - csum[z1, y1, x] + csum[z, yy, x1] + csum[z, y1, x] + csum[z1, yy, x] - csum[z, yy, x])
-    want_gk = np.array([box(z, yy, x) for z in range(7) for yy in range(7) for x in range(7)])
-    np.testing.assert_allclose(gk, want_gk, rtol=1e-9, atol=1e-6)
-    # oracle (general deconvolution) on a few taps: 122^3 terms each
+    # grad wrt kernel with error = ones is a box sum of the volume: all 343 taps against summed-area tables in
+    # extended precision, bound 1e-12 x the box sum of |v|
+    def boxes(vol):
+        csum = np.zeros((129, 129, 129), dtype=np.longdouble)
+        csum[1:, 1:, 1:] = vol.reshape(128, 128, 128).astype(np.longdouble).cumsum(0).cumsum(1).cumsum(2)
+        out = []
+        for z in range(7):
+            for yy in range(7):
+                for x in range(7):
+                    z1, y1, x1 = z + 122, yy + 122, x + 122
+                    out.append(csum[z1, y1, x1] - csum[z, y1, x1] - csum[z1, yy, x1] - csum[z1, y1, x] + csum[z, yy, x1]
+                               + csum[z, y1, x] + csum[z1, yy, x] - csum[z, yy, x])
+        return np.array(out, dtype=np.longdouble)
+    want_gk, scale_gk = boxes(v), boxes(av)
+    assert np.all(np.abs(gk - want_gk) <= 1e-12 * scale_gk), float(np.max(np.abs(gk - want_gk) / scale_gk))
+    # the oracle's general deconvolution on two taps (122^3 terms each), same bound
     ref_gk = np.zeros(343)
-    oracle.conv_range(ref_gk, ck.as_inline_array(), v, cv.as_inline_array(), err, cy.as_inline_array(), 0, 170, 172)
-    np.testing.assert_allclose(gk[170:172], ref_gk[170:172], rtol=1e-12 * 1e3)
+    oracle.conv_range(ref_gk, ik, v, iv, err, iy, 0, 170, 172)
+    assert_conv_close(gk[170:172], ref_gk[170:172], np.asarray(scale_gk[170:172], dtype=np.float64), "config 4 kernel gradient")
     # grad wrt volume: oracle on sampled ranges (each element visits all of the error in the reference: keep it short)
-    ref_gv = np.zeros(128 ** 3)
-    for s in (0, 128 * 128 * 64 + 128 * 60 + 50):
-        oracle.conv_range(ref_gv, cv.as_inline_array(), k, ck.as_inline_array(), err, cy.as_inline_array(), 0, s, s + 2)
-        np.testing.assert_allclose(gv[s:s + 2], ref_gv[s:s + 2], rtol=1e-11, atol=1e-13)
+    ref_gv, scale_gv = np.zeros(128 ** 3), np.zeros(128 ** 3)
+    for s in (0, 128 * 128 * 64 + 128 * 60 + 50, 128 ** 3 - 2):
+        oracle.conv_range(ref_gv, iv, k, ik, err, iy, 0, s, s + 2)
+        oracle.conv_range(scale_gv, iv, ak, ik, err, iy, 0, s, s + 2)
+        assert_conv_close(gv[s:s + 2], ref_gv[s:s + 2], scale_gv[s:s + 2], f"config 4 volume gradient at {s}")
+    # error = ones: every volume gradient is a box sum of the kernel -- all 128^3 of them against the same tables idea
+    kc = np.zeros((8, 8, 8), dtype=np.longdouble)
+    kc[1:, 1:, 1:] = k.reshape(7, 7, 7).astype(np.longdouble).cumsum(0).cumsum(1).cumsum(2)
+    ka = np.zeros((8, 8, 8), dtype=np.longdouble)
+    ka[1:, 1:, 1:] = ak.reshape(7, 7, 7).astype(np.longdouble).cumsum(0).cumsum(1).cumsum(2)
+    idx = np.arange(128)
+    lo, hi = np.maximum(idx - 121, 0), np.minimum(idx, 6) + 1     # taps t with 0 <= p - t < 122
+    def box3(c):
+        L0, H0 = lo[:, None, None], hi[:, None, None]
+        L1, H1 = lo[None, :, None], hi[None, :, None]
+        L2, H2 = lo[None, None, :], hi[None, None, :]
+        return (c[H0, H1, H2] - c[L0, H1, H2] - c[H0, L1, H2] - c[H0, H1, L2] + c[L0, L1, H2] + c[L0, H1, L2] + c[H0, L1, L2] - c[L0, L1, L2])
+    want_gv, scale_all = box3(kc).reshape(-1), box3(ka).reshape(-1)
+    assert np.all(np.abs(gv - want_gv) <= 1e-12 * scale_all)
     # adjoint identity <conv(v,k), e> = <v, grad_v(e)> = <k, grad_k(e)> for a random error
     e = rng.standard_normal(cy.size)
     gk_e = gpu_conv(device, np.zeros(343), ck, v, cv, e, cy, d=0)
@@ -88,8 +111,8 @@ def test_config5_full_size_on_one_gpu(device, oracle):
     """4 GiB input: oracle spot checks on sampled output ranges, plus properties that hold at any size."""
     a_shape, k_shape, o_shape = [8, 32, 2048, 2048], [1, 32, 5, 5], [8, 1, 2044, 2044]
     n_in, n_out = int(np.prod(a_shape)), int(np.prod(o_shape))
-    a = _rand(np.float32, n_in, 0, 5, 0.0, 1.0)
-    k = _rand(np.float32, 800, 1, 6, 0.0, 0.2)
+    a = B.cfg5_image()
+    k = B.cfg5_kernel()
     A = DevArray(device, a)
     K = DevArray(device, k)
     O = DevArray(device, np.zeros(1, dtype=np.float32))
@@ -104,8 +127,12 @@ def test_config5_full_size_on_one_gpu(device, oracle):
     rng = np.random.default_rng(55)
     ref = np.zeros(n_out, dtype=np.float32)
     starts = [0, n_out - 500, 2044 * 2044 * 3 + 2044 * 2043 + 1500] + [int(s) for s in rng.integers(0, n_out - 500, size=5)]
+    scale = np.zeros(n_out, dtype=np.float32)
+    ak = np.abs(k)    # the image is uniform on [0, 1): already non-negative
     for s in starts:
         oracle.conv_range(ref, ko, a, ka, k, kk, -1, s, s + 500)
+        oracle.conv_range(scale, ko, a, ka, ak, kk, -1, s, s + 500)
+        assert_conv_close(y[s:s + 500], ref[s:s + 500], scale[s:s + 500], f"config 5, range at {s}")
         assert np.abs(y[s:s + 500] - ref[s:s + 500]).max() <= 1e-5 * np.abs(ref[s:s + 500]).max()
     # linearity in the kernel: conv(a, 2k) == 2 conv(a, k) exactly (power-of-two scaling)
     K2 = DevArray(device, k * 2)
@@ -136,8 +163,7 @@ def test_config3_full_size_beyond_java_int(device, oracle):
         pytest.skip("needs ~100 GiB of device memory")
     n, m, k = 4096, 2048, 1024
     N = n * m * k
-    a_h = _rand(np.float32, n * k, 0, 3, -2.0, 2.0)
-    b_h = _rand(np.float32, m * k, 0, 4, -2.0, 2.0)
+    a_h, b_h = B.cfg3_inputs()   # one uniform stream of seed 3: a, then b
     A, B = DevArray(device, a_h), DevArray(device, b_h)
     bufs = []
     for _ in range(2):

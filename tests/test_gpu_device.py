@@ -107,6 +107,112 @@ def test_out_of_memory_is_reported(device):
     device.restore(t)
 
 
+def test_sizes_that_would_wrap_are_refused_before_any_allocation(device):
+    """n_elems * element size must not wrap (a wrapped allocation would succeed and claim memory it does not have), and a
+    view's element count is checked before each multiplication (eight extents of 2^16 wrap int64 to 0)."""
+    import ctypes as C
+    buf = C.c_void_p()
+    assert L.lib.nk_alloc(device.ctx, L.NK_F64, 1 << 61, C.byref(buf)) == L.NK_ERR_OOM and not buf
+    assert L.lib.nk_alloc(device.ctx, L.NK_F64, 1 << 43, C.byref(buf)) == L.NK_ERR_OOM and not buf     # 64 TiB: the driver refuses
+    assert L.lib.nk_wrap(device.ctx, L.NK_F32, C.c_void_p(256), 1 << 61, C.byref(buf)) == L.NK_ERR_BAD_ARG
+    L.check(L.lib.nk_alloc(device.ctx, L.NK_F32, 16, C.byref(buf)), device.ctx)
+    try:
+        rank = 8
+        cfg = np.array([1 << 16] * rank + [0] * rank + [1] * rank + [0] * rank + [1] * rank, dtype=np.int32)   # stride-0 view, 2^128 elements
+        st = L.lib.nk_unary(device.ctx, L.FUN["relu"], L.NK_F32, rank, buf, cfg.ctypes.data_as(C.POINTER(C.c_int32)),
+                            buf, cfg.ctypes.data_as(C.POINTER(C.c_int32)), -1)
+        assert st == L.NK_ERR_UNSUPPORTED
+        assert b"too large" in L.lib.nk_last_error(device.ctx)
+    finally:
+        L.lib.nk_free(device.ctx, buf)
+
+
+def test_pooled_allocations_are_reused_and_shared_ones_export(device):
+    """nk_alloc / nk_free go through the stream-ordered pool: a freed block comes back for the next request of the same
+    size without a device-wide wait; pooled memory has no IPC handle, nk_alloc_shared memory has."""
+    import ctypes as C
+    ctx = device.ctx
+    n = 1 << 22
+    seen = set()
+    for _ in range(6):
+        b = C.c_void_p()
+        L.check(L.lib.nk_alloc(ctx, L.NK_F32, n, C.byref(b)), ctx)
+        L.check(L.lib.nk_fill(ctx, b, C.c_double(1.0), 0, n), ctx)
+        p = C.c_void_p()
+        L.lib.nk_buf_info(b, C.byref(p), None, None)
+        seen.add(p.value)
+        L.check(L.lib.nk_free(ctx, b), ctx)
+    assert len(seen) <= 2, "freed blocks were not handed out again"
+    handle = (C.c_uint8 * L.NK_IPC_HANDLE_BYTES)()
+    b = C.c_void_p()
+    L.check(L.lib.nk_alloc(ctx, L.NK_F32, n, C.byref(b)), ctx)
+    assert L.lib.nk_ipc_export(ctx, b, handle) == L.NK_ERR_BAD_ARG
+    L.check(L.lib.nk_free(ctx, b), ctx)
+    L.check(L.lib.nk_alloc_shared(ctx, L.NK_F32, n, C.byref(b)), ctx)
+    L.check(L.lib.nk_ipc_export(ctx, b, handle), ctx)
+    assert any(handle)
+    L.check(L.lib.nk_free(ctx, b), ctx)
+
+
+def test_null_arguments_of_a_call_are_refused(device):
+    """Cross_Device_Type_Spec.groovy:221-252: an ExecutionCall with a null tensor argument is an IllegalArgumentException
+    with this very message (AbstractDeviceAlgorithm.java:119-124)."""
+    from neureka_b200 import backend as Bk
+    from neureka_b200.functions import _execute_on_common_device
+    t = Tensor.of(np.float32, [2], [1, 2]).to(device)
+    call = Bk.ExecutionCall([t, None], "+", device, -1)
+    with pytest.raises(ValueError) as e:
+        _execute_on_common_device(call, Bk.backend().implementation_for("+", Bk.BI_ELEMENTWISE))
+    assert "Device arguments may not be null!" in str(e.value)
+    assert "One or more tensor arguments within the given ExecutionCall instance is null." in str(e.value)
+    device.restore(t)
+
+
+def test_device_counts_tensors_and_data_objects(device):
+    """Cross_Device_Type_Spec.groovy:362-413: a stored tensor is one tensor and one data object; a result of an
+    operation on it is another of each; a reshaped view is a new tensor on the same data object; dropping them all
+    brings both counts back."""
+    import gc
+    gc.collect()
+    initial, initial_data = device.number_of_stored(), device.number_of_data_objects()
+    t = Tensor.of(np.float64, [2, 2], [42, 73, 11, 7])
+    assert device.number_of_stored() == initial
+    t.to(device)
+    assert device.number_of_stored() == initial + 1 and device.number_of_data_objects() == initial_data + 1
+    t2 = t * 2
+    assert t2.items.tolist() == [84, 146, 22, 14]
+    assert device.number_of_stored() == initial + 2 and device.number_of_data_objects() == initial_data + 2
+    t3 = t.permute(1, 0)
+    assert device.has(t3)
+    assert device.number_of_stored() == initial + 3 and device.number_of_data_objects() == initial_data + 2
+    for x in (t3, t2, t):
+        device.free(x)
+    del t, t2, t3
+    gc.collect()
+    assert device.number_of_stored() == initial and device.number_of_data_objects() == initial_data
+
+
+def test_a_slice_lives_where_its_parent_lives(device):
+    """Cross_Device_Type_Spec.groovy:415-466 (AbstractDevice.java:92-99): a slice has no device data of its own. Storing
+    the parent outsources the slice with it and adds one data object, not two; here storing the slice first moves its
+    root along (the reference throws "Data parent is not outsourced!" at that point -- in a spec it keeps ignored)."""
+    a = Tensor.of(np.float32, [2, 3], [1, 2, 3, 4, 5, 6])
+    b = a[1:2, 0:3]
+    n_data = device.number_of_data_objects()
+    assert not device.has(a) and not device.has(b)
+    a.to(device)
+    assert a.is_outsourced and b.is_outsourced and device.has(a) and device.has(b)
+    assert device.number_of_data_objects() == n_data + 1
+    assert b.items.tolist() == [4, 5, 6]
+    device.restore(a)
+    assert not device.has(b) and not b.is_outsourced and b.items.tolist() == [4, 5, 6]
+    c = Tensor.of(np.float32, [2, 3], [1, 2, 3, 4, 5, 6])
+    d = c[0:1, 1:3]
+    d.to(device)
+    assert device.has(c) and device.has(d) and device.number_of_data_objects() == n_data + 1
+    device.restore(c)
+
+
 def test_events_order_two_contexts_on_one_device(device):
     """A second context on the same device is a second stream; an event recorded on the first makes the second wait.
     The producer stream fills and squares a buffer many times over (long enough to still be running when the copy is

@@ -159,3 +159,56 @@ def test_sharded_gradients_match_unsharded(tmp_path, world):
                         "--master-port", str(29720 + world), str(script), ROOT], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "GRAD_SHARDED_OK" in r.stdout
+
+
+LOCKSTEP_WORKER = r'''
+import sys
+sys.path.insert(0, sys.argv[1])
+import torch, torch.distributed as dist
+import bench_sharded as S
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+
+# 1. one rank fails while preparing a stage: every rank skips it, nobody enters its collectives
+def prepare():
+    if rank == 1:
+        raise MemoryError("no room on this rank")
+    return "ready"
+try:
+    S._prepared(dist, prepare)
+    raise SystemExit("the stage should have been skipped on every rank")
+except S.StageSkipped as e:
+    assert ("no room" in str(e)) == (rank == 1)
+
+# 2. everybody prepared: a local failure after that point is kept, the rank still enters the stage's collectives
+assert S._prepared(dist, lambda: "ready") == "ready"
+guard = S._Guard()
+calls = []
+def launches():
+    calls.append(1)
+    if rank == 0:
+        raise ValueError("refused launch")
+for _ in range(3):
+    guard.local(launches)                       # raises once on rank 0, is skipped afterwards
+    t = torch.ones(4)
+    dist.all_reduce(t)                          # every rank is here, every time
+    assert float(t[0]) == world
+assert len(calls) == (1 if rank == 0 else 3)
+assert (guard.error is not None) == (rank == 0)
+assert S.agree(dist, guard.error is None) is False   # ... and all ranks report the stage as failed together
+assert S.agree(dist, True) is True
+print(f"LOCKSTEP_OK {rank}")
+dist.destroy_process_group()
+'''
+
+
+def test_a_failing_rank_keeps_its_peers_in_step(tmp_path):
+    """bench_sharded's rule for stages with collectives: skip together when a rank fails while preparing, otherwise
+    record local failures and keep entering the collectives (gloo, world size 2; no GPU involved)."""
+    script = tmp_path / "lockstep_worker.py"
+    script.write_text(LOCKSTEP_WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29731", str(script), ROOT], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "LOCKSTEP_OK 0" in r.stdout and "LOCKSTEP_OK 1" in r.stdout

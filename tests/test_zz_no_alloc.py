@@ -55,8 +55,8 @@ def test_static_sum_rejects_views_beyond_its_fixed_scratch(device):
         L.check(L.lib.nk_fill(device.ctx, buf, 0.5, 0, n), device.ctx)
         L.check(L.lib.nk_sum(device.ctx, L.NK_F32, 1, buf, p, out.buf, 0), device.ctx)
         assert out.read()[0] == pytest.approx(0.5 * n, rel=1e-3)
+        with pytest.raises(ValueError):   # an integer dtype is refused (while the handles are still alive)
+            L.check(L.lib.nk_sum_static(device.ctx, L.NK_I32, 1, out.buf, p, out.buf, 0), device.ctx)
     finally:
         L.lib.nk_free(device.ctx, buf)
         out.free()
-    with pytest.raises(ValueError):
-        L.check(L.lib.nk_sum_static(device.ctx, L.NK_I32, 1, out.buf, p, out.buf, 0), device.ctx)
