@@ -22,7 +22,7 @@ lib = C.CDLL(LIB_PATH)
 NK_OK, NK_ERR_BAD_ARG, NK_ERR_UNSUPPORTED, NK_ERR_OOM, NK_ERR_CUDA, NK_ERR_TIMEOUT, NK_ERR_BOUNDS = range(7)
 NK_F32, NK_F64, NK_I8, NK_I16, NK_I32, NK_I64 = range(6)
 NK_OP_ADD, NK_OP_SUB, NK_OP_MUL, NK_OP_DIV, NK_OP_MOD, NK_OP_POW, NK_OP_IDY, NK_OP_MUL_BOTH = range(8)
-NK_CONV_AUTO, NK_CONV_GENERIC, NK_CONV_TILED, NK_CONV_TMA, NK_CONV_GEMM = range(5)
+NK_CONV_AUTO, NK_CONV_GENERIC, NK_CONV_TILED, NK_CONV_TMA, NK_CONV_GEMM, NK_CONV_TC = range(6)
 NK_IPC_HANDLE_BYTES = 64
 
 FUN_IDS = [

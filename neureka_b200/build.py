@@ -32,6 +32,7 @@ SOURCES = [
     ("nk_ew_unary.cu", ["-fmad=false"]),
     ("nk_conv.cu", []),
     ("nk_conv_gemm.cu", []),
+    ("nk_conv_tc.cu", []),
     ("nk_conv_tiled.cu", []),
     ("nk_conv_tiled_inst_f32_ldgsts.cu", []),
     ("nk_conv_tiled_inst_f32_tma4.cu", []),

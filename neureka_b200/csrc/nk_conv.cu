@@ -168,12 +168,12 @@ extern "C" int nk_conv(nk_ctx* ctx, int32_t dtype, int32_t rank,
     if ((st = nk_view_parse(ctx, "nk_conv(src2)", src2, cfg2, rank, dtype, &v2))) return st;
 
     const int path = ctx->conv_path;
-    if (path == NK_CONV_AUTO || path == NK_CONV_GEMM) {
+    if (path == NK_CONV_AUTO || path == NK_CONV_GEMM || path == NK_CONV_TC) {
         bool handled = false;
-        st = nk_conv_gemm_try(ctx, dtype, drn, v0, src1, v1, src2, v2, d, &handled);
+        st = nk_conv_gemm_try(ctx, dtype, drn, v0, src1, v1, src2, v2, d, &handled);   // sets last_conv_path (GEMM or TC)
         if (st) return st;
-        if (handled) { ctx->last_conv_path = NK_CONV_GEMM; return NK_OK; }
-        if (path == NK_CONV_GEMM) return nk_fail(ctx, NK_ERR_UNSUPPORTED, "nk_conv: the forced kernel family %d does not apply to these views", path);
+        if (handled) return NK_OK;
+        if (path != NK_CONV_AUTO) return nk_fail(ctx, NK_ERR_UNSUPPORTED, "nk_conv: the forced kernel family %d does not apply to these views", path);
     }
     if (path != NK_CONV_GENERIC) {
         bool handled = false;

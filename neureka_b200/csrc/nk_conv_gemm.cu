@@ -12,22 +12,9 @@
 //
 // Plain FP32 / FP64 FMAs on purpose: the parity bar is 1e-5 / 1e-12 against a sum in the tensor's own type; FP64
 // tensor-core MMA has the same rate as the FP64 FMA pipe on this GPU, and a 3xTF32 tcgen05 pipeline is not built.
-#include "nk_internal.h"
+#include "nk_gemm_plan.h"
 
 namespace {
-
-struct GemmDims {
-    int n;                      // dims in this group
-    int64_t ext[NK_MAX_RANK];
-    int64_t sa[NK_MAX_RANK];    // stride in the first table of the group
-    int64_t sb[NK_MAX_RANK];    // stride in the second table of the group
-};
-
-struct GemmPlan {
-    GemmDims m, n, k;           // m: (A, drain)   n: (B, drain)   k: (A, B)
-    int64_t M, N, K;
-    int64_t bA, bB, bO;
-};
 
 // tables: [offA_m | offO_m] (M each), [offB_n | offO_n] (N each), [offA_k | offB_k] (K each)
 __global__ void __launch_bounds__(256) nk_gemm_offsets_kernel(int64_t* __restrict__ tab, GemmPlan p) {
@@ -49,6 +36,15 @@ __global__ void __launch_bounds__(256) nk_gemm_offsets_kernel(int64_t* __restric
         t2[idx] = b;
     }
 }
+
+}  // namespace
+
+int nk_gemm_build_tables(nk_ctx* ctx, const GemmPlan& p, int64_t* tab) {
+    nk_gemm_offsets_kernel<<<nk_grid_for(ctx, p.M + p.N + p.K, 256, 4), 256, 0, ctx->stream>>>(tab, p);
+    return nk_after_launch(ctx, "nk_gemm_offsets_kernel");
+}
+
+namespace {
 
 template <class T> struct GemmTile;
 template <> struct GemmTile<float> { static constexpr int BM = 128, BN = 128, BK = 16, TM = 8, TN = 8; };
@@ -177,8 +173,7 @@ int launch_gemm(nk_ctx* ctx, T* out, const T* A, const T* B, const GemmPlan& p, 
     int st = nk_scratch(ctx, size_t(entries) * sizeof(int64_t), &scratch);
     if (st) return st;
     int64_t* tab = reinterpret_cast<int64_t*>(scratch);
-    nk_gemm_offsets_kernel<<<nk_grid_for(ctx, p.M + p.N + p.K, 256, 4), 256, 0, ctx->stream>>>(tab, p);
-    st = nk_after_launch(ctx, "nk_gemm_offsets_kernel");
+    st = nk_gemm_build_tables(ctx, p, tab);
     if (st) return st;
     const int64_t tiles = ((p.M + C::BM - 1) / C::BM) * ((p.N + C::BN - 1) / C::BN);
     if (tiles > 0x7fffffffLL) return -1;
@@ -189,46 +184,29 @@ int launch_gemm(nk_ctx* ctx, T* out, const T* A, const T* B, const GemmPlan& p, 
 
 }  // namespace
 
-// Forward calls only (d < 0). *handled is set when the call was a contraction and has been launched.
+// Forward calls and deconvolutions. *handled is set when the call was a contraction and has been launched.
 int nk_conv_gemm_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_buf* s1, const NkView& v1, nk_buf* s2, const NkView& v2,
                      int d, bool* handled) {
     *handled = false;
-    if (d >= 0) return NK_OK;
     GemmPlan p;
-    memset(&p, 0, sizeof(p));
-    p.M = p.N = p.K = 1;
-    for (int k = 0; k < v0.rank; k++) {
-        const int64_t a = v1.shape[k], b = v2.shape[k], o = v0.shape[k];
-        if (a == b) {                       // summed away (AbstractCPUConvolution.java:285-308, the a == b branch)
-            if (o != 1) return NK_OK;       // malformed: the generic path reports it
-            if (a == 1) continue;
-            GemmDims& g = p.k;
-            g.ext[g.n] = a; g.sa[g.n] = v1.estride[k]; g.sb[g.n] = v2.estride[k]; g.n++;
-            p.K *= a;
-        } else if (b == 1) {                // only A spans this dim: the output index goes to A
-            if (o != a) return NK_OK;
-            GemmDims& g = p.m;
-            g.ext[g.n] = a; g.sa[g.n] = v1.estride[k]; g.sb[g.n] = v0.estride[k]; g.n++;
-            p.M *= a;
-        } else if (a == 1) {                // only B spans it
-            if (o != b) return NK_OK;
-            GemmDims& g = p.n;
-            g.ext[g.n] = b; g.sa[g.n] = v2.estride[k]; g.sb[g.n] = v0.estride[k]; g.n++;
-            p.N *= b;
-        } else {
-            return NK_OK;                   // a sliding window: not a contraction
-        }
-    }
+    if (!nk_gemm_classify(v0, v1, v2, d, &p)) return NK_OK;
     // small or skinny problems stay on the gather family (one launch, no tables; a 128-wide tile would be mostly empty)
+    const bool forced = ctx->conv_path != NK_CONV_AUTO;   // a forced family skips the "is it worth it" volume test only
     if (p.M < 32 || p.N < 32 || p.K < 16) return NK_OK;
-    if (double(p.M) * double(p.N) * double(p.K) < double(1 << 21)) return NK_OK;
-    p.bA = v1.base; p.bB = v2.base; p.bO = v0.base;
+    if (!forced && double(p.M) * double(p.N) * double(p.K) < double(1 << 21)) return NK_OK;
     int st;
+    if (dtype == NK_F32 && ctx->conv_path != NK_CONV_GEMM) {   // the tensor-core family first; it declines what it cannot take
+        st = nk_conv_tc_try(ctx, drn, s1, s2, p, handled);
+        if (st) return st;
+        if (*handled) { ctx->last_conv_path = NK_CONV_TC; return NK_OK; }
+    }
+    if (ctx->conv_path == NK_CONV_TC) return NK_OK;
     const bool narrow = s1->n_elems < (int64_t(1) << 31) && s2->n_elems < (int64_t(1) << 31);   // every gather offset fits 32 bits
     if (dtype == NK_F32) st = launch_gemm<float>(ctx, (float*)drn->ptr, (const float*)s1->ptr, (const float*)s2->ptr, p, narrow);
     else st = launch_gemm<double>(ctx, (double*)drn->ptr, (const double*)s1->ptr, (const double*)s2->ptr, p, narrow);
     if (st == -1) return NK_OK;
     if (st) return st;
+    ctx->last_conv_path = NK_CONV_GEMM;
     *handled = true;
     return NK_OK;
 }

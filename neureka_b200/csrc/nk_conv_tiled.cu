@@ -60,6 +60,22 @@ int nk_tma_encode(nk_ctx* ctx, int dtype, const TmaImage& img, int box_w, int bo
     return NK_OK;
 }
 
+// A dense 2-D F32 array [rows, cols] (row pitch in bytes, a multiple of 16) as a tensor map with a box of box_cols x
+// box_rows elements and the given shared-memory swizzle (0 none, 1 = 32 B, 2 = 64 B, 3 = 128 B). -1 when the driver's
+// encoder is missing or refuses.
+int nk_tma_encode_2d_f32(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, int box_cols, int box_rows, int swizzle,
+                         CUtensorMap* out) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return -1;
+    cuuint64_t dims[2] = {cols, rows}, strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {cuuint32_t(box_cols), cuuint32_t(box_rows)}, estr[2] = {1, 1};
+    const CUtensorMapSwizzle sw = swizzle == 3 ? CU_TENSOR_MAP_SWIZZLE_128B : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                : swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? NK_OK : -1;
+}
+
 // Tensor map description of a whole view: X, optionally Y, then the outer dims (innermost first). False when the
 // view cannot be described (unaligned base, strides that are not positive multiples of 16 bytes).
 static bool nk_describe_for_tma(const nk_buf* buf, const NkView& v, size_t es, bool has_y, int n_outer, TmaImage* img) {

@@ -435,7 +435,7 @@ extern "C" int nk_host_free(void* host) {
 // ------------------------------------------------------------------------------------------------
 extern "C" int nk_set_conv_path(nk_ctx* ctx, int32_t path) {
     NK_CHECK_CTX(ctx);
-    if (path < NK_CONV_AUTO || path > NK_CONV_GEMM) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_set_conv_path: unknown path %d", path);
+    if (path < NK_CONV_AUTO || path > NK_CONV_TC) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_set_conv_path: unknown path %d", path);
     ctx->conv_path = path;
     return NK_OK;
 }

@@ -9,7 +9,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
-import baseline_configs as B
+import baseline_configs as BC
 from helpers import DevArray, assert_conv_close, cfgp, gpu_conv
 from neureka_b200 import _lib as L
 from neureka_b200.ndconf import NDConfiguration as ND
@@ -18,7 +18,7 @@ pytestmark = pytest.mark.gpu
 
 
 def test_config1_conv2d_matches_the_simple_cpu_convolution(device, oracle):
-    a, k = B.cfg1_inputs()   # one stream of seed 42: the image, then the kernel
+    a, k = BC.cfg1_inputs()   # one stream of seed 42: the image, then the kernel
     co, ca, ck = ND.of_shape([252, 252]), ND.of_shape([256, 256]), ND.of_shape([5, 5])
     ref = np.zeros(co.size, dtype=np.float32)
     assert oracle.conv(ref, co.as_inline_array(), a, ca.as_inline_array(), k, ck.as_inline_array()) == 1   # SimpleCPUConvolution path
@@ -30,7 +30,7 @@ def test_config1_conv2d_matches_the_simple_cpu_convolution(device, oracle):
 
 
 def test_config2_channel_collapsing_conv(device, oracle):
-    a, k = B.cfg2_inputs()   # one N(0,1) stream of seed 7: the image, then the kernel
+    a, k = BC.cfg2_inputs()   # one N(0,1) stream of seed 7: the image, then the kernel
     co, ca, ck = ND.of_shape([1, 510, 510]), ND.of_shape([64, 512, 512]), ND.of_shape([64, 3, 3])
     ref = np.zeros(co.size, dtype=np.float32)
     assert oracle.conv(ref, co.as_inline_array(), a, ca.as_inline_array(), k, ck.as_inline_array(), threads=8) == 0   # general nd path
@@ -42,7 +42,7 @@ def test_config2_channel_collapsing_conv(device, oracle):
 
 
 def test_config4_f64_forward_and_both_gradients(device, oracle):
-    v, k = B.cfg4_inputs()
+    v, k = BC.cfg4_inputs()
     cv, ck, cy = ND.of_shape([128] * 3), ND.of_shape([7] * 3), ND.of_shape([122] * 3)
     iv, ik, iy = cv.as_inline_array(), ck.as_inline_array(), cy.as_inline_array()
     av, ak = np.abs(v), np.abs(k)
@@ -111,8 +111,8 @@ def test_config5_full_size_on_one_gpu(device, oracle):
     """4 GiB input: oracle spot checks on sampled output ranges, plus properties that hold at any size."""
     a_shape, k_shape, o_shape = [8, 32, 2048, 2048], [1, 32, 5, 5], [8, 1, 2044, 2044]
     n_in, n_out = int(np.prod(a_shape)), int(np.prod(o_shape))
-    a = B.cfg5_image()
-    k = B.cfg5_kernel()
+    a = BC.cfg5_image()
+    k = BC.cfg5_kernel()
     A = DevArray(device, a)
     K = DevArray(device, k)
     O = DevArray(device, np.zeros(1, dtype=np.float32))
@@ -163,7 +163,7 @@ def test_config3_full_size_beyond_java_int(device, oracle):
         pytest.skip("needs ~100 GiB of device memory")
     n, m, k = 4096, 2048, 1024
     N = n * m * k
-    a_h, b_h = B.cfg3_inputs()   # one uniform stream of seed 3: a, then b
+    a_h, b_h = BC.cfg3_inputs()   # one uniform stream of seed 3: a, then b
     A, B = DevArray(device, a_h), DevArray(device, b_h)
     bufs = []
     for _ in range(2):
