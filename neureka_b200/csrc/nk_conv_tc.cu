@@ -18,9 +18,15 @@
 //   3. nk_conv_tc_kernel       -- persistent, warp-specialised: one producer thread issues cp.async.bulk.tensor (TMA,
 //      64-byte swizzle, no multicast, this GPU's memory only) into a 4-stage ring of {A_hi, A_lo, B_hi, B_lo} panels
 //      of 16 k each; one thread issues tcgen05.mma (kind::tf32, M = 128, N = 256, K = 8; six per stage) into one of
-//      two 128 x 256 F32 accumulators in tensor memory and hands stages back with tcgen05.commit; four warps read
-//      the finished accumulator with tcgen05.ld and scatter it through the drain's tables while the next tile's
-//      products already run into the other accumulator.
+//      two 128 x 256 F32 accumulators in tensor memory and hands stages back with tcgen05.commit; sixteen warps read
+//      finished accumulators with tcgen05.ld and scatter the tile through the drain's tables.
+//
+// Accumulation. The tensor core adds each product block into the accumulator with truncation (measured: a sum of K
+// same-signed terms came out low by K/8 * 3 * 2^-25 relative, 9e-5 at K = 8192). A tile's sum over k is therefore cut
+// into chunks of 128 k (48 accumulations, bias below 1.5e-6): the two accumulators alternate chunk by chunk, and the
+// sixteen epilogue warps add every finished chunk into per-thread F32 running sums with ordinary round-to-nearest adds
+// while the next chunk's products already run into the other accumulator. The running sums of a tile (64 per thread)
+// go to the drain after its last chunk.
 // Every mbarrier wait is bounded (nk_mbar_wait_bounded); on expiry the waiter raises the CTA's abort word and the
 // host-visible status, all roles leave their loops, outstanding copies and tensor-core work are waited for (bounded),
 // tensor memory is released and the kernel returns; the host then reports NK_ERR_TIMEOUT.
@@ -39,8 +45,10 @@ constexpr int TC_A_PART = TC_BM * TC_BK * 4;                 // 8 KiB: one of A_
 constexpr int TC_B_PART = TC_BN * TC_BK * 4;                 // 16 KiB
 constexpr int TC_STAGE_BYTES = 2 * TC_A_PART + 2 * TC_B_PART;   // 48 KiB
 constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
-constexpr int TC_THREADS = 192;                              // warp 0 producer, warp 1 tensor-core issue, warps 2..5 epilogue
+constexpr int TC_THREADS = 576;                              // warp 0 producer, warp 1 tensor-core issue, warps 2..17 epilogue
+constexpr int TC_EPI_COLS = 64;                              // accumulator columns an epilogue warp owns (4 warps per lane quarter)
 constexpr unsigned TC_TMEM_COLS = 512;                       // two 128 x 256 F32 accumulators
+constexpr int TC_KC = 8;                                     // k blocks (of 16) per accumulation chunk
 
 // ---- split: v -> hi = tf32(v), lo = tf32(v - hi) ------------------------------------------------------------------------
 __device__ __forceinline__ void tc_split(float v, float* hi, float* lo) {
@@ -125,14 +133,11 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
-    uint32_t* r = reinterpret_cast<uint32_t*>(v);
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+// 16 consecutive accumulator columns of this thread's lane (32 lanes x 32 bits per warp and column)
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-                   "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-                   "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
@@ -168,7 +173,7 @@ nk_conv_tc_kernel(float* __restrict__ out, const __grid_constant__ CUtensorMap m
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; s++) { nk_mbar_init(&full_bar[s], 1); nk_mbar_init(&empty_bar[s], 1); }
-        for (int b = 0; b < 2; b++) { nk_mbar_init(&acc_full[b], 1); nk_mbar_init(&acc_empty[b], 4); }
+        for (int b = 0; b < 2; b++) { nk_mbar_init(&acc_full[b], 1); nk_mbar_init(&acc_empty[b], 16); }
         nk_mbar_init(drain_bar, 1);
         *abort_word = 0;
         nk_fence_barrier_init();
@@ -221,33 +226,37 @@ nk_conv_tc_kernel(float* __restrict__ out, const __grid_constant__ CUtensorMap m
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // ---- tensor-core issue: per stage two k-steps of 8, three products each (small terms first) ----
-            int it = 0, tl = 0;
+            // ---- tensor-core issue: per stage two k-steps of 8, three products each (small terms first); a new
+            // accumulator every TC_KC stages ----
+            int it = 0, ch = 0;
             bool ok = true;
-            for (int64_t t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, tl++) {
-                const int b = tl & 1;
-                ok = wait_or_abort(&acc_empty[b], ((unsigned(tl) >> 1) & 1u) ^ 1u);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t acc = tmem_base + uint32_t(b) * TC_BN;
-                for (int kb = 0; kb < p.k_blocks && ok; kb++, it++) {
-                    const int s = it % TC_STAGES;
-                    ok = wait_or_abort(&full_bar[s], (unsigned(it) / TC_STAGES) & 1u);
+            for (int64_t t = blockIdx.x; t < p.tiles && ok; t += gridDim.x) {
+                for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += TC_KC, ch++) {
+                    const int b = ch & 1;
+                    ok = wait_or_abort(&acc_empty[b], ((unsigned(ch) >> 1) & 1u) ^ 1u);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem + size_t(s) * TC_STAGE_BYTES);
+                    const uint32_t acc = tmem_base + uint32_t(b) * TC_BN;
+                    const int kb1 = kb0 + TC_KC < p.k_blocks ? kb0 + TC_KC : p.k_blocks;
+                    for (int kb = kb0; kb < kb1 && ok; kb++, it++) {
+                        const int s = it % TC_STAGES;
+                        ok = wait_or_abort(&full_bar[s], (unsigned(it) / TC_STAGES) & 1u);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem + size_t(s) * TC_STAGE_BYTES);
 #pragma unroll
-                    for (int ks = 0; ks < TC_BK / 8; ks++) {
-                        const uint32_t koff = uint32_t(ks) * 32u;   // 8 F32 further along the 64-byte row
-                        const uint64_t a_hi = tc_smem_desc(sa + koff), a_lo = tc_smem_desc(sa + TC_A_PART + koff);
-                        const uint64_t b_hi = tc_smem_desc(sa + 2 * TC_A_PART + koff), b_lo = tc_smem_desc(sa + 2 * TC_A_PART + TC_B_PART + koff);
-                        tc_mma(acc, a_lo, b_hi, (kb | ks) != 0 ? 1u : 0u);
-                        tc_mma(acc, a_hi, b_lo, 1u);
-                        tc_mma(acc, a_hi, b_hi, 1u);
+                        for (int ks = 0; ks < TC_BK / 8; ks++) {
+                            const uint32_t koff = uint32_t(ks) * 32u;   // 8 F32 further along the 64-byte row
+                            const uint64_t a_hi = tc_smem_desc(sa + koff), a_lo = tc_smem_desc(sa + TC_A_PART + koff);
+                            const uint64_t b_hi = tc_smem_desc(sa + 2 * TC_A_PART + koff), b_lo = tc_smem_desc(sa + 2 * TC_A_PART + TC_B_PART + koff);
+                            tc_mma(acc, a_lo, b_hi, (kb > kb0 || ks != 0) ? 1u : 0u);
+                            tc_mma(acc, a_hi, b_lo, 1u);
+                            tc_mma(acc, a_hi, b_hi, 1u);
+                        }
+                        tc_commit(&empty_bar[s]);       // the stage goes back to the producer when these products are done
                     }
-                    tc_commit(&empty_bar[s]);       // the stage goes back to the producer when these products are done
+                    if (ok) tc_commit(&acc_full[b]);    // ... and the chunk to the epilogue
                 }
-                if (ok) tc_commit(&acc_full[b]);    // ... and the tile to the epilogue
             }
             if (!ok || *abort_word) {
                 tc_commit(drain_bar);               // nothing of this CTA may still run on the tensor cores at release time
@@ -255,37 +264,53 @@ nk_conv_tc_kernel(float* __restrict__ out, const __grid_constant__ CUtensorMap m
             }
         }
     } else {
-        // ---- epilogue: warp w reads the 32 accumulator lanes of its quarter (w % 4), 32 columns at a time ----
-        const int q = warp & 3;
-        int tl = 0;
+        // ---- epilogue: warps 2..17; warp w reads the 32 accumulator lanes of its quarter (w % 4) and the 64 columns of
+        // part (w - 2) / 4, adds every finished chunk into its running sums and stores them after the tile's last chunk ----
+        const int q = warp & 3, half = (warp - 2) >> 2;
+        int ch = 0;
         bool ok = true;
-        for (int64_t t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, tl++) {
-            const int b = tl & 1;
+        for (int64_t t = blockIdx.x; t < p.tiles && ok; t += gridDim.x) {
             const int64_t m = int64_t(t % p.tiles_m) * TC_BM + q * 32 + lane;
-            const int64_t n0 = int64_t(t / p.tiles_m) * TC_BN;
-            ok = wait_or_abort(&acc_full[b], (unsigned(tl) >> 1) & 1u);
-            if (!ok) break;
-            tc_fence_after();
-            const int64_t row = m < p.M ? p.bO + p.offOm[m] : 0;
-#pragma unroll 1
-            for (int c = 0; c < TC_BN / 32; c++) {
-                float v[32];
-                tc_ld32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b) * TC_BN + uint32_t(c) * 32u, v);
-                const int64_t n = n0 + c * 32;
-                if (m >= p.M || n >= p.N) continue;
-                if (p.out_vec && n + 32 <= p.N) {
-                    float4* dst = reinterpret_cast<float4*>(out + row + p.offOn[0] + n);
+            const int64_t n0 = int64_t(t / p.tiles_m) * TC_BN + half * TC_EPI_COLS;
+            float sum[TC_EPI_COLS];
+            for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += TC_KC, ch++) {
+                const int b = ch & 1;
+                ok = wait_or_abort(&acc_full[b], (unsigned(ch) >> 1) & 1u);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t src = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(b) * TC_BN + uint32_t(half) * TC_EPI_COLS;
 #pragma unroll
-                    for (int j = 0; j < 8; j++) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                for (int c = 0; c < TC_EPI_COLS / 16; c++) {
+                    uint32_t v[16];
+                    tc_ld16(src + uint32_t(c) * 16u, v);
+                    if (kb0 == 0) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) sum[c * 16 + j] = __uint_as_float(v[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) sum[c * 16 + j] += __uint_as_float(v[j]);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) nk_mbar_arrive(&acc_empty[b]);
+            }
+            if (!ok || m >= p.M) continue;
+            const int64_t row = p.bO + p.offOm[m];
+#pragma unroll
+            for (int c = 0; c < TC_EPI_COLS / 32; c++) {
+                const int64_t n = n0 + c * 32;
+                if (n >= p.N) continue;
+                if (p.out_vec && n + 32 <= p.N) {
+                    float4* dst = reinterpret_cast<float4*>(out + row + n);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) dst[j] = make_float4(sum[c * 32 + 4 * j], sum[c * 32 + 4 * j + 1], sum[c * 32 + 4 * j + 2], sum[c * 32 + 4 * j + 3]);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; j++)
-                        if (n + j < p.N) out[row + p.offOn[n + j]] = v[j];
+                        if (n + j < p.N) out[row + p.offOn[n + j]] = sum[c * 32 + j];
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) nk_mbar_arrive(&acc_empty[b]);
         }
     }
 

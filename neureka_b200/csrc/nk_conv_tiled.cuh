@@ -19,10 +19,15 @@
 //
 // Launch shapes (chosen by nk_launch_tiled from the tile count and the kernel's real occupancy):
 //   * one tile per CTA, the hardware scheduling the CTAs -- a few tiles per resident CTA slot;
-//   * persistent walk -- many tiles per slot: the grid is one resident wave, CTA b takes tiles b, b + grid, ...; the
-//     producer warp keeps loading across tile boundaries; tiles with their own weights select one of the weight
-//     sets staged at once; for one-channel tiles (RING) the compute warps take tile positions from a ring the
-//     producer fills instead of decoding the tile index;
+//   * balanced persistent walk (TMA, two sliding dims, no channel split) -- the output is a list of column strips
+//     (outer coordinate x 128-bit-per-lane column block), each OH rows high; the rows of all strips, laid end to end,
+//     are dealt to one resident wave of CTAs in equal contiguous ranges (to the row), and a CTA walks its range in
+//     chunks of up to TH rows: a chunk of h rows gives every warp ceil(h / 8) rows (the multiply-add loop exists once
+//     per rows-per-warp value 1..RH), its tile load uses the tensor map whose box is 8 * ceil(h / 8) + KH - 1 rows high.
+//     No whole-tile rounding: every CTA finishes within one chunk row of the others whatever the row count is. The
+//     producer warp keeps loading across chunk boundaries; strips with their own weights select one of the weight
+//     sets staged at once; for one-channel chunks (RING) the compute warps take chunk positions from a ring the
+//     producer fills instead of decoding them;
 //   * channel split -- fewer tiles than slots and many channels: up to 8 parts of a tile form a thread-block cluster
 //     and add their partial tiles through distributed shared memory; more parts go through scratch and a finish
 //     kernel. Both add in part order, so the result is deterministic and the same on either path.
@@ -49,8 +54,8 @@ struct TiledPlan {
     int64_t bI, bK, bO;
     int tilesX, tilesY, splits;
     int remote_out;   // the drain lives on another GPU (stores cross NVLink)
-    int persist;      // TMA family: the grid is one resident wave and every CTA walks tiles blockIdx.x, +gridDim.x, ...
-    int64_t tiles_total;
+    int persist;      // TMA family: the grid is one resident wave; CTA b walks rows [b, b + 1) * rows_total / grid of the strips laid end to end
+    int64_t rows_total;   // strips * OH
     int wsets;        // persistent walk over tiles whose weights differ: weight sets staged at once (1 = same weights everywhere)
     int cluster;   // channel-split CTAs of a tile form one thread-block cluster and add their tiles through shared memory
     int vec;       // LDGSTS: 16-byte global->shared copies are legal for every chunk
@@ -111,20 +116,24 @@ struct TiledCfg {
     }
 };
 
-// RING (persistent walk over short tiles only): the compute warps take each tile's position from a ring the producer
-// thread fills instead of decoding the tile index themselves. A compile-time switch: with the ring code merely present
-// the long-tile launches measured 3 % slower (register allocation of the main loop), so they get a kernel without it.
+// The tensor maps of a launch: entry r - 1 has a box of 8 * r + KH - 1 rows (r = rows per warp of a chunk).
+struct TmapSet { CUtensorMap m[8]; };
+template <int N> struct NkRows { static constexpr int value = N; };
+
+// RING (persistent walk over short chunks only): the compute warps take each chunk's position from a ring the producer
+// thread fills instead of decoding it themselves. A compile-time switch: with the ring code merely present
+// the long-chunk launches measured 3 % slower (register allocation of the main loop), so they get a kernel without it.
 template <class T, int KH, int KW, int RH, bool TMA, bool RING = false>
 __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __restrict__ out, T* __restrict__ partial,
                                                             const T* __restrict__ I, const T* __restrict__ K,
-                                                            const TiledPlan p, const __grid_constant__ CUtensorMap tmap) {
+                                                            const TiledPlan p, const __grid_constant__ TmapSet tmaps) {
     using C = TiledCfg<T, KH, KW, RH>;
     constexpr int CW = C::CW, TW = C::TW, TH = C::TH, SW = C::SW, SH = C::SH, STAGES = C::STAGES, NS = C::NS, WPAD = C::WPAD;
     extern __shared__ __align__(128) unsigned char nk_smem[];
     unsigned char* stage_base = nk_smem;
     uint64_t* mbar = reinterpret_cast<uint64_t*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES);
-    // persistent walk: the producer thread publishes where each tile lives (x0, y0, weight set, drain base), 32 bytes
-    // per tile in a ring of STAGES + 1 entries; the compute warps pick an entry up after the tile's first load landed
+    // persistent walk: the producer thread publishes where each chunk lives (x0, y0, weight set, rows, drain base), 32 bytes
+    // per chunk in a ring of STAGES + 1 entries; the compute warps pick an entry up after the chunk's first load landed
     int4* tinfo = reinterpret_cast<int4*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES + 128);
     T* wsm = reinterpret_cast<T*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES + 384);
     // channel table, 32 bytes per channel: image offset, kernel offset, then the tile's tensor-map coordinates 1..4
@@ -136,20 +145,23 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
 
     // ---- which tile / outer coordinate / channel range ----------------------------------------------------------
     // One tile per CTA (the parts of a channel split are neighbours: one cluster), or -- persistent -- a walk over
-    // tiles blockIdx.x, blockIdx.x + gridDim.x, ... with the load pipeline running on across tile boundaries.
+    // the CTA's range of strip rows with the load pipeline running on across chunk boundaries.
     const int split = p.persist ? 0 : int(blockIdx.x % unsigned(p.splits));
-    const int64_t tile_first = p.persist ? int64_t(blockIdx.x) : int64_t(blockIdx.x / unsigned(p.splits));
-    const int64_t tile_step = gridDim.x;
+    const int64_t tile_first = p.persist ? 0 : int64_t(blockIdx.x / unsigned(p.splits));
+    // persistent: this CTA's rows of the strips laid end to end
+    const int64_t r_lo = p.persist ? (int64_t(blockIdx.x) * p.rows_total) / int64_t(gridDim.x) : 0;
+    const int64_t r_hi = p.persist ? (int64_t(blockIdx.x + 1) * p.rows_total) / int64_t(gridDim.x) : 0;
     int64_t baseI, baseK, baseO;
     int pidx[NK_TILED_MAX_OUTER];
     int x0, y0;
+    int rh_cur = RH;        // rows per warp of the chunk / tile this thread stands on
+    int y_end = p.OH;       // first row below it
     int wset = 0;   // which of the staged weight sets the current tile uses (outer output dims that move the kernel)
-    // Takes a tile index apart with divisions (once per thread; the producer thread of a persistent CTA steps on digit by digit, see below).
-    auto tile_set = [&](int64_t tile) {
-        const int tx = int(tile % p.tilesX); tile /= p.tilesX;
-        const int ty = int(tile % p.tilesY); tile /= p.tilesY;
+    // Places the thread on column block tx of the outer coordinate `outer` (divisions: once per thread, and once per chunk
+    // of long chunks; the producer thread of a persistent CTA steps on digit by digit instead, see below).
+    auto strip_set = [&](int tx, int64_t outer) {
         baseI = p.bI; baseK = p.bK; baseO = p.bO;
-        int64_t rem = tile;
+        int64_t rem = outer;
         int ws = 0, wm = 1;
         for (int k = p.n_outer - 1; k >= 0; k--) {
             const int idx = int(rem % p.oext[k]);
@@ -160,10 +172,30 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         }
         wset = p.wsets > 1 ? ws : 0;
         x0 = tx * TW - p.xoff;
-        y0 = ty * TH;
     };
-    tile_set(tile_first);
-    const int64_t pflat = tile_first / (int64_t(p.tilesX) * p.tilesY);   // used by the two-pass split path (one tile per CTA)
+    // The chunk that starts at row r of the end-to-end rows: at most TH rows, never across a strip's end or the range's end.
+    auto chunk_rows = [&](int y, int64_t r) -> int {
+        int h = p.OH - y;
+        if (h > TH) h = TH;
+        if (int64_t(h) > r_hi - r) h = int(r_hi - r);
+        return h;
+    };
+    int64_t pflat = 0;      // flat outer index: used by the two-pass split path (one tile per CTA)
+    if (p.persist) {
+        const int64_t strip = r_lo / p.OH;
+        y0 = int(r_lo - strip * p.OH);
+        strip_set(int(strip % p.tilesX), strip / p.tilesX);
+        const int h = r_lo < r_hi ? chunk_rows(y0, r_lo) : 0;
+        rh_cur = h > 0 ? (h + 7) >> 3 : 1;
+        y_end = y0 + h;
+    } else {
+        int64_t tile = tile_first;
+        const int tx = int(tile % p.tilesX); tile /= p.tilesX;
+        const int ty = int(tile % p.tilesY); tile /= p.tilesY;
+        pflat = tile;
+        strip_set(tx, tile);
+        y0 = ty * TH;
+    }
     const int cper = (p.NQ + p.splits - 1) / p.splits;
     const int c_begin = split * cper;
     const int c_end = (c_begin + cper < p.NQ) ? c_begin + cper : p.NQ;
@@ -199,12 +231,13 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         }
         return make_int4(b[0], b[1], b[2], b[3]);
     };
-    auto tma_fire = [&](int stage, int c1, int c2, int c3, int c4) {
+    auto tma_fire = [&](int stage, int rh, int c1, int c2, int c3, int c4) {
         // without a row dim in the map the box is a single row; the other tile rows are never stored from
-        nk_mbar_expect_tx(&full_bar[stage], unsigned((p.has_y ? SH : 1) * SW * sizeof(T)));
-        nk_tma_load5(stage_base + size_t(stage) * C::STAGE_BYTES, &tmap, &full_bar[stage], p.tma_nd, x0 - p.padX, c1, c2, c3, c4);
+        nk_mbar_expect_tx(&full_bar[stage], unsigned((p.has_y ? 8 * rh + KH - 1 : 1) * SW * sizeof(T)));
+        nk_tma_load5(stage_base + size_t(stage) * C::STAGE_BYTES, &tmaps.m[rh - 1], &full_bar[stage], p.tma_nd, x0 - p.padX, c1, c2, c3, c4);
         issued++;
     };
+    const bool have_work = !p.persist || r_lo < r_hi;
     if (TMA && tid == 256) {
         // the producer thread sets the barriers up and requests the first tiles right away, so that they travel
         // while the other warps stage the weights; everybody else meets the barriers only after the __syncthreads below
@@ -213,10 +246,10 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         nk_fence_barrier_init();
         nk_fence_proxy_async();
         const int4 tb = tile_coords();
-        for (int it = 0; it < STAGES && it < n_it; it++) {
+        for (int it = 0; it < STAGES && it < n_it && have_work; it++) {
             int cc[4];
             chan_coords(c_begin + it, cc);
-            tma_fire(it, cc[0] + tb.x, cc[1] + tb.y, cc[2] + tb.z, cc[3] + tb.w);
+            tma_fire(it, rh_cur, cc[0] + tb.x, cc[1] + tb.y, cc[2] + tb.z, cc[3] + tb.w);
         }
     }
 
@@ -241,7 +274,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         const int ws = e / per_set, r = e - ws * per_set;
         const int c = c_begin + r / WPAD, t = r % WPAD;
         int64_t kb = baseK;   // one set: the weights of this CTA's (only, or every) tile
-        if (p.wsets > 1) {    // several: set ws belongs to the outer output indices that tile_set() folds into ws
+        if (p.wsets > 1) {    // several: set ws belongs to the outer output indices that strip_set() folds into ws
             kb = p.bK;
             int rem = ws;
             for (int k = p.n_outer - 1; k >= 0; k--)
@@ -298,9 +331,11 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
 
     __syncthreads();   // weights + table + barrier init visible
 
-    // One channel's worth of multiply-adds for this thread (tile rows warp*RH .. +RH, columns lane*CW .. +CW).
-    auto consume = [&](int stage, int c) {
-        const T* tile = reinterpret_cast<const T*>(stage_base + size_t(stage) * C::STAGE_BYTES) + (warp * RH) * SW + lane * CW;
+    // One channel's worth of multiply-adds for this thread, RHC rows per warp (tile rows warp*RHC .. +RHC, columns
+    // lane*CW .. +CW). The order of the additions into one output does not depend on RHC: channel, then ky, then kx.
+    auto consume = [&](auto rows_tag, int stage, int c) {
+        constexpr int RHC = decltype(rows_tag)::value;
+        const T* tile = reinterpret_cast<const T*>(stage_base + size_t(stage) * C::STAGE_BYTES) + (warp * RHC) * SW + lane * CW;
         const T* wc = wsm + (size_t(wset) * p.NQ + c) * WPAD;
         T w[C::WREG ? WPAD : CW];
         if (C::WREG) {
@@ -311,7 +346,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             }
         }
 #pragma unroll
-        for (int j = 0; j < RH + KH - 1; j++) {
+        for (int j = 0; j < RHC + KH - 1; j++) {
             T seg[NS];
 #pragma unroll
             for (int v = 0; v < NS / CW; v++) {
@@ -319,7 +354,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                 else *reinterpret_cast<double2*>(&seg[v * CW]) = *reinterpret_cast<const double2*>(tile + j * SW + v * CW);
             }
 #pragma unroll
-            for (int i = 0; i < RH; i++) {
+            for (int i = 0; i < RHC; i++) {
                 const int ky = j - i;
                 if (ky >= 0 && ky < KH) {
 #pragma unroll
@@ -332,15 +367,29 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             }
         }
     };
+    // the same for a rows-per-warp value known only at run time (chunks of a balanced walk)
+    auto consume_rows = [&](int rh, int stage, int c) {
+        if constexpr (!TMA) { consume(NkRows<RH>{}, stage, c); return; }
+        switch (rh) {
+            case 1: consume(NkRows<1>{}, stage, c); break;
+            case 2: if constexpr (RH >= 2) consume(NkRows<2>{}, stage, c); break;
+            case 3: if constexpr (RH >= 3) consume(NkRows<3>{}, stage, c); break;
+            case 4: if constexpr (RH >= 4) consume(NkRows<4>{}, stage, c); break;
+            case 5: if constexpr (RH >= 5) consume(NkRows<5>{}, stage, c); break;
+            case 6: if constexpr (RH >= 6) consume(NkRows<6>{}, stage, c); break;
+            case 7: if constexpr (RH >= 7) consume(NkRows<7>{}, stage, c); break;
+            default: if constexpr (RH >= 8) consume(NkRows<8>{}, stage, c); break;
+        }
+    };
 
-    // Stores this thread's RH x CW results of the tile the thread currently stands on: into the drain, or -- two-pass
-    // channel split -- into this part's plane of the scratch buffer.
+    // Stores this thread's results of the tile / chunk the thread currently stands on (rh_cur rows per warp, rows below
+    // y_end only): into the drain, or -- two-pass channel split -- into this part's plane of the scratch buffer.
     auto store_tile = [&]() {
         const int ox = x0 + lane * CW;
 #pragma unroll
         for (int i = 0; i < RH; i++) {
-            const int oy = y0 + warp * RH + i;
-            if (oy >= p.OH || ox >= p.OW || ox + CW <= 0) continue;
+            const int oy = y0 + warp * rh_cur + i;
+            if (i >= rh_cur || oy >= y_end || ox >= p.OW || ox + CW <= 0) continue;
             T* dst;
             bool vec_ok;
             if (p.splits == 1) {
@@ -374,23 +423,23 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             return r > 0;
         };
         if (warp == 8) {
-            if (lane == 0) {
+            if (lane == 0 && have_work) {
                 // `issued` counts tile loads over the CTA's whole life: load g uses stage g % STAGES in round g / STAGES.
-                // A tile index is a mixed-radix number (tx | ty | outer output indices, last outer dim fastest); the
-                // walk adds gridDim.x to it digit by digit with carry -- a few adds and compares per tile, no division.
-                // Everything the per-tile step needs sits in registers under compile-time indices (j counts the outer
-                // dims from the last one): the step is a few dozen instructions, the producer's time per tile bounds short tiles.
-                constexpr int NO = NK_TILED_MAX_OUTER, NDIG = 2 + NO;
-                int dg[NDIG], sg[NDIG], rx[NDIG], wmj[NO];
+                // Persistent walk: after a chunk of h rows the producer moves h rows down its strip; at the strip's end it
+                // steps to the next strip, a mixed-radix number (tx | outer output indices, last outer dim fastest) that
+                // it counts up by one with carry -- adds and compares only, no division. Everything the step needs sits in
+                // registers under compile-time indices (j counts the outer dims from the last one): the producer's time
+                // per chunk bounds short chunks.
+                constexpr int NO = NK_TILED_MAX_OUTER, NDIG = 1 + NO;
+                int dg[NDIG], rx[NDIG], wmj[NO];
                 long long osj[NO];
                 bool foli[NO];
                 if (p.persist) {
-                    int64_t t = tile_first, st = tile_step;
+                    int64_t t = r_lo / p.OH;
 #pragma unroll
                     for (int i = 0; i < NDIG; i++) {
-                        rx[i] = i == 0 ? p.tilesX : i == 1 ? p.tilesY : ((i - 2) < p.n_outer ? int(p.oext[p.n_outer - 1 - (i - 2)]) : 1);
+                        rx[i] = i == 0 ? p.tilesX : ((i - 1) < p.n_outer ? int(p.oext[p.n_outer - 1 - (i - 1)]) : 1);
                         dg[i] = int(t % rx[i]); t /= rx[i];
-                        sg[i] = int(st % rx[i]); st /= rx[i];
                     }
                     int wm = 1;
 #pragma unroll
@@ -405,36 +454,45 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                     }
                 }
                 bool ok = true;
-                int64_t tile = tile_first;
-                int tile_no = 0;
-                bool announce = false;      // a new tile's info still has to go into the ring (after the stage came free)
-                int c = c_begin + issued;   // the first loads of the first tile were requested in the prologue
+                int64_t r = r_lo;           // first row of the chunk being loaded
+                int h = y_end - y0;         // its rows (persistent)
+                int rh = rh_cur;
+                int chunk_no = 0;
+                bool announce = false;      // a new chunk's info still has to go into the ring (after the stage came free)
+                int c = c_begin + issued;   // the first loads of the first chunk were requested in the prologue
                 int4 tb = tile_coords();
                 while (ok) {
                     if (c >= c_end) {
-                        tile += tile_step;
-                        if (!p.persist || tile >= p.tiles_total) break;
-                        int carry = 0;
+                        if (!p.persist) break;
+                        r += h;
+                        if (r >= r_hi) break;
+                        y0 += h;
+                        if (y0 >= p.OH) {   // next strip
+                            y0 = 0;
+                            int carry = 1;
 #pragma unroll
-                        for (int i = 0; i < NDIG; i++) {
-                            const int v = dg[i] + sg[i] + carry;
-                            carry = v >= rx[i] ? 1 : 0;
-                            dg[i] = v - (carry ? rx[i] : 0);
-                        }
-                        baseO = p.bO;
-                        int ws = 0, P[NO];
+                            for (int i = 0; i < NDIG; i++) {
+                                const int v = dg[i] + carry;
+                                carry = v >= rx[i] ? 1 : 0;
+                                dg[i] = carry ? 0 : v;
+                            }
+                            baseO = p.bO;
+                            int ws = 0, P[NO];
 #pragma unroll
-                        for (int j = 0; j < NO; j++) {
-                            baseO += dg[2 + j] * osj[j];
-                            P[j] = foli[j] ? dg[2 + j] : 0;
-                            ws += dg[2 + j] * wmj[j];
+                            for (int j = 0; j < NO; j++) {
+                                baseO += dg[1 + j] * osj[j];
+                                P[j] = foli[j] ? dg[1 + j] : 0;
+                                ws += dg[1 + j] * wmj[j];
+                            }
+                            wset = p.wsets > 1 ? ws : 0;
+                            x0 = dg[0] * TW - p.xoff;
+                            tb = make_int4(0, P[0], P[1], P[2]);   // balanced walks always have a row dim: coordinate 1 is y
                         }
-                        wset = p.wsets > 1 ? ws : 0;
-                        x0 = dg[0] * TW - p.xoff;
-                        y0 = dg[1] * TH;
-                        tb = p.has_y ? make_int4(y0, P[0], P[1], P[2]) : make_int4(P[0], P[1], P[2], P[3]);
+                        h = chunk_rows(y0, r);
+                        rh = (h + 7) >> 3;
+                        tb.x = y0;
                         c = c_begin;
-                        tile_no++;
+                        chunk_no++;
                         announce = true;
                     }
                     const int stage = issued % STAGES;
@@ -442,14 +500,14 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                     if (issued >= STAGES) ok = wait_or_abort(&empty_bar[stage], unsigned(issued / STAGES - 1) & 1u);
                     if (ok) {
                         if (RING && announce) {
-                            // every compute warp is past the tile whose entry this overwrites (ring of STAGES + 1, at least
-                            // one load per tile, and the wait above); the arrive inside tma_fire publishes the stores
-                            int4* e = tinfo + 2 * (tile_no % (STAGES + 1));
-                            e[0] = make_int4(x0, y0, wset, 0);
+                            // every compute warp is past the chunk whose entry this overwrites (ring of STAGES + 1, at least
+                            // one load per chunk, and the wait above); the arrive inside tma_fire publishes the stores
+                            int4* e = tinfo + 2 * (chunk_no % (STAGES + 1));
+                            e[0] = make_int4(x0, y0, wset, h);
                             *reinterpret_cast<int64_t*>(e + 1) = baseO;
                             announce = false;
                         }
-                        tma_fire(stage, cc.x + tb.x, cc.y + tb.y, cc.z + tb.z, cc.w + tb.w);
+                        tma_fire(stage, rh, cc.x + tb.x, cc.y + tb.y, cc.z + tb.z, cc.w + tb.w);
                     }
                     c++;
                 }
@@ -460,28 +518,39 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                     }
                 }
             }
-        } else {
+        } else if (have_work) {
             int g = 0;   // loads consumed so far, same numbering as the producer's
             bool ok = true;
-            int64_t tile = tile_first;
-            int tile_no = 0;
+            int64_t r = r_lo;
+            int chunk_no = 0;
             while (true) {
-                if (!RING && tile_no > 0) tile_set(tile);   // long tiles: a dozen divisions per tile do not matter
-                if (RING && tile_no > 0) {
-                    // where this tile lives: published by the producer before the tile's first load, so wait for that
+                if (RING && chunk_no > 0) {
+                    // where this chunk lives: published by the producer before the chunk's first load, so wait for that
                     // load (the loop below finds it complete) and pick the entry up
                     if (!wait_or_abort(&full_bar[g % STAGES], unsigned(g / STAGES) & 1u)) { ok = false; break; }
-                    const int4* e = tinfo + 2 * (tile_no % (STAGES + 1));
+                    const int4* e = tinfo + 2 * (chunk_no % (STAGES + 1));
                     const int4 a = e[0];
                     x0 = a.x; y0 = a.y; wset = a.z;
+                    rh_cur = (a.w + 7) >> 3;
+                    y_end = a.y + a.w;
                     baseO = *reinterpret_cast<const int64_t*>(e + 1);
                 }
-                for (int c = c_begin; c < c_end; c++, g++) {
-                    const int stage = g % STAGES;
-                    if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; break; }
-                    consume(stage, c);
-                    __syncwarp();
-                    if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
+                if (p.persist) {
+                    for (int c = c_begin; c < c_end; c++, g++) {
+                        const int stage = g % STAGES;
+                        if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; break; }
+                        consume_rows(rh_cur, stage, c);
+                        __syncwarp();
+                        if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
+                    }
+                } else {
+                    for (int c = c_begin; c < c_end; c++, g++) {
+                        const int stage = g % STAGES;
+                        if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; break; }
+                        consume(NkRows<RH>{}, stage, c);
+                        __syncwarp();
+                        if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
+                    }
                 }
                 if (!ok || !p.persist) break;   // one tile per CTA: its epilogue follows below
                 store_tile();
@@ -489,13 +558,21 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                 for (int i = 0; i < RH; i++)
 #pragma unroll
                     for (int x = 0; x < CW; x++) acc[i][x] = T(0);
-                tile += tile_step;
-                if (tile >= p.tiles_total) break;
-                tile_no++;
+                r += y_end - y0;
+                if (r >= r_hi) break;
+                chunk_no++;
+                if (!RING) {   // long chunks: a dozen divisions per chunk do not matter
+                    const int64_t strip = r / p.OH;
+                    y0 = int(r - strip * p.OH);
+                    strip_set(int(strip % p.tilesX), strip / p.tilesX);
+                    const int h = chunk_rows(y0, r);
+                    rh_cur = (h + 7) >> 3;
+                    y_end = y0 + h;
+                }
             }
         }
         __syncthreads();
-        if (p.persist) return;   // every tile was stored on the way
+        if (p.persist) return;   // every chunk was stored on the way
         if (*abort_word) {
             if (!p.cluster) return;
             aborted = true;   // the cluster's barriers below still have to be met; the host reports the time-out
@@ -513,7 +590,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             const int nxt = it + STAGES - 1;
             if (nxt < n_it) ldgsts_stage(nxt % STAGES, c_begin + nxt);
             nk_cp_async_commit();
-            consume(it % STAGES, c_begin + it);
+            consume(NkRows<RH>{}, it % STAGES, c_begin + it);
         }
         nk_cp_async_wait<0>();
     }
@@ -642,37 +719,43 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     };
     p.wsets = (sets_fit && wsets > 1) ? int(wsets) : 1;
     int cst = configure(p.wsets);
-    if (cst == 0 && p.wsets > 1 && !(splits == 1 && tiles >= 8 * slots)) {   // no persistent walk after all: one set per CTA
+    // The balanced persistent walk: a tensor map with a row dim, no channel split, and the same weights for every
+    // strip or all weight sets resident at once.
+    auto balanced = [&]() { return TMA && p.has_y && splits == 1 && (wsets == 1 || p.wsets > 1); };
+    if (cst == 0 && p.wsets > 1 && !balanced()) {   // no persistent walk after all: one set per CTA
         p.wsets = 1;
         cst = configure(1);
     }
     if (cst) return cst;
     p.splits = splits;
     p.cluster = 0;
-    CUtensorMap tmap;
-    memset(&tmap, 0, sizeof(tmap));
+    p.persist = 0;
+    p.rows_total = int64_t(p.tilesX) * p.NP * p.OH;
+    TmapSet tmaps;
+    memset(&tmaps, 0, sizeof(tmaps));
+    bool ring = false;
+    int64_t grid = tiles * splits;
     if (TMA) {
         if (C::SW > 256 || C::SH > 256) return -1;
-        int st = nk_tma_encode(ctx, sizeof(T) == 4 ? NK_F32 : NK_F64, *img, C::SW, C::SH, p.has_y != 0, &tmap);
-        if (st == -1) return -1;
-        if (st) return st;
+        p.persist = balanced() ? 1 : 0;
+        // persistent: one map per rows-per-warp value (box of 8 r + KH - 1 rows); otherwise only the full tile's map
+        for (int r = p.persist ? 1 : RH; r <= RH; r++) {
+            int st = nk_tma_encode(ctx, sizeof(T) == 4 ? NK_F32 : NK_F64, *img, C::SW, 8 * r + KH - 1, p.has_y != 0, &tmaps.m[r - 1]);
+            if (st == -1) return -1;
+            if (st) return st;
+        }
         p.status = ctx->tma_status_dev;
+        if (p.persist) {
+            // Every resident CTA slot gets an equal, contiguous share of the strip rows -- but not so many CTAs that a
+            // share shrinks to a few rows (each chunk re-reads KH - 1 halo rows and pays a fixed set-up).
+            ring = p.NQ < 8;   // short chunks: decoding would cost as much as the chunk's arithmetic
+            const int64_t min_rows = 16;
+            grid = p.rows_total / min_rows;
+            if (grid > slots) grid = slots;
+            if (grid < 1) grid = 1;
+        }
     }
-    int64_t grid = tiles * splits;
     if (grid > 0x7fffffffLL) return -1;
-    // Many more tiles than resident CTAs: one resident wave of CTAs walks the tiles, so that weights, table and
-    // barriers are set up once per CTA and the load pipeline never drains between tiles. Needs the same weights for
-    // every tile, or for all its weight sets to fit in shared memory together. With only a few tiles per CTA the
-    // fixed tile-to-CTA assignment loses more to imbalance (up to one tile in tiles/slots) than the set-up costs,
-    // and the hardware's own CTA scheduling does better (measured on 3.3 and 5.2 tiles per CTA: 3 % and 15 % slower).
-    p.persist = 0;
-    p.tiles_total = tiles;
-    bool ring = false;
-    if (TMA && splits == 1 && tiles >= 8 * slots && (wsets == 1 || p.wsets > 1)) {
-        p.persist = 1;
-        ring = p.NQ < 8;   // short tiles: decoding would cost as much as the tile's arithmetic
-        grid = slots;
-    }
     const unsigned threads = TMA ? 288 : 256;
     if (splits > 1 && splits <= 8) {
         // one launch: the parts of a tile as a thread-block cluster that adds itself up through shared memory
@@ -693,7 +776,7 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
         if (cudaOccupancyMaxActiveClusters(&active, nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, &cfg) == cudaSuccess && active >= 1) {
             p.cluster = 1;
             T* none = nullptr;
-            cudaError_t e = cudaLaunchKernelEx(&cfg, nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, out, none, I, K, p, tmap);
+            cudaError_t e = cudaLaunchKernelEx(&cfg, nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, out, none, I, K, p, tmaps);
             if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaLaunchKernelEx(nk_conv_tiled_kernel, cluster)");
             return nk_after_launch(ctx, TMA ? "nk_conv_tiled_kernel<tma,cluster>" : "nk_conv_tiled_kernel<ldgsts,cluster>");
         }
@@ -711,12 +794,12 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
         if (ring) {
             cudaError_t e = cudaFuncSetAttribute(nk_conv_tiled_kernel<T, KH, KW, RH, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
             if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel, ring)");
-            nk_conv_tiled_kernel<T, KH, KW, RH, true, true><<<unsigned(grid), threads, smem, ctx->stream>>>(out, partial, I, K, p, tmap);
+            nk_conv_tiled_kernel<T, KH, KW, RH, true, true><<<unsigned(grid), threads, smem, ctx->stream>>>(out, partial, I, K, p, tmaps);
             return nk_after_launch(ctx, "nk_conv_tiled_kernel<tma,ring>");
         }
     }
-    nk_conv_tiled_kernel<T, KH, KW, RH, TMA><<<unsigned(grid), threads, smem, ctx->stream>>>(out, partial, I, K, p, tmap);
-    int st = nk_after_launch(ctx, TMA ? "nk_conv_tiled_kernel<tma>" : "nk_conv_tiled_kernel<ldgsts>");
+    nk_conv_tiled_kernel<T, KH, KW, RH, TMA><<<unsigned(grid), threads, smem, ctx->stream>>>(out, partial, I, K, p, tmaps);
+    int st = nk_after_launch(ctx, TMA ? (p.persist ? "nk_conv_tiled_kernel<tma,balanced>" : "nk_conv_tiled_kernel<tma>") : "nk_conv_tiled_kernel<ldgsts>");
     if (st || splits == 1) return st;
     const int64_t plane = p.NP * int64_t(p.OH) * p.OW;
     int g = nk_grid_for(ctx, plane, 256, 8);

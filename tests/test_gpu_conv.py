@@ -189,6 +189,41 @@ def test_stencil_shapes_all_kernel_families(device, oracle, dt, case):
 
 @pytest.mark.parametrize("dt", [np.float32, np.float64])
 @pytest.mark.parametrize("case", [
+    ([3, 6, 333, 700], [1, 6, 5, 5]),      # 18 strips of 329 rows over ~300 CTAs: ranges of ~20 rows that cross strip ends
+    ([2, 9, 1000, 300], [1, 9, 3, 3]),     # long strips: full chunks, then a remainder of every rows-per-warp value
+    ([5, 70, 250], [1, 7, 7]),             # one channel per chunk: the ring-fed kernel
+    ([40, 2, 90, 140], [1, 2, 5, 3]),      # many short strips (86 rows each)
+])
+def test_balanced_walk_gives_the_same_bits_as_one_tile_per_cta(device, oracle, dt, case):
+    """The persistent TMA launch deals the rows of all column strips to the CTAs in equal contiguous ranges and walks a
+    range in chunks of any height; the additions into one output still come in the same order (channel, window row,
+    window column), so the result must equal the one-tile-per-CTA LDGSTS family bit for bit, whatever the row counts --
+    for the forward call and for the image gradient (the same kernel on a padded, flipped problem)."""
+    rng = np.random.default_rng(41)
+    sa, sb = case
+    so = [abs(x - y) + 1 for x, y in zip(sa, sb)]
+    a = rng.standard_normal(int(np.prod(sa))).astype(dt)
+    b = rng.standard_normal(int(np.prod(sb))).astype(dt)
+    c0, c1, c2 = ND.of_shape(so), ND.of_shape(sa), ND.of_shape(sb)
+    tma = gpu_conv(device, np.full(c0.size, 777.0, dtype=dt), c0, a, c1, b, c2, path=L.NK_CONV_TMA)
+    assert device.last_kernel() in ("nk_conv_tiled_kernel<tma,balanced>", "nk_conv_tiled_kernel<tma,ring>"), device.last_kernel()
+    one_tile = gpu_conv(device, np.full(c0.size, -1.0, dtype=dt), c0, a, c1, b, c2, path=L.NK_CONV_TILED)
+    assert device.last_kernel() == "nk_conv_tiled_kernel<ldgsts>"
+    assert np.array_equal(tma, one_tile)
+    rngs = np.random.default_rng(42)
+    check_against_oracle_sampled(oracle, dt, tma, c0, a, c1, b, c2, -1, rngs, n_ranges=4, span=300)
+    # image gradient: drain image-shaped, T1 = kernel, T2 = error
+    e = rng.standard_normal(c0.size).astype(dt)
+    grad = gpu_conv(device, np.full(c1.size, 777.0, dtype=dt), c1, b, c2, e, c0, d=0)
+    if (so[-1] * np.dtype(dt).itemsize) % 16 == 0:
+        assert device.last_conv_path() == L.NK_CONV_TMA
+    generic = gpu_conv(device, np.zeros(c1.size, dtype=dt), c1, b, c2, e, c0, d=0, path=L.NK_CONV_GENERIC)
+    check_against_oracle_sampled(oracle, dt, grad, c1, b, c2, e, c0, 0, rngs, n_ranges=3, span=40)
+    assert np.abs(grad - generic).max() <= (1e-5 if dt == np.float32 else 1e-12) * np.abs(generic).max() * 4
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("case", [
     ([32, 64, 256], [32, 3, 3], 8), ([16, 70, 132], [16, 5, 5], 4), ([24, 50, 260], [24, 3, 3], 6),
     ([2, 16, 40, 128], [1, 16, 3, 3], 4), ([64, 40, 256], [64, 3, 3], 16),
 ])
