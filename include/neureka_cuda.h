@@ -185,7 +185,7 @@ int nk_measure_fma_peak(nk_ctx* ctx, int32_t dtype, double* out_tflops);
 
 /* ---- fused elementwise expressions, compiled at run time ----
  * Counterpart of the kernels the reference generates for Device.optimizedOperationOf(Function, name)
- * (src/main/java/neureka/devices/Device.java:216-241; model: backend/ocl/utility/CLFunctionCompiler.java:47-196), plus
+ * (src/main/java/neureka/devices/Device.java:216-241; model: src/main/java/neureka/devices/opencl/utility/CLFunctionCompiler.java:47-196), plus
  * broadcasting, which the reference's compiler does not do. `expr` is one C expression of type T over x0 .. x5 built from
  *   op_add(a,b) op_sub op_mul op_div op_mod op_pow      the six Operator ops, forward
  *   f_<id>(a), df_<id>(a)                               the 23 functions of nk_fun and their derivatives (f_tanh, df_relu ...)
@@ -199,9 +199,21 @@ int nk_fused_compile(nk_ctx* ctx, int32_t dtype, int32_t n_inputs, const char* e
 int nk_fused_run(nk_ctx* ctx, nk_fused* f, int32_t rank, nk_buf* drn, const int32_t* cfg0,
                  nk_buf* const* srcs, const int32_t* const* cfgs);
 int nk_fused_free(nk_fused* f);
-/* Plan arithmetic of nk_fused_run, exposed so that it can be checked without a device: 1 when a launch of `units`
- * work units over `rows` rows on a grid of `grid` CTAs must use 64-bit unit and row counters in the kernel. */
-int nk_fused_plan_is_wide(int64_t units, int64_t rows, int64_t grid);
+/* The backward pass of such an expression w.r.t. input `target`, the sum over the dims that input is broadcast along
+ * included: one kernel that recomputes the expression per element of the full index space, multiplies the error through
+ * it and reduces -- no result-sized intermediate is read or written. The reference's compiler produces derivative kernels
+ * too (src/main/java/neureka/devices/opencl/utility/CLFunctionCompiler.java:114, :155-157: a second kernel for `getDerivative(d)`); the reduction is this library's.
+ * `terms` is a list of C statements over e (the error element) and x0 .. x5 that assigns term[0] .. term[n_leaves-1], one
+ * per occurrence of the input in the expression, built from the forward vocabulary plus dop_div(d,a,b), dop_mod, dop_pow
+ * (local derivative of the operator w.r.t. operand d), e.g. for tanh(x0*x1+x1) and target 1:
+ *   "const T t0 = op_mul(x0,x1); const T t1 = op_add(t0,x1); const T t2 = op_mul(e, df_tanh(t1)); term[0] = t2;
+ *    term[1] = op_mul(x0, t2);"
+ * Every occurrence is summed separately, lowest reduced dim fastest (the order of nk_broadcast with d >= 0), and the
+ * sums are added in occurrence order: where the op-by-op backward pass reduces at a single node of the expression the
+ * result equals it bit for bit. `err` is result-shaped or a single (virtual) value; `grad` has the input's shape. */
+int nk_fused_compile_grad(nk_ctx* ctx, int32_t dtype, int32_t n_inputs, int32_t target, int32_t n_leaves, const char* terms, nk_fused** out);
+int nk_fused_run_grad(nk_ctx* ctx, nk_fused* f, int32_t rank, nk_buf* grad, const int32_t* cfg_grad, nk_buf* err, const int32_t* cfg_err,
+                      nk_buf* const* srcs, const int32_t* const* cfgs);
 
 /* ---- ordering between contexts (no reference counterpart: OpenCLDevice owns a single in-order queue) ----
  * A second nk_ctx on the same device is a second stream. An event recorded on one context's stream can be waited
@@ -219,11 +231,32 @@ int nk_event_free(nk_event* ev);
 int nk_probe_wait_timeout(nk_ctx* ctx, uint64_t limit_ns, uint64_t* out_waited_ns);
 
 /* ---- multi-GPU (no reference counterpart: the reference has no multi-device execution) ----
- * One process per GPU. A rank exports a buffer; peers open it and use it as the drain of nk_conv, so a
+ * (a) One process per GPU. A rank exports a buffer; peers open it and use it as the drain of nk_conv, so a
  * slab's results are stored straight into the owner's memory over NVLink (plain stores). */
 #define NK_IPC_HANDLE_BYTES 64
 int nk_ipc_export(nk_ctx* ctx, nk_buf* buf, uint8_t handle[NK_IPC_HANDLE_BYTES]);
 int nk_ipc_open(nk_ctx* ctx, const uint8_t handle[NK_IPC_HANDLE_BYTES], int32_t dtype, int64_t n_elems, nk_buf** out);
+
+/* (b) One process, several GPUs: the way a JVM holds several Device objects (J/devices/Device.java:259-279; the
+ * backend extension hands them out, J/backend/api/BackendExtension.java:15-70). nk_group_open opens one context per
+ * ordinal and enables peer access between the members once (the same ordinal twice = one GPU, two streams).
+ * nk_group_ctx gives a member's context for the ordinary calls (alloc, write, kernels). */
+typedef struct nk_group nk_group;
+int nk_group_open(const int32_t* ordinals, int32_t n, nk_group** out);
+int nk_group_size(nk_group* grp, int32_t* out_n);
+int nk_group_ctx(nk_group* grp, int32_t member, nk_ctx** out_ctx);
+int nk_group_close(nk_group* grp);
+/* The split of `out_extent` output indices over `parts` members with `halo` extra input indices each (host
+ * arithmetic only): member g computes outputs [out_lo[g], out_lo[g] + out_len[g]) from inputs
+ * [in_lo[g], in_lo[g] + in_len[g]). Near-equal contiguous parts, the remainder to the first members. */
+int nk_group_plan_slabs(int64_t out_extent, int32_t parts, int64_t halo, int64_t* out_lo, int64_t* out_len, int64_t* in_lo, int64_t* in_len);
+/* Forward convolution image x kernel cut along output dim split_dim (image extent > kernel extent there): slabs[g] is
+ * member g's dense input slab (the image's shape with in_len[g] along split_dim, on member g's device), kernels[g] its
+ * copy of the kernel, `out` the full result on the FIRST member's device. Member 0 convolves into place; the others
+ * convolve into a local slab and push it into `out` over NVLink on a second stream (overlapping the next call); the
+ * first member's stream waits for the pushes, so work queued on it afterwards sees the assembled result. */
+int nk_conv_sharded(nk_group* grp, int32_t dtype, int32_t rank, const int64_t* image_shape, const int64_t* kernel_shape, int32_t split_dim,
+                    nk_buf* const* slabs, nk_buf* const* kernels, nk_buf* out);
 
 /* ---- synthetic inputs: java.util.Random-compatible streams (host side) ----
  * Constants and polar Gaussian as J/backend/main/implementations/elementwise/CPURandomization.java:12-15, :265-284.

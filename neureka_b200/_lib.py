@@ -71,7 +71,8 @@ SIGNATURES = {
     "nk_fused_compile": (C.c_int, [_vp, _i32, _i32, C.c_char_p, C.POINTER(_vp)]),
     "nk_fused_run": (C.c_int, [_vp, _vp, _i32, _vp, _cfg, C.POINTER(_vp), C.POINTER(_cfg)]),
     "nk_fused_free": (C.c_int, [_vp]),
-    "nk_fused_plan_is_wide": (C.c_int, [_i64, _i64, _i64]),
+    "nk_fused_compile_grad": (C.c_int, [_vp, _i32, _i32, _i32, _i32, C.c_char_p, C.POINTER(_vp)]),
+    "nk_fused_run_grad": (C.c_int, [_vp, _vp, _i32, _vp, _cfg, _vp, _cfg, C.POINTER(_vp), C.POINTER(_cfg)]),
     "nk_probe_wait_timeout": (C.c_int, [_vp, C.c_uint64, C.POINTER(C.c_uint64)]),
     "nk_event_create": (C.c_int, [_vp, C.POINTER(_vp)]),
     "nk_event_record": (C.c_int, [_vp, _vp]),
@@ -98,6 +99,12 @@ SIGNATURES = {
     "nk_measure_fma_peak": (C.c_int, [_vp, _i32, C.POINTER(C.c_double)]),
     "nk_ipc_export": (C.c_int, [_vp, _vp, C.POINTER(C.c_uint8)]),
     "nk_ipc_open": (C.c_int, [_vp, C.POINTER(C.c_uint8), _i32, _i64, C.POINTER(_vp)]),
+    "nk_group_open": (C.c_int, [C.POINTER(_i32), _i32, C.POINTER(_vp)]),
+    "nk_group_size": (C.c_int, [_vp, C.POINTER(_i32)]),
+    "nk_group_ctx": (C.c_int, [_vp, _i32, C.POINTER(_vp)]),
+    "nk_group_close": (C.c_int, [_vp]),
+    "nk_group_plan_slabs": (C.c_int, [_i64, _i32, _i64, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64)]),
+    "nk_conv_sharded": (C.c_int, [_vp, _i32, _i32, C.POINTER(_i64), C.POINTER(_i64), _i32, C.POINTER(_vp), C.POINTER(_vp), _vp]),
     "nk_jrand_fill": (C.c_int, [_i32, _i32, _i64, _dbl, _dbl, _vp, _i64]),
     "nk_jrand_fill_at": (C.c_int, [_i32, _i32, _i64, _dbl, _dbl, _i64, _vp, _i64]),
 }

@@ -19,15 +19,18 @@
 //
 // Launch shapes (chosen by nk_launch_tiled from the tile count and the kernel's real occupancy):
 //   * one tile per CTA, the hardware scheduling the CTAs -- a few tiles per resident CTA slot;
-//   * balanced persistent walk (TMA, two sliding dims, no channel split) -- the output is a list of column strips
-//     (outer coordinate x 128-bit-per-lane column block), each OH rows high; the rows of all strips, laid end to end,
-//     are dealt to one resident wave of CTAs in equal contiguous ranges (to the row), and a CTA walks its range in
-//     chunks of up to TH rows: a chunk of h rows gives every warp ceil(h / 8) rows (the multiply-add loop exists once
-//     per rows-per-warp value 1..RH), its tile load uses the tensor map whose box is 8 * ceil(h / 8) + KH - 1 rows high.
-//     No whole-tile rounding: every CTA finishes within one chunk row of the others whatever the row count is. The
-//     producer warp keeps loading across chunk boundaries; strips with their own weights select one of the weight
-//     sets staged at once; for one-channel chunks (RING) the compute warps take chunk positions from a ring the
-//     producer fills instead of decoding them;
+//   * balanced persistent walk (TMA, two sliding dims, no channel split) -- the grid is one resident wave of G CTAs.
+//     Tiles are numbered with the column block fastest, then the row block, then the outer coordinate. First come
+//     W = tiles / G whole waves: in wave w CTA b takes tile w * G + b, so the CTAs of a wave work side by side on one band
+//     of the tensor (neighbouring column blocks of the same rows: their loads and stores form long contiguous runs in
+//     DRAM). The remaining tiles -- less than one per CTA -- are not dealt whole: each is cut into groups of 8 rows, and
+//     the groups of all remaining tiles, laid end to end in tile order, are dealt to the CTAs in equal contiguous ranges;
+//     a range is walked in chunks that stop at tile ends, a chunk of n groups giving every warp n rows (the
+//     multiply-add loop exists once per rows-per-warp value 1..RH) and loading through the tensor map whose box is
+//     8 n + KH - 1 rows high. So the last, partial wave costs its share of a tile instead of a whole one. The producer
+//     warp keeps loading across chunk boundaries; tiles with their own weights select one of the weight sets staged
+//     at once; for one-channel chunks (RING) the compute warps take chunk positions from a ring the producer fills
+//     instead of decoding them;
 //   * channel split -- fewer tiles than slots and many channels: up to 8 parts of a tile form a thread-block cluster
 //     and add their partial tiles through distributed shared memory; more parts go through scratch and a finish
 //     kernel. Both add in part order, so the result is deterministic and the same on either path.
@@ -54,8 +57,9 @@ struct TiledPlan {
     int64_t bI, bK, bO;
     int tilesX, tilesY, splits;
     int remote_out;   // the drain lives on another GPU (stores cross NVLink)
-    int persist;      // TMA family: the grid is one resident wave; CTA b walks rows [b, b + 1) * rows_total / grid of the strips laid end to end
-    int64_t rows_total;   // strips * OH
+    int persist;      // TMA family: the grid is one resident wave; whole waves of tiles, then the rest dealt in 8-row groups
+    int64_t tiles_total;
+    int waves;            // whole waves: in wave w CTA b takes tile w * gridDim.x + b
     int wsets;        // persistent walk over tiles whose weights differ: weight sets staged at once (1 = same weights everywhere)
     int cluster;   // channel-split CTAs of a tile form one thread-block cluster and add their tiles through shared memory
     int vec;       // LDGSTS: 16-byte global->shared copies are legal for every chunk
@@ -147,21 +151,19 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     // One tile per CTA (the parts of a channel split are neighbours: one cluster), or -- persistent -- a walk over
     // the CTA's range of strip rows with the load pipeline running on across chunk boundaries.
     const int split = p.persist ? 0 : int(blockIdx.x % unsigned(p.splits));
-    const int64_t tile_first = p.persist ? 0 : int64_t(blockIdx.x / unsigned(p.splits));
-    // persistent: this CTA's rows of the strips laid end to end
-    const int64_t r_lo = p.persist ? (int64_t(blockIdx.x) * p.rows_total) / int64_t(gridDim.x) : 0;
-    const int64_t r_hi = p.persist ? (int64_t(blockIdx.x + 1) * p.rows_total) / int64_t(gridDim.x) : 0;
     int64_t baseI, baseK, baseO;
     int pidx[NK_TILED_MAX_OUTER];
     int x0, y0;
     int rh_cur = RH;        // rows per warp of the chunk / tile this thread stands on
     int y_end = p.OH;       // first row below it
     int wset = 0;   // which of the staged weight sets the current tile uses (outer output dims that move the kernel)
-    // Places the thread on column block tx of the outer coordinate `outer` (divisions: once per thread, and once per chunk
-    // of long chunks; the producer thread of a persistent CTA steps on digit by digit instead, see below).
-    auto strip_set = [&](int tx, int64_t outer) {
+    // Places the thread on a tile (divisions: once per thread, and once per chunk of long chunks; the producer thread of a
+    // persistent CTA steps on digit by digit instead, see below). Returns the tile's first row.
+    auto tile_set = [&](int64_t tile) -> int {
+        const int tx = int(tile % p.tilesX); tile /= p.tilesX;
+        const int ty = int(tile % p.tilesY); tile /= p.tilesY;
         baseI = p.bI; baseK = p.bK; baseO = p.bO;
-        int64_t rem = outer;
+        int64_t rem = tile;
         int ws = 0, wm = 1;
         for (int k = p.n_outer - 1; k >= 0; k--) {
             const int idx = int(rem % p.oext[k]);
@@ -172,29 +174,69 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         }
         wset = p.wsets > 1 ? ws : 0;
         x0 = tx * TW - p.xoff;
+        return ty * TH;
     };
-    // The chunk that starts at row r of the end-to-end rows: at most TH rows, never across a strip's end or the range's end.
-    auto chunk_rows = [&](int y, int64_t r) -> int {
-        int h = p.OH - y;
-        if (h > TH) h = TH;
-        if (int64_t(h) > r_hi - r) h = int(r_hi - r);
-        return h;
+    // Persistent walk of CTA b: steps 0 .. waves-1 are the whole tiles step * G + b; after them the CTA's range
+    // [q, q_hi) of 8-row groups of the remaining tiles (RH groups per tile), cut into chunks at tile ends.
+    const int64_t G = gridDim.x;
+    const int64_t tail_first = int64_t(p.waves) * G;                                    // first tile that is dealt in groups
+    const int64_t tail_groups = p.persist ? (p.tiles_total - tail_first) * RH : 0;
+    const int64_t q_lo = (int64_t(blockIdx.x) * tail_groups) / G, q_hi = (int64_t(blockIdx.x + 1) * tail_groups) / G;
+    // The chunk after `step` whole tiles and `q` groups: false when the walk is over. Sets the tile, y0, rh_cur, y_end
+    // and advances step / q. Chunks that lie entirely below the image's last row are skipped.
+    int step = 0;
+    int64_t q = q_lo;
+    int64_t cur_tile = 0;
+    auto next_chunk = [&]() -> bool {
+        while (true) {
+            if (step < p.waves) {
+                cur_tile = int64_t(step) * G + blockIdx.x;
+                const int ty0 = tile_set(cur_tile);
+                step++;
+                y0 = ty0;
+                int h = p.OH - y0;
+                if (h > TH) h = TH;
+                rh_cur = (h + 7) >> 3;
+                y_end = y0 + h;
+                return true;
+            }
+            if (q >= q_hi) return false;
+            const int64_t t = q / RH;
+            const int g0 = int(q - t * RH);
+            int n = RH - g0;
+            if (int64_t(n) > q_hi - q) n = int(q_hi - q);
+            q += n;
+            cur_tile = tail_first + t;
+            const int ty0 = tile_set(cur_tile);
+            y0 = ty0 + g0 * 8;
+            int h = p.OH - y0;
+            if (h <= 0) continue;
+            if (h > n * 8) h = n * 8;
+            rh_cur = (h + 7) >> 3;
+            y_end = y0 + h;
+            return true;
+        }
     };
     int64_t pflat = 0;      // flat outer index: used by the two-pass split path (one tile per CTA)
+    bool have_work = true;
+    int n_chunks = 0;       // persistent: chunks of this CTA's walk (what the ring-fed compute warps count down)
     if (p.persist) {
-        const int64_t strip = r_lo / p.OH;
-        y0 = int(r_lo - strip * p.OH);
-        strip_set(int(strip % p.tilesX), strip / p.tilesX);
-        const int h = r_lo < r_hi ? chunk_rows(y0, r_lo) : 0;
-        rh_cur = h > 0 ? (h + 7) >> 3 : 1;
-        y_end = y0 + h;
+        n_chunks = p.waves;
+        for (int64_t qq = q_lo; qq < q_hi;) {   // at most a few tiles: the range is less than one tile's worth per CTA, plus its cuts
+            const int64_t t = qq / RH;
+            const int g0 = int(qq - t * RH);
+            int n = RH - g0;
+            if (int64_t(n) > q_hi - qq) n = int(q_hi - qq);
+            qq += n;
+            const int ty = int(((tail_first + t) / p.tilesX) % p.tilesY);
+            if (ty * TH + g0 * 8 < p.OH) n_chunks++;
+        }
+        have_work = next_chunk();
+        if (!have_work) { tile_set(0); y0 = 0; rh_cur = 1; y_end = 0; }
     } else {
-        int64_t tile = tile_first;
-        const int tx = int(tile % p.tilesX); tile /= p.tilesX;
-        const int ty = int(tile % p.tilesY); tile /= p.tilesY;
-        pflat = tile;
-        strip_set(tx, tile);
-        y0 = ty * TH;
+        const int64_t tile = int64_t(blockIdx.x / unsigned(p.splits));
+        pflat = tile / (int64_t(p.tilesX) * p.tilesY);
+        y0 = tile_set(tile);
     }
     const int cper = (p.NQ + p.splits - 1) / p.splits;
     const int c_begin = split * cper;
@@ -237,7 +279,6 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         nk_tma_load5(stage_base + size_t(stage) * C::STAGE_BYTES, &tmaps.m[rh - 1], &full_bar[stage], p.tma_nd, x0 - p.padX, c1, c2, c3, c4);
         issued++;
     };
-    const bool have_work = !p.persist || r_lo < r_hi;
     if (TMA && tid == 256) {
         // the producer thread sets the barriers up and requests the first tiles right away, so that they travel
         // while the other warps stage the weights; everybody else meets the barriers only after the __syncthreads below
@@ -274,7 +315,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         const int ws = e / per_set, r = e - ws * per_set;
         const int c = c_begin + r / WPAD, t = r % WPAD;
         int64_t kb = baseK;   // one set: the weights of this CTA's (only, or every) tile
-        if (p.wsets > 1) {    // several: set ws belongs to the outer output indices that strip_set() folds into ws
+        if (p.wsets > 1) {    // several: set ws belongs to the outer output indices that tile_set() folds into ws
             kb = p.bK;
             int rem = ws;
             for (int k = p.n_outer - 1; k >= 0; k--)
@@ -425,21 +466,40 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         if (warp == 8) {
             if (lane == 0 && have_work) {
                 // `issued` counts tile loads over the CTA's whole life: load g uses stage g % STAGES in round g / STAGES.
-                // Persistent walk: after a chunk of h rows the producer moves h rows down its strip; at the strip's end it
-                // steps to the next strip, a mixed-radix number (tx | outer output indices, last outer dim fastest) that
-                // it counts up by one with carry -- adds and compares only, no division. Everything the step needs sits in
+                // A tile index is a mixed-radix number (tx | ty | outer output indices, last outer dim fastest). The walk
+                // adds gridDim.x to it per whole wave and then 1 per tile of the CTA's range of row groups, digit by
+                // digit with carry -- a few adds and compares per chunk, no division. Everything the step needs sits in
                 // registers under compile-time indices (j counts the outer dims from the last one): the producer's time
                 // per chunk bounds short chunks.
-                constexpr int NO = NK_TILED_MAX_OUTER, NDIG = 1 + NO;
-                int dg[NDIG], rx[NDIG], wmj[NO];
+                constexpr int NO = NK_TILED_MAX_OUTER, NDIG = 2 + NO;
+                int dg[NDIG], sg[NDIG], rx[NDIG], wmj[NO];
                 long long osj[NO];
                 bool foli[NO];
+                auto digits_of = [&](int64_t t) {
+#pragma unroll
+                    for (int i = 0; i < NDIG; i++) { dg[i] = int(t % rx[i]); t /= rx[i]; }
+                };
+                // puts the producer on the tile its digits name (drain base, weight set, x0, tensor-map coordinates 2..4)
+                int4 tb = tile_coords();
+                auto apply_digits = [&]() {
+                    baseO = p.bO;
+                    int ws = 0, P[NO];
+#pragma unroll
+                    for (int j = 0; j < NO; j++) {
+                        baseO += dg[2 + j] * osj[j];
+                        P[j] = foli[j] ? dg[2 + j] : 0;
+                        ws += dg[2 + j] * wmj[j];
+                    }
+                    wset = p.wsets > 1 ? ws : 0;
+                    x0 = dg[0] * TW - p.xoff;
+                    tb = make_int4(0, P[0], P[1], P[2]);   // persistent walks always have a row dim: coordinate 1 is y
+                };
                 if (p.persist) {
-                    int64_t t = r_lo / p.OH;
+                    int64_t st = G;
 #pragma unroll
                     for (int i = 0; i < NDIG; i++) {
-                        rx[i] = i == 0 ? p.tilesX : ((i - 1) < p.n_outer ? int(p.oext[p.n_outer - 1 - (i - 1)]) : 1);
-                        dg[i] = int(t % rx[i]); t /= rx[i];
+                        rx[i] = i == 0 ? p.tilesX : i == 1 ? p.tilesY : ((i - 2) < p.n_outer ? int(p.oext[p.n_outer - 1 - (i - 2)]) : 1);
+                        sg[i] = int(st % rx[i]); st /= rx[i];
                     }
                     int wm = 1;
 #pragma unroll
@@ -452,43 +512,69 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                         wmj[j] = moves_kernel ? wm : 0;
                         if (moves_kernel) wm *= int(p.oext[k]);
                     }
+                    digits_of(cur_tile);   // the tile of the first chunk (the prologue placed every thread on it)
                 }
+                int64_t ptile = cur_tile;
                 bool ok = true;
-                int64_t r = r_lo;           // first row of the chunk being loaded
-                int h = y_end - y0;         // its rows (persistent)
-                int rh = rh_cur;
+                // the producer's own copy of the walk's position: `pstep` whole tiles done, `pq` = next row group of the
+                // range; (step, q) of this thread already stand after the first chunk
+                int pstep = step;
+                int64_t pq = q;
+                int rh = rh_cur, h = y_end - y0;
                 int chunk_no = 0;
                 bool announce = false;      // a new chunk's info still has to go into the ring (after the stage came free)
                 int c = c_begin + issued;   // the first loads of the first chunk were requested in the prologue
-                int4 tb = tile_coords();
+                tb.x = y0;
                 while (ok) {
                     if (c >= c_end) {
                         if (!p.persist) break;
-                        r += h;
-                        if (r >= r_hi) break;
-                        y0 += h;
-                        if (y0 >= p.OH) {   // next strip
-                            y0 = 0;
-                            int carry = 1;
+                        bool found = false;
+                        while (!found) {
+                            if (pstep < p.waves) {
+                                {   // next whole tile: + gridDim.x (pstep >= 1 here: the first chunk was a whole tile)
+                                    int carry = 0;
 #pragma unroll
-                            for (int i = 0; i < NDIG; i++) {
-                                const int v = dg[i] + carry;
-                                carry = v >= rx[i] ? 1 : 0;
-                                dg[i] = carry ? 0 : v;
-                            }
-                            baseO = p.bO;
-                            int ws = 0, P[NO];
+                                    for (int i = 0; i < NDIG; i++) {
+                                        const int v = dg[i] + sg[i] + carry;
+                                        carry = v >= rx[i] ? 1 : 0;
+                                        dg[i] = v - (carry ? rx[i] : 0);
+                                    }
+                                    ptile += G;
+                                }
+                                pstep++;
+                                apply_digits();
+                                y0 = dg[1] * TH;
+                                h = p.OH - y0;
+                                if (h > TH) h = TH;
+                                found = true;
+                            } else {
+                                if (pq >= q_hi) break;
+                                const int64_t t = pq / RH;   // RH is a power of two or small constant: a shift / multiply
+                                const int g0 = int(pq - t * RH);
+                                int n = RH - g0;
+                                if (int64_t(n) > q_hi - pq) n = int(q_hi - pq);
+                                if (tail_first + t == ptile + 1) {   // next tile of the range: + 1
+                                    int carry = 1;
 #pragma unroll
-                            for (int j = 0; j < NO; j++) {
-                                baseO += dg[1 + j] * osj[j];
-                                P[j] = foli[j] ? dg[1 + j] : 0;
-                                ws += dg[1 + j] * wmj[j];
+                                    for (int i = 0; i < NDIG; i++) {
+                                        const int v = dg[i] + carry;
+                                        carry = v >= rx[i] ? 1 : 0;
+                                        dg[i] = carry ? 0 : v;
+                                    }
+                                } else if (tail_first + t != ptile) {
+                                    digits_of(tail_first + t);   // once per CTA: where its range of row groups starts
+                                }
+                                ptile = tail_first + t;
+                                pq += n;
+                                apply_digits();
+                                y0 = dg[1] * TH + g0 * 8;
+                                h = p.OH - y0;
+                                if (h <= 0) continue;
+                                if (h > n * 8) h = n * 8;
+                                found = true;
                             }
-                            wset = p.wsets > 1 ? ws : 0;
-                            x0 = dg[0] * TW - p.xoff;
-                            tb = make_int4(0, P[0], P[1], P[2]);   // balanced walks always have a row dim: coordinate 1 is y
                         }
-                        h = chunk_rows(y0, r);
+                        if (!found) break;
                         rh = (h + 7) >> 3;
                         tb.x = y0;
                         c = c_begin;
@@ -521,7 +607,6 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         } else if (have_work) {
             int g = 0;   // loads consumed so far, same numbering as the producer's
             bool ok = true;
-            int64_t r = r_lo;
             int chunk_no = 0;
             while (true) {
                 if (RING && chunk_no > 0) {
@@ -558,17 +643,11 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                 for (int i = 0; i < RH; i++)
 #pragma unroll
                     for (int x = 0; x < CW; x++) acc[i][x] = T(0);
-                r += y_end - y0;
-                if (r >= r_hi) break;
                 chunk_no++;
-                if (!RING) {   // long chunks: a dozen divisions per chunk do not matter
-                    const int64_t strip = r / p.OH;
-                    y0 = int(r - strip * p.OH);
-                    strip_set(int(strip % p.tilesX), strip / p.tilesX);
-                    const int h = chunk_rows(y0, r);
-                    rh_cur = (h + 7) >> 3;
-                    y_end = y0 + h;
-                }
+                // long chunks: a dozen divisions per chunk do not matter; with the ring the walk only has to be counted
+                // (the position comes from the ring entry at the top of the loop)
+                if (RING) { if (chunk_no >= n_chunks) break; }
+                else if (!next_chunk()) break;
             }
         }
         __syncthreads();
@@ -730,7 +809,8 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     p.splits = splits;
     p.cluster = 0;
     p.persist = 0;
-    p.rows_total = int64_t(p.tilesX) * p.NP * p.OH;
+    p.tiles_total = tiles;
+    p.waves = 0;
     TmapSet tmaps;
     memset(&tmaps, 0, sizeof(tmaps));
     bool ring = false;
@@ -746,13 +826,17 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
         }
         p.status = ctx->tma_status_dev;
         if (p.persist) {
-            // Every resident CTA slot gets an equal, contiguous share of the strip rows -- but not so many CTAs that a
-            // share shrinks to a few rows (each chunk re-reads KH - 1 halo rows and pays a fixed set-up).
+            // One resident wave of CTAs: whole waves of tiles first, then the rest in 8-row groups, at least two groups
+            // (16 rows) per CTA (each chunk re-reads KH - 1 halo rows and pays a fixed set-up).
             ring = p.NQ < 8;   // short chunks: decoding would cost as much as the chunk's arithmetic
-            const int64_t min_rows = 16;
-            grid = p.rows_total / min_rows;
-            if (grid > slots) grid = slots;
-            if (grid < 1) grid = 1;
+            grid = slots;
+            if (tiles < grid) {
+                grid = tiles * RH / 2;
+                if (grid > slots) grid = slots;
+                if (grid < 1) grid = 1;
+            }
+            p.waves = int(tiles / grid);
+            if (tiles / grid > 0x3fffffff) return -1;
         }
     }
     if (grid > 0x7fffffffLL) return -1;

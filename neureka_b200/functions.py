@@ -28,6 +28,7 @@ from . import _lib as L
 from . import backend as B
 from .backend import ExecutionCall
 from .device import CudaDevice
+from .ndconf import NDConfiguration
 from .tensor import Tensor
 
 # ---------------------------------------------------------------------------------------------------
@@ -370,6 +371,91 @@ def fused_expression_of(root: Node) -> Tuple[str, int]:
     return expr, highest[0] + 1
 
 
+def fused_gradient_terms_of(root: Node, target: int) -> Tuple[str, int]:
+    """The statement list nk_fused_compile_grad takes for the gradient of an elementwise expression w.r.t. input
+    `target`: reverse mode over the tree, one `term[l]` per occurrence of the input. Every step rounds to the tensor's
+    type exactly like the kernel the op-by-op backward pass would run at that node:
+      function f(c):          error_c = error * f'(c)            (FallbackAlgorithm.java:118-129: error times the eager derivative)
+      a + b, a - b:           error, error / error, 0 - error    (Addition.java:90-110: the error itself, reduced)
+      a * b:                  b * error, a * error                (Multiplication.java:51-71, handle times drain)
+      a / b, a % b, a ** b:   error * d(op)/d(operand)
+    Returns (statements, number of occurrences)."""
+    lines: List[str] = []
+    counter = [0]
+    leaves = [0]
+
+    def tmp(expr: str) -> str:
+        name = f"t{counter[0]}"
+        counter[0] += 1
+        lines.append(f"const T {name} = {expr};")
+        return name
+
+    def value(n: Node) -> str:
+        """forward value of a subtree as a named temporary (recomputed, rounded per operator)"""
+        if n.kind == "input":
+            return f"x{int(n.value)}"
+        if n.kind == "const":
+            return f"T({float(n.value)!r})"
+        if n.kind == "fun":
+            if n.value not in L.FUN_IDS:
+                raise ValueError(f"'{n.value}' is not an elementwise function and cannot be fused")
+            return tmp(f"f_{n.value}({value(n.children[0])})")
+        if n.kind == "op":
+            if n.value not in _FUSED_OPS:
+                raise ValueError(f"operator '{n.value}' is not elementwise and cannot be fused")
+            acc = value(n.children[0])
+            for c in n.children[1:]:
+                acc = tmp(f"{_FUSED_OPS[n.value]}({acc}, {value(c)})")
+            return acc
+        raise ValueError(f"cannot fuse node kind {n.kind}")
+
+    def back(n: Node, err: str) -> None:
+        if not n.depends_on(target):
+            return
+        if n.kind == "input":
+            lines.append(f"term[{leaves[0]}] = {err};")
+            leaves[0] += 1
+            return
+        if n.kind == "fun":
+            child = n.children[0]
+            back(child, tmp(f"op_mul({err}, df_{n.value}({value(child)}))"))
+            return
+        # n-ary chains nest to the left: ((c0 o c1) o c2) ...; walk from the outermost pair inwards
+        sym = n.value
+        kids = n.children
+        prefix = [value(kids[0])]
+        for c in kids[1:-1]:
+            prefix.append(tmp(f"{_FUSED_OPS[sym]}({prefix[-1]}, {value(c)})"))
+        e = err
+        for i in range(len(kids) - 1, 0, -1):
+            a, b_node = prefix[i - 1], kids[i]
+            if b_node.depends_on(target) or any(k.depends_on(target) for k in kids[:i]):
+                b = value(b_node)
+            if sym == "+":
+                eb, ea = e, e
+            elif sym == "-":
+                eb, ea = (tmp(f"op_sub(T(0), {e})") if b_node.depends_on(target) else None), e
+            elif sym == "*":
+                eb = tmp(f"op_mul({a}, {e})") if b_node.depends_on(target) else None
+                ea = tmp(f"op_mul({b}, {e})") if any(k.depends_on(target) for k in kids[:i]) else None
+            else:
+                d = {"/": "dop_div", "%": "dop_mod", "**": "dop_pow"}[sym]
+                eb = tmp(f"op_mul({e}, {d}(1, {a}, {b}))") if b_node.depends_on(target) else None
+                ea = tmp(f"op_mul({e}, {d}(0, {a}, {b}))") if any(k.depends_on(target) for k in kids[:i]) else None
+            if b_node.depends_on(target):
+                back(b_node, eb)
+            e = ea
+            if e is None:
+                break
+        if e is not None:
+            back(kids[0], e)
+
+    back(root, "e")
+    if leaves[0] == 0:
+        raise ValueError(f"the expression does not depend on input {target}")
+    return " ".join(lines), leaves[0]
+
+
 class FusedOperation:
     """What CudaDevice.optimized_operation_of returns: one kernel for a whole elementwise Function, compiled per
     item type on first use. Calling it allocates the (broadcast-shaped) output on the device and launches once."""
@@ -387,10 +473,19 @@ class FusedOperation:
             self._handles[dt] = h
         return h
 
-    def __call__(self, *inputs: Tensor) -> Tensor:
+    def _grad_handle(self, dt: int, target: int):
+        key = (dt, target)
+        h = self._handles.get(key)
+        if h is None:
+            terms, leaves = fused_gradient_terms_of(self.function.root, target)
+            h = C.c_void_p()
+            L.check(L.lib.nk_fused_compile_grad(self.device.ctx, dt, self.n_inputs, target, leaves, terms.encode(), C.byref(h)), self.device.ctx)
+            self._handles[key] = h
+        return h
+
+    def _fit(self, inputs):
         if len(inputs) != self.n_inputs:
             raise ValueError(f"{self.name} takes {self.n_inputs} inputs, got {len(inputs)}")
-        dev = self.device
         tensors = make_fit(list(inputs)) if len({t.rank for t in inputs}) > 1 else list(inputs)
         rank = tensors[0].rank
         shape = []
@@ -399,21 +494,68 @@ class FusedOperation:
             if len(ext) > 1:
                 raise ValueError(f"shapes {[t.shape for t in tensors]} cannot be broadcast")
             shape.append(ext.pop() if ext else 1)
-        dt = B.nk_dtype(tensors[0].dtype)
         for t in tensors:
             if t.dtype != tensors[0].dtype:
                 raise ValueError("all tensors of a call must have the same item type")
             t.set_is_virtual(False)
-            if not dev.has(t):
+            if not self.device.has(t):
                 raise ValueError("every input of a fused operation must be stored on its device")
-        out = _new_output(tensors[0].dtype, tuple(shape), dev)
+        return tensors, tuple(shape)
+
+    @staticmethod
+    def _operands(tensors):
         cfgs = [t.ndconf.as_inline_array() for t in tensors]
         cfg_ptrs = (C.POINTER(C.c_int32) * len(tensors))(*[c.ctypes.data_as(C.POINTER(C.c_int32)) for c in cfgs])
         bufs = (C.c_void_p * len(tensors))(*[t._data.buf for t in tensors])
+        return cfgs, cfg_ptrs, bufs
+
+    def __call__(self, *inputs: Tensor) -> Tensor:
+        dev = self.device
+        tensors, shape = self._fit(inputs)
+        rank = tensors[0].rank
+        dt = B.nk_dtype(tensors[0].dtype)
+        out = _new_output(tensors[0].dtype, shape, dev)
+        cfgs, cfg_ptrs, bufs = self._operands(tensors)
         c0 = out.ndconf.as_inline_array()
         L.check(L.lib.nk_fused_run(dev.ctx, self._handle(dt), rank, out._data.buf, c0.ctypes.data_as(C.POINTER(C.c_int32)), bufs, cfg_ptrs), dev.ctx)
         out.version += 1
+        if self.function.do_ad:
+            # one ADAction per differentiable input: the whole backward of the expression for that input, reduction over
+            # its broadcast dims included, is one kernel (gradient)
+            from . import autograd
+            parents = []
+            for j, (orig, fitted) in enumerate(zip(inputs, tensors)):
+                if autograd._tracks(orig) and self.function.root.depends_on(j):
+                    parents.append((orig, lambda err, j=j, tensors=tensors: self.gradient(j, err, *tensors)))
+            if parents:
+                out.graph_node = autograd.GraphNode(out, parents)
         return out
+
+    def gradient(self, target: int, error: Tensor, *inputs: Tensor) -> Tensor:
+        """d(sum(error * f(inputs))) / d(inputs[target]), shaped like that input: the error (result-shaped, or one virtual
+        value as the backward pass of a sum hands it over) is multiplied through the expression and summed over the dims
+        the input is broadcast along, in one kernel."""
+        dev = self.device
+        tensors, shape = self._fit(inputs)
+        rank = tensors[0].rank
+        dt = B.nk_dtype(tensors[0].dtype)
+        if not dev.has(error):
+            dev.store(error)
+        err = error
+        if err.rank != rank:
+            err = make_fit([err, tensors[0]])[0] if err.size > 1 else Tensor.of(err.dtype, shape, float(dev.access(err).read_at(0)))
+            if not dev.has(err):
+                dev.store(err)
+        grad = _new_output(tensors[target].dtype, tensors[target].shape, dev)
+        cfgs, cfg_ptrs, bufs = self._operands(tensors)
+        # a virtual error (one value standing for all, as the backward pass of a sum hands it over) stays one element:
+        # its configuration maps every index to element 0
+        ce_conf = NDConfiguration.virtual_of(err.shape) if err.is_virtual else err.ndconf
+        cg, ce = grad.ndconf.as_inline_array(), ce_conf.as_inline_array()
+        L.check(L.lib.nk_fused_run_grad(dev.ctx, self._grad_handle(dt, target), rank, grad._data.buf, cg.ctypes.data_as(C.POINTER(C.c_int32)),
+                                        err._data.buf, ce.ctypes.data_as(C.POINTER(C.c_int32)), bufs, cfg_ptrs), dev.ctx)
+        grad.version += 1
+        return grad
 
     def close(self) -> None:
         for h in self._handles.values():

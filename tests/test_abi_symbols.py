@@ -70,13 +70,35 @@ def test_host_only_generator_library_matches_the_cuda_library_and_splits_one_str
     assert a1.size == 65536 and k1.size == 25 and np.abs(a1).max() <= 1.0
 
 
-def test_fused_plan_switches_to_64_bit_counters_before_32_bit_ones_can_wrap():
+def test_slab_planner_through_the_abi_matches_the_host_planner():
+    """nk_group_plan_slabs (what nk_conv_sharded splits with) against neureka_b200.sharding.plan_slabs."""
     from neureka_b200 import _lib as L
-    wide = L.lib.nk_fused_plan_is_wide
-    grid = 148 * 16
-    assert wide(1000, 2000, grid) == 0
-    assert wide((1 << 32) - grid - 1, 1000, grid) == 0
-    assert wide((1 << 32) - grid, 1000, grid) == 1          # the unit counter steps by the grid size past 2^32
-    assert wide(1 << 31, (1 << 32) - 2, grid) == 1            # the second row of the last group: row index 2^32 - 1 + 1
-    assert wide(1 << 31, (1 << 32) - 3, grid) == 0
-    assert wide(1 << 33, 1 << 34, grid) == 1
+    from neureka_b200.sharding import plan_slabs
+    for extent, parts, halo in [(2044, 8, 4), (2044, 1, 4), (7, 8, 2), (10, 3, 0), (1, 2, 6), (122, 5, 6)]:
+        arrs = [(C.c_int64 * parts)() for _ in range(4)]
+        assert L.lib.nk_group_plan_slabs(extent, parts, halo, *arrs) == 0
+        want = plan_slabs(extent, parts, halo)
+        assert [int(x) for x in arrs[0]] == [s.out_lo for s in want]
+        assert [int(x) for x in arrs[1]] == [s.out_len for s in want]
+        assert [int(x) for x in arrs[2]] == [s.in_lo for s in want]
+        assert [int(x) for x in arrs[3]] == [s.in_len for s in want]
+    arrs = [(C.c_int64 * 2)() for _ in range(4)]
+    assert L.lib.nk_group_plan_slabs(0, 2, 1, *arrs) == L.NK_ERR_BAD_ARG
+    assert L.lib.nk_group_open(None, 0, None) == L.NK_ERR_BAD_ARG
+
+
+def test_fused_gradient_statements():
+    """The statement list handed to nk_fused_compile_grad: one term per occurrence of the input, the error multiplied
+    through the tree with one rounding per node."""
+    from neureka_b200.functions import Function, fused_gradient_terms_of
+    f = Function.of("tanh(i0*i1+i1)", False)
+    terms, leaves = fused_gradient_terms_of(f.root, 0)
+    assert leaves == 1 and "df_tanh" in terms and terms.rstrip().endswith("term[0] = t4;") and "op_mul(x1, t2)" in terms
+    terms, leaves = fused_gradient_terms_of(f.root, 1)
+    assert leaves == 2 and "term[0] = t2;" in terms and "op_mul(x0, t2)" in terms
+    g = Function.of("i0/i1 - i1**i0", False)
+    terms, leaves = fused_gradient_terms_of(g.root, 1)
+    assert leaves == 2 and "dop_pow(0, x1, x0)" in terms and "dop_div(1, x0, x1)" in terms and "op_sub(T(0), e)" in terms
+    import pytest
+    with pytest.raises(ValueError):
+        fused_gradient_terms_of(Function.of("relu(i0)", False).root, 1)

@@ -43,7 +43,7 @@ def test_fused_equals_op_by_op_bit_for_bit(device, dt, expr, shapes):
     fused = device.optimized_operation_of(f, "fused_test")
     before = device.launch_count()
     got = fused(*tensors)
-    assert device.launch_count() - before == 1 and device.last_kernel() == "nk_fused_kernel"
+    assert device.launch_count() - before == 1 and device.last_kernel() in ("nk_fused_kernel", "nk_fused_rows_kernel")
     assert got.shape == want.shape
     assert _same_bits(got.items, want.items), np.abs(got.items - want.items).max()
     fused.close()
@@ -84,6 +84,73 @@ def test_fused_config3_scaled(device):
         g = device.access(got).read_array(start, 4096)
         w = device.access(want).read_array(start, 4096)
         assert _same_bits(g, w)
+    fused.close()
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
+@pytest.mark.parametrize("expr,shapes", [
+    ("tanh(i0*i1+i1)", [[64, 1, 96], [1, 48, 96]]),                      # BASELINE config 3 in small: b occurs twice
+    ("i0*i1 - i2", [[5, 1, 32], [1, 7, 32], [5, 7, 1]]),                 # the innermost dim is summed away for i2
+    ("relu(i0) + sig(i0) * i1", [[40, 52], [40, 52]]),                    # no broadcasting: nothing to reduce
+    ("sin(i0) * i1", [[33, 20], [1, 1]]),                                 # a single element against a matrix
+])
+def test_fused_backward_equals_op_by_op_bit_for_bit(device, dt, expr, shapes):
+    """backward() through a fused operation: per input one kernel that multiplies the error through the expression and
+    sums over the dims that input is broadcast along. Every product rounds like the op-by-op pass, every occurrence of an
+    input is summed separately in the reduction kernels' order, and these expressions reduce at one node each: the
+    gradients equal the op-by-op gradients bit for bit. The forward result is checked on the way."""
+    rng = np.random.default_rng(47)
+    hosts = [rng.uniform(-2.0, 2.0, size=int(np.prod(s))).astype(dt) for s in shapes]
+    out_shape = [max(s[k] for s in shapes) for k in range(len(shapes[0]))]
+    err_h = rng.uniform(-1.0, 1.0, size=int(np.prod(out_shape))).astype(dt)
+
+    def run(make_result):
+        ts = [Tensor.of(dt, s, h).set_rqs_gradient(True).to(device) for s, h in zip(shapes, hosts)]
+        y = make_result(ts)
+        y.backward(Tensor.of(dt, out_shape, err_h))
+        return y.items, [t.gradient.items for t in ts]
+
+    f = Function.of(expr)
+    fused = device.optimized_operation_of(f, "fused_backward_test")
+    y_ref, g_ref = run(lambda ts: f(*ts))
+    n0 = device.launch_count()
+    y_fus, g_fus = run(lambda ts: fused(*ts))
+    assert _same_bits(y_fus, y_ref)
+    for j, (a, b) in enumerate(zip(g_fus, g_ref)):
+        assert a.shape == b.shape
+        assert _same_bits(a, b), (j, np.abs(a - b).max())
+    fused.close()
+
+
+def test_fused_backward_of_a_sum_takes_one_kernel_per_input(device, oracle):
+    """sum(tanh(a*b+b)).backward() with a [n,1,k], b [1,m,k] through the fused operation: the virtual all-ones error stays
+    one element, each gradient is one launch of the gradient kernel, and no result-sized tensor besides the forward
+    result exists. Checked against float64 sums of the oracle's tanh derivative."""
+    from neureka_b200.ndconf import NDConfiguration as ND
+    import baseline_configs as BC
+    n, m, k = 48, 40, 256
+    a_h, b_h = BC.cfg3_inputs(n, m, k)
+    a = Tensor.of(np.float32, [n, 1, k], a_h).set_rqs_gradient(True).to(device)
+    b = Tensor.of(np.float32, [1, m, k], b_h).set_rqs_gradient(True).to(device)
+    fused = device.optimized_operation_of(Function.of("tanh(i0*i1+i1)"), "cfg3")
+    y = fused(a, b)
+    s = y.sum()
+    n0 = device.launch_count()
+    s.backward()
+    kernels = device.launch_count() - n0
+    assert device.last_kernel() != "" and kernels <= 8, kernels     # two gradient kernels + the assigns into .gradient
+    A, Bm = a_h.reshape(n, 1, k).astype(np.float32), b_h.reshape(1, m, k).astype(np.float32)
+    u = (A * Bm).astype(np.float32) + Bm
+    g = np.zeros(u.size, dtype=np.float32)
+    c = ND.of_shape([u.size]).as_inline_array()
+    oracle.unary("tanh", g, c, np.ascontiguousarray(u.reshape(-1)), c, d=0)
+    g = g.reshape(n, m, k).astype(np.float64)
+    da = (g * Bm).sum(axis=1)
+    db = (g * (A.astype(np.float64) + 1)).sum(axis=0)
+    mag_a = (np.abs(g) * np.abs(Bm)).sum(axis=1)
+    mag_b = (np.abs(g) * (np.abs(A) + 1)).sum(axis=0)
+    assert np.all(np.abs(a.gradient.items.reshape(n, k) - da) <= 1e-5 * mag_a + 1e-30)
+    assert np.all(np.abs(b.gradient.items.reshape(m, k) - db) <= 1e-5 * mag_b + 1e-30)
     fused.close()
 
 
