@@ -183,6 +183,13 @@ int nk_timer_end(nk_ctx* ctx, float* out_ms);            /* second event + synch
  * denominator for the FMA-bound kernels (F32 stencil, F64 convolution, double-evaluated activations). */
 int nk_measure_fma_peak(nk_ctx* ctx, int32_t dtype, double* out_tflops);
 
+/* Operations Min / Max: replaces CLReduce (J/backend/main/operations/linear/internal/opencl/CLReduce.java:34-147) with
+ * the CPU implementation's semantics (J/backend/main/operations/other/internal/CPUReduce.java:72-140): writes ONE int, the
+ * flat index of the smallest (want_max = 0) or largest element of the view, to element out_index of an I32 buffer.
+ * Strict comparison: among equal extremes the lowest index wins. A NaN is never selected unless all elements are NaN
+ * (the reference's choice then depends on its 64-element tiling). F32 / F64, fewer than 2^31 elements. */
+int nk_arg_reduce(nk_ctx* ctx, int32_t want_max, int32_t dtype, int32_t rank, nk_buf* src, const int32_t* cfg, nk_buf* out_i32, int64_t out_index);
+
 /* ---- fused elementwise expressions, compiled at run time ----
  * Counterpart of the kernels the reference generates for Device.optimizedOperationOf(Function, name)
  * (src/main/java/neureka/devices/Device.java:216-241; model: src/main/java/neureka/devices/opencl/utility/CLFunctionCompiler.java:47-196), plus

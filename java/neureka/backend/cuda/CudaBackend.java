@@ -34,14 +34,29 @@ public final class CudaBackend implements BackendExtension
 {
     private final List<CudaDevice> _devices = new ArrayList<>();
 
-    public CudaBackend() { _devices.add(new CudaDevice(0)); }
+    /** One CudaDevice per visible GPU; all of them are members of one native device group (nk_group_open: peer access
+     *  between the members is enabled once), so that CudaKernels.convSharded can cut a large convolution across them. */
+    public CudaBackend() {
+        int n = CudaDevice.count();
+        for ( int i = 0; i < Math.max(n, 1); i++ ) _devices.add(new CudaDevice(i));
+    }
 
+    /** "cuda" / "gpu" / "nvidia" / "first" / "b200" -> the first GPU; "cuda:2", "gpu:2" or a plain "2" -> that ordinal
+     *  (the keyword scheme Device.get uses for OpenCL devices, devices/Query.java:22-24). */
     @Override public DeviceOption find( String key ) {
         String k = key.trim().toLowerCase();
-        if ( k.equals("cuda") || k.equals("gpu") || k.equals("nvidia") || k.equals("first") || k.equals("b200") )
-            return new DeviceOption(_devices.get(0), 1.0);
+        int ordinal = -1;
+        if ( k.equals("cuda") || k.equals("gpu") || k.equals("nvidia") || k.equals("first") || k.equals("b200") ) ordinal = 0;
+        else {
+            String digits = k.startsWith("cuda:") || k.startsWith("gpu:") ? k.substring(k.indexOf(':') + 1) : k;
+            if ( !digits.isEmpty() && digits.chars().allMatch(Character::isDigit) ) ordinal = Integer.parseInt(digits);
+        }
+        if ( ordinal >= 0 && ordinal < _devices.size() ) return new DeviceOption(_devices.get(ordinal), 1.0);
         return new DeviceOption(null, 0.0);
     }
+
+    /** The devices of this backend, in ordinal order (the members of the native group). */
+    public List<CudaDevice> devices() { return java.util.Collections.unmodifiableList(_devices); }
 
     @Override public void dispose() { _devices.forEach(CudaDevice::dispose); _devices.clear(); }
     @Override public boolean update( OwnerChangeRequest<Extensions> changeRequest ) { return true; }

@@ -40,6 +40,17 @@ public final class CudaDevice extends AbstractDevice<Number>
         _ordinal = ordinal;
     }
 
+    /** Number of CUDA devices the library sees (nk_device_count). */
+    public static int count() {
+        try ( Arena a = Arena.ofConfined() ) {
+            MemorySegment out = a.allocate(ValueLayout.JAVA_INT);
+            NeurekaCuda.check((int) NeurekaCuda.DEVICE_COUNT.invokeExact(out), MemorySegment.NULL);
+            return out.get(ValueLayout.JAVA_INT, 0);
+        } catch ( RuntimeException e ) { throw e; } catch ( Throwable t ) { throw new IllegalStateException(t); }
+    }
+
+    public int ordinal() { return _ordinal; }
+
     static int typeOf( Class<?> c ) {
         if ( c == Float.class   ) return NeurekaCuda.F32;
         if ( c == Double.class  ) return NeurekaCuda.F64;

@@ -46,6 +46,20 @@ public final class NeurekaCuda
     static final MethodHandle FUSED_COMPILE = h("nk_fused_compile", FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS));
     static final MethodHandle FUSED_RUN     = h("nk_fused_run",     FunctionDescriptor.of(JAVA_INT, ADDRESS, ADDRESS, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS));
     static final MethodHandle FUSED_FREE    = h("nk_fused_free",    FunctionDescriptor.of(JAVA_INT, ADDRESS));
+    // backward of a fused expression w.r.t. one input, reduction over that input's broadcast dims included
+    static final MethodHandle FUSED_COMPILE_GRAD = h("nk_fused_compile_grad", FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS));
+    static final MethodHandle FUSED_RUN_GRAD     = h("nk_fused_run_grad",     FunctionDescriptor.of(JAVA_INT, ADDRESS, ADDRESS, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS));
+
+    // memory a second process may open (nk_ipc_export); everything else comes from the stream-ordered pool behind nk_alloc
+    static final MethodHandle ALLOC_SHARED  = h("nk_alloc_shared",  FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_LONG, ADDRESS));
+
+    // several GPUs in this JVM: one context per member, peer access enabled once, halo-split convolution across the members
+    static final MethodHandle GROUP_OPEN    = h("nk_group_open",    FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, ADDRESS));
+    static final MethodHandle GROUP_SIZE    = h("nk_group_size",    FunctionDescriptor.of(JAVA_INT, ADDRESS, ADDRESS));
+    static final MethodHandle GROUP_CTX     = h("nk_group_ctx",     FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, ADDRESS));
+    static final MethodHandle GROUP_CLOSE   = h("nk_group_close",   FunctionDescriptor.of(JAVA_INT, ADDRESS));
+    static final MethodHandle GROUP_PLAN    = h("nk_group_plan_slabs", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_LONG, ADDRESS, ADDRESS, ADDRESS, ADDRESS));
+    static final MethodHandle CONV_SHARDED  = h("nk_conv_sharded",  FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, JAVA_INT, ADDRESS, ADDRESS, ADDRESS));
 
     private NeurekaCuda() {}
 

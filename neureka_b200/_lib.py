@@ -89,6 +89,7 @@ SIGNATURES = {
     "nk_scalar_binary": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _cfg, _vp, _cfg, _dbl, _i32]),
     "nk_fill_fun": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _cfg, _dbl, _i32]),
     "nk_sum": (C.c_int, [_vp, _i32, _i32, _vp, _cfg, _vp, _i64]),
+    "nk_arg_reduce": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _cfg, _vp, _i64]),
     "nk_sum_static": (C.c_int, [_vp, _i32, _i32, _vp, _cfg, _vp, _i64]),
     "nk_set_conv_path": (C.c_int, [_vp, _i32]),
     "nk_last_conv_path": (C.c_int, [_vp, C.POINTER(_i32)]),

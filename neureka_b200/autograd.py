@@ -140,6 +140,30 @@ def _record_function(fid: str, x: Tensor, out: Tensor) -> None:
     out.graph_node = GraphNode(out, [(x, action)])
 
 
+def dot(a: Tensor, b: Tensor) -> Tensor:
+    """a.dot(b) with its ADActions: the gradient of either vector is the error times the other one, which is what the
+    convolution's recipe yields for two equal shapes (Convolution.java:56-89 -> XConvRight(error, other, zeros))."""
+    out = F.run_dot(a, b)
+    _record_operator("x", a, b, out)
+    return out
+
+
+def extreme(x: Tensor, want_max: bool) -> Tensor:
+    """x.min() / x.max(): Min.java:44-66 -- the ADAction builds a zero tensor of the input's shape and puts the (one
+    element) error at the index of the extreme item."""
+    out, index = F.run_extreme(want_max, x)
+    if _tracks(x):
+        def action(err, x=x, index=index):
+            dev = err.device or x.device
+            g = Tensor.of(x.dtype, x.shape, 0).set_is_virtual(False)
+            dev.store(g)
+            value = float(dev.access(err).read_at(0))
+            dev.access(g).write(value).at(g.ndconf.index_of_index(index))
+            return g
+        out.graph_node = GraphNode(out, [(x, action)])
+    return out
+
+
 def evaluate(node, inputs: List[Tensor], do_ad: bool) -> Tensor:
     """Executes an expression tree bottom-up (no fusion), recording ADActions when do_ad."""
     if node.kind == "input":

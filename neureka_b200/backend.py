@@ -29,6 +29,8 @@ ELEMENTWISE = "ElementwiseAlgorithm"
 SCALAR_ALGORITHM = "ScalarAlgorithm"
 SCALAR_BROADCAST = "ScalarBroadcast"
 SUM_ALGORITHM = "SumAlgorithm"
+MIN_ALGORITHM, MAX_ALGORITHM = "min_algorithm", "max_algorithm"
+DOT_ALGORITHM = "DotProductAlgorithm"
 
 OPERATORS = ["**", "/", "*", "%", "-", "+"]                       # Power ... Addition
 CONV_OPS = ["x", "«x", "x»"]                            # Convolution, XConvLeft, XConvRight
@@ -224,6 +226,24 @@ class CudaSum(ImplementationFor):
         return out
 
 
+class CudaReduce(ImplementationFor):
+    """Replaces CLReduce (operations/linear/internal/opencl/CLReduce.java:34-147; CPU twin operations/other/internal/CPUReduce.java):
+    the flat index of the smallest / largest element as a [1] tensor of ints."""
+
+    def __init__(self, want_max: bool):
+        self.want_max = 1 if want_max else 0
+
+    def run(self, call: ExecutionCall) -> Tensor:
+        dev = call.device
+        src = call.input(0) if call.input(0) is not None else call.input(1)
+        src.set_is_virtual(False)
+        out = Tensor.of(np.int32, (1,), [0])
+        dev.store(out)
+        k, c = _cfg(src)
+        L.check(L.lib.nk_arg_reduce(dev.ctx, self.want_max, nk_dtype(src.dtype), src.rank, src._data.buf, c, out._data.buf, 0), dev.ctx)
+        return out
+
+
 class CudaBackend:
     """BackendExtension for the CUDA device (src/main/java/neureka/backend/api/BackendExtension.java:15-70).
 
@@ -252,6 +272,11 @@ class CudaBackend:
             self._set(name, SCALAR_ALGORITHM, CudaScalarFunction(fid))
             self._set(name, SCALAR_BROADCAST, CudaScalarBroadcastFunction(fid))
         self._set("sumItems", SUM_ALGORITHM, CudaSum())
+        self._set("min", MIN_ALGORITHM, CudaReduce(False))
+        self._set("max", MAX_ALGORITHM, CudaReduce(True))
+        # DotProduct (linear/DotProduct.java; CLDot / CPUDot): two vectors of one length are the `x` call whose single dim
+        # is summed away -- the convolution implementation serves it (its long-reduction kernel)
+        self._set("dot", DOT_ALGORITHM, CudaConvolution())
 
     def implementation_for(self, operation: str, algorithm: str) -> ImplementationFor:
         try:

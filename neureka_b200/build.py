@@ -44,6 +44,7 @@ SOURCES = [
     ("nk_conv_wgrad_inst_f64.cu", []),
     ("nk_fused.cu", ["-I", OBJDIR]),
     ("nk_group.cu", []),
+    ("nk_reduce.cu", []),
     ("nk_probe.cu", []),
     ("nk_sum_static.cu", ["-fmad=false"]),
     ("nk_jrand.cpp", ["-Xcompiler", "-ffp-contract=off"]),

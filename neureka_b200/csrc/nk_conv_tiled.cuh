@@ -408,21 +408,6 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             }
         }
     };
-    // the same for a rows-per-warp value known only at run time (chunks of a balanced walk)
-    auto consume_rows = [&](int rh, int stage, int c) {
-        if constexpr (!TMA) { consume(NkRows<RH>{}, stage, c); return; }
-        switch (rh) {
-            case 1: consume(NkRows<1>{}, stage, c); break;
-            case 2: if constexpr (RH >= 2) consume(NkRows<2>{}, stage, c); break;
-            case 3: if constexpr (RH >= 3) consume(NkRows<3>{}, stage, c); break;
-            case 4: if constexpr (RH >= 4) consume(NkRows<4>{}, stage, c); break;
-            case 5: if constexpr (RH >= 5) consume(NkRows<5>{}, stage, c); break;
-            case 6: if constexpr (RH >= 6) consume(NkRows<6>{}, stage, c); break;
-            case 7: if constexpr (RH >= 7) consume(NkRows<7>{}, stage, c); break;
-            default: if constexpr (RH >= 8) consume(NkRows<8>{}, stage, c); break;
-        }
-    };
-
     // Stores this thread's results of the tile / chunk the thread currently stands on (rh_cur rows per warp, rows below
     // y_end only): into the drain, or -- two-pass channel split -- into this part's plane of the scratch buffer.
     auto store_tile = [&]() {
@@ -620,21 +605,27 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                     y_end = a.y + a.w;
                     baseO = *reinterpret_cast<const int64_t*>(e + 1);
                 }
-                if (p.persist) {
+                // the channel loop of one chunk, specialised on the rows per warp: the switch sits outside the loop, so the
+                // loop body is straight-line code the compiler can schedule across iterations, as for a fixed tile height
+                auto run_chunk = [&](auto rows_tag) {
                     for (int c = c_begin; c < c_end; c++, g++) {
                         const int stage = g % STAGES;
                         if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; break; }
-                        consume_rows(rh_cur, stage, c);
+                        consume(rows_tag, stage, c);
                         __syncwarp();
                         if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
                     }
-                } else {
-                    for (int c = c_begin; c < c_end; c++, g++) {
-                        const int stage = g % STAGES;
-                        if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; break; }
-                        consume(NkRows<RH>{}, stage, c);
-                        __syncwarp();
-                        if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
+                };
+                if (!p.persist || rh_cur == RH) run_chunk(NkRows<RH>{});
+                else {
+                    switch (rh_cur) {
+                        case 1: run_chunk(NkRows<1>{}); break;
+                        case 2: if constexpr (RH > 2) run_chunk(NkRows<2>{}); break;
+                        case 3: if constexpr (RH > 3) run_chunk(NkRows<3>{}); break;
+                        case 4: if constexpr (RH > 4) run_chunk(NkRows<4>{}); break;
+                        case 5: if constexpr (RH > 5) run_chunk(NkRows<5>{}); break;
+                        case 6: if constexpr (RH > 6) run_chunk(NkRows<6>{}); break;
+                        default: if constexpr (RH > 7) run_chunk(NkRows<7>{}); break;
                     }
                 }
                 if (!ok || !p.persist) break;   // one tile per CTA: its epilogue follows below

@@ -243,6 +243,39 @@ def run_xconv(op: str, i0: Tensor, i1: Tensor, i2: Tensor) -> Tensor:
     return _execute_on_common_device(call, B.backend().implementation_for(op, B.ND_CONVOLUTION))
 
 
+def run_dot(a: Tensor, b: Tensor) -> Tensor:
+    """Operation "dot" (linear/DotProduct.java; CPUDot.java:11-40): two vectors of the same length and type -> [1]."""
+    if a.rank != 1 or b.rank != 1:
+        raise ValueError("Dot product only works on vectors.")
+    if a.shape[0] != b.shape[0]:
+        raise ValueError("Dot product only works on vectors of the same length.")
+    if a.dtype != b.dtype:
+        raise ValueError("Type inconsistency between provided tensors encountered. All tensors must be of the same type.")
+    dev = _common_device([a, b])
+    out = _new_output(a.dtype, (1,), dev)
+    call = ExecutionCall([out, a, b], "dot", dev, -1)
+    return _execute_on_common_device(call, B.backend().implementation_for("dot", B.DOT_ALGORITHM))
+
+
+def run_extreme(want_max: bool, x: Tensor):
+    """Operations "min" / "max" (operations/other/Min.java:21-75, Max.java): the device implementation returns the index of
+    the extreme element, the operation reads the item there into a [1] tensor. Returns (result, index)."""
+    dev = _common_device([x])
+    name, algo = ("max", B.MAX_ALGORITHM) if want_max else ("min", B.MIN_ALGORITHM)
+    call = ExecutionCall([x], name, dev, -1)
+    index = _execute_on_common_device(call, B.backend().implementation_for(name, algo))
+    i = int(dev.access(index).read_at(0))
+    dev.free(index)
+    x.set_is_virtual(False)
+    off = x.ndconf.index_of_index(i)                 # the element's place in the data array (one read, not the whole tensor)
+    value = dev.access(x).read_array(off, 1)[0]
+    out = Tensor.of(x.dtype, (1,), [value])
+    out.set_is_virtual(False)
+    out.is_intermediate = True
+    dev.store(out)
+    return out, i
+
+
 def run_matmul(a: Tensor, b: Tensor) -> Tensor:
     """Operation "@" (linear/MatMul.java:15-40, algorithms/MatMulAlgorithm.java:62-84): [M,K] @ [K,N] -> [M,N], output
     allocated zero-filled in the operands' type. On this backend a matrix product is a convolution in which every

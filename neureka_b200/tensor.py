@@ -266,6 +266,20 @@ class Tensor:
     def sum(self):
         return self._fn().Function.of("sumItems(I[0])").call(self)
 
+    def dot(self, other):
+        """Tensor.dot (linear/DotProduct.java): two vectors -> a [1] tensor; differentiable like `x`."""
+        from . import autograd
+        return autograd.dot(self, other)
+
+    def min(self):
+        """Tensor.min (operations/other/Min.java): the smallest item as a [1] tensor; backward puts the error at its index."""
+        from . import autograd
+        return autograd.extreme(self, False)
+
+    def max(self):
+        from . import autograd
+        return autograd.extreme(self, True)
+
     def backward(self, error=None):
         from . import autograd
         autograd.backward(self, error)

@@ -934,3 +934,47 @@ void orc_fill_randomly(int dtype, void* out, int64_t n, int64_t seed) {
 }
 
 }  // extern "C"
+
+// ---- MatMul and DotProduct (the CPU implementations the `@` and `dot` operations run) -------------------------------------
+// CPUMatMul (implementations/matmul/CPUMatMul.java:30-110) hands dense row-major F32/F64 matrices to
+// GEMM.operationForF32/F64 (operations/linear/internal/blas/GEMM.java:55-125); every variant it picks adds the products of one
+// output in rising order of the common index into a product array that starts at zero -- the general row-major one
+// (partial_F32_MxN_RM, GEMM.java:282-305) as one AXPY per (common index c, left row j):
+// product[j, :] += left[j, c] * right[c, :] (AXPY.java: y[i] += a * x[i], a separate multiply and add). Restated as such.
+template <class T>
+static void matmul_rm(T* product, const T* left, const T* right, int64_t rows, int64_t complexity, int64_t cols) {
+    for (int64_t i = 0; i < rows * cols; i++) product[i] = T(0);
+    for (int64_t c = 0; c < complexity; c++)
+        for (int64_t j = 0; j < rows; j++) {
+            const T a = left[c + j * complexity];
+            T* y = product + j * cols;
+            const T* x = right + c * cols;
+            for (int64_t i = 0; i < cols; i++) y[i] = y[i] + a * x[i];
+        }
+}
+extern "C" void orc_matmul(int dtype, void* product, const void* left, const void* right, int64_t rows, int64_t complexity, int64_t cols) {
+    if (dtype == 0) matmul_rm((float*)product, (const float*)left, (const float*)right, rows, complexity, cols);
+    else matmul_rm((double*)product, (const double*)left, (const double*)right, rows, complexity, cols);
+}
+
+// CPUDot (implementations/linear/CPUDot.java:11-90) -> DOT.unrolled04 (operations/linear/internal/blas/DOT.java:148-179): four
+// partial sums over the elements i % 4 == 0..3 of the largest multiple of four, the remainder into the first one, then
+// sum0 + sum1 + sum2 + sum3 left to right.
+template <class T>
+static T dot_unrolled04(const T* a, const T* b, int64_t n) {
+    const int64_t remainder = n % 4;
+    T s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+    int64_t i = 0;
+    for (const int64_t lim = n - remainder; i < lim; i += 4) {
+        s0 += a[i] * b[i];
+        s1 += a[i + 1] * b[i + 1];
+        s2 += a[i + 2] * b[i + 2];
+        s3 += a[i + 3] * b[i + 3];
+    }
+    for (; i < n; i++) s0 += a[i] * b[i];
+    return s0 + s1 + s2 + s3;
+}
+extern "C" double orc_dot(int dtype, const void* a, const void* b, int64_t n) {
+    if (dtype == 0) return double(dot_unrolled04((const float*)a, (const float*)b, n));
+    return dot_unrolled04((const double*)a, (const double*)b, n);
+}

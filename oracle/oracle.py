@@ -46,6 +46,9 @@ def _load():
     lib.orc_fun32.restype = C.c_float
     lib.orc_sum.argtypes = [i32, vp, i64]
     lib.orc_sum.restype = dbl
+    lib.orc_matmul.argtypes = [i32, vp, vp, vp, i64, i64, i64]
+    lib.orc_dot.argtypes = [i32, vp, vp, i64]
+    lib.orc_dot.restype = dbl
     lib.orc_layout.argtypes = [i32, cfg]
     lib.orc_is_simple.argtypes = [i32, cfg]
     lib.orc_index_of_index.argtypes = [i32, cfg, i64]
@@ -124,6 +127,22 @@ def fun32(fun, x, derive=False) -> np.float32:
 def cpu_sum(a: np.ndarray) -> float:
     a = np.ascontiguousarray(a)
     return _lib.orc_sum(_dt(a), _p(a), a.size)
+
+
+def matmul(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """CPUMatMul on dense row-major matrices [M,K] @ [K,N] (F32 or F64), the reference's summation order."""
+    assert a.dtype == b.dtype and a.ndim == 2 and b.ndim == 2 and a.shape[1] == b.shape[0]
+    a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+    out = np.zeros((a.shape[0], b.shape[1]), dtype=a.dtype)
+    _lib.orc_matmul(_dt(a), _p(out), _p(a), _p(b), a.shape[0], a.shape[1], b.shape[1])
+    return out
+
+
+def dot(a: np.ndarray, b: np.ndarray) -> float:
+    """CPUDot on two vectors of one type (DOT.unrolled04's four partial sums)."""
+    assert a.dtype == b.dtype and a.size == b.size
+    a, b = np.ascontiguousarray(a).reshape(-1), np.ascontiguousarray(b).reshape(-1)
+    return float(_lib.orc_dot(_dt(a), _p(a), _p(b), a.size))
 
 
 def layout(cfg) -> int:

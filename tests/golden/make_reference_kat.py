@@ -116,6 +116,21 @@ KAT = {
         {"src": f"{T}/it/Cross_Device_Sliced_Tensor_System_Test.groovy:236-240 (a fresh [3,4] tensor)", "parent_shape": [3, 4],
          "slice_shape": None, "inline": [3, 4, 4, 1, 4, 1, 0, 0, 1, 1]},
     ],
+    # ---- MatMul / DotProduct ("next" rows: the callers of the contraction kernels) -----------------------------------------
+    "matmul": [
+        {"src": f"{T}/ut/backend/Matrix_Multiplication_Spec.groovy:22-35 (andFill repeats 1,2,3 / 2,-4,-1)", "M": 1, "K": 7, "N": 8,
+         "a": [1, 2, 3, 1, 2, 3, 1], "b": [2, -4, -1] * 18 + [2, -4], "c": [-22, -10, -7, -22, -10, -7, -22, -10]},
+        {"src": f"{T}/ut/backend/Matrix_Multiplication_Spec.groovy:68-75", "M": 2, "K": 2, "N": 2, "a": [4, 3, 2, 1], "b": [-0.5, 1.5, 1, -2], "c": [1, 0, 0, 1]},
+        {"src": f"{T}/ut/backend/Matrix_Multiplication_Spec.groovy:69", "M": 1, "K": 2, "N": 1, "a": [-2, 1], "b": [-1, -1.5], "c": [0.5]},
+        {"src": f"{T}/ut/backend/Matrix_Multiplication_Spec.groovy:70", "M": 2, "K": 1, "N": 2, "a": [-2, 1], "b": [-1, -1.5], "c": [2.0, 3.0, -1.0, -1.5]},
+    ],
+    "dot": [
+        {"src": f"{T}/ut/tensors/Tensor_Dot_Product_Spec.groovy:29-40", "a": [3, 2], "b": [1, -0.5], "value": 2.0},
+        {"src": f"{T}/ut/tensors/Tensor_Dot_Product_Spec.groovy:42-57 (rows of [[1,2],[3,4]])", "a": [1, 2], "b": [3, 4], "value": 11.0},
+        {"src": f"{T}/ut/tensors/Tensor_Dot_Product_Spec.groovy:87-103", "a": [-1, -3, 0, 4, 2], "b": [1, 2, 7, -1, 3], "value": -5.0},
+        {"src": f"{T}/ut/tensors/Tensor_Dot_Product_Spec.groovy:59-85 (forward 4, error 0.5 -> gradient of w = 0.5 * a)", "a": [4, -1, 2], "b": [1, 0, 0],
+         "value": 4.0, "error": 0.5, "grad_b": [2, -0.5, 1]},
+    ],
     # ---- RNG ----------------------------------------------------------------------------------------------------------
     "fill_randomly": {
         "src": "src/test/groovy/ut/backend/core/Randomization_Spec.groovy:58-62",

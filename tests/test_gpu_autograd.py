@@ -214,3 +214,76 @@ def test_matmul_operator_forward_and_backward(device, dt, mkn):
     assert np.abs(c3.numpy() - ref.T).max() <= tol * max(1.0, np.abs(ref).max()) / k
     with pytest.raises(ValueError):
         Function.of("i0 @ i1", False)(a, a)
+
+
+def test_dot_product_golden_vectors_and_autograd(device, kat, oracle):
+    """Tensor_Dot_Product_Spec.groovy: forward values, the gradient of the weight vector for error 0.5, and a long pair of
+    vectors against the oracle's restatement of CPUDot (DOT.unrolled04's four partial sums)."""
+    for v in kat["dot"]:
+        for dt in (np.float32, np.float64):
+            a = Tensor.of(dt, [len(v["a"])], v["a"]).to(device)
+            b = Tensor.of(dt, [len(v["b"])], v["b"]).set_rqs_gradient("grad_b" in v).to(device)
+            r = a.dot(b)
+            assert r.shape == (1,) and r.items.tolist() == [v["value"]]
+            assert oracle.dot(np.asarray(v["a"], dtype=dt), np.asarray(v["b"], dtype=dt)) == v["value"]
+            if "grad_b" in v:
+                r.backward(Tensor.of(dt, [1], [v["error"]]))
+                assert b.gradient.items.tolist() == v["grad_b"]
+    rng = np.random.default_rng(3)
+    n = 300_001
+    x, y = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+    got = float(Tensor.of(np.float32, [n], x).to(device).dot(Tensor.of(np.float32, [n], y).to(device)).item())
+    want = oracle.dot(x, y)
+    assert abs(got - want) <= 1e-5 * float(np.abs(x.astype(np.float64) * y).sum())
+    with pytest.raises(ValueError, match="vectors"):
+        Tensor.of(np.float32, [2, 2], [1, 2, 3, 4]).to(device).dot(Tensor.of(np.float32, [2, 2], [1, 2, 3, 4]).to(device))
+    with pytest.raises(ValueError, match="same length"):
+        Tensor.of(np.float32, [2], [1, 2]).to(device).dot(Tensor.of(np.float32, [3], [1, 2, 3]).to(device))
+
+
+def test_matmul_golden_vectors_and_oracle(device, kat, oracle):
+    """Matrix_Multiplication_Spec.groovy's vectors through `@`, and larger products against the oracle's restatement of
+    CPUMatMul (GEMM.partial_F32_MxN_RM: products added in rising order of the common index) within 1e-5 / 1e-12 of
+    sum|a||b| per element -- through the FMA contraction family and, for the largest, the tensor cores."""
+    for v in kat["matmul"]:
+        for dt in (np.float32, np.float64):
+            a = Tensor.of(dt, [v["M"], v["K"]], v["a"]).to(device)
+            b = Tensor.of(dt, [v["K"], v["N"]], v["b"]).to(device)
+            c = a @ b
+            assert c.shape == (v["M"], v["N"]) and c.items.tolist() == v["c"]
+            ref = oracle.matmul(np.asarray(v["a"], dtype=dt).reshape(v["M"], v["K"]), np.asarray(v["b"], dtype=dt).reshape(v["K"], v["N"]))
+            assert ref.reshape(-1).tolist() == v["c"]
+    rng = np.random.default_rng(8)
+    for dt, tol, (m, k, n) in ((np.float32, 1e-5, (96, 130, 80)), (np.float64, 1e-12, (96, 130, 80)), (np.float32, 1e-5, (384, 512, 320))):
+        a_h, b_h = rng.standard_normal((m, k)).astype(dt), rng.standard_normal((k, n)).astype(dt)
+        c = Tensor.of(dt, [m, k], a_h).to(device) @ Tensor.of(dt, [k, n], b_h).to(device)
+        ref = oracle.matmul(a_h, b_h)
+        mag = np.abs(a_h).astype(np.float64) @ np.abs(b_h).astype(np.float64)
+        assert np.all(np.abs(c.numpy().astype(np.float64) - ref) <= tol * mag)
+    assert device.last_conv_path() == L.NK_CONV_TC
+
+
+def test_min_and_max_return_the_extreme_item_and_route_the_error_to_its_index(device):
+    """operations/other/Min.java / Max.java on CPUReduce's semantics: the first of equal extremes wins; backward puts the
+    error at that index of a zero tensor."""
+    rng = np.random.default_rng(12)
+    for dt in (np.float32, np.float64):
+        for shape in ([7], [65, 3], [1000, 333]):
+            h = rng.standard_normal(int(np.prod(shape))).astype(dt)
+            h[h.size // 3] = h[h.size // 2] = h.max() + 1      # two equal maxima: the earlier one is the answer
+            h[5 % h.size] = h[h.size - 1] = h.min() - 1        # ... and two equal minima
+            t = Tensor.of(dt, shape, h).set_rqs_gradient(True).to(device)
+            mx, mn = t.max(), t.min()
+            assert mx.shape == (1,) and float(mx.item()) == h.max() and float(mn.item()) == h.min()
+            mx.backward(Tensor.of(dt, [1], [2.5]))
+            g = t.gradient.items
+            assert g[int(np.argmax(h))] == 2.5 and np.count_nonzero(g) == 1
+    # a strided slice: the index counts the view's elements, the value is read through the view
+    base = Tensor.of(np.float32, [6, 8], np.arange(48)).to(device)
+    v = base[1:5:2, 2:8:3]            # rows 1, 3; columns 2, 5 -> items 10, 13, 26, 29
+    assert float(v.max().item()) == 29 and float(v.min().item()) == 10
+    import ctypes as C
+    out = Tensor.of(np.float32, [1], [0]).to(device)     # a result buffer of the wrong type is refused
+    k = base.ndconf.as_inline_array()
+    st = L.lib.nk_arg_reduce(device.ctx, 1, L.NK_F32, 2, base._data.buf, k.ctypes.data_as(C.POINTER(C.c_int32)), out._data.buf, 0)
+    assert st == L.NK_ERR_BAD_ARG

@@ -236,3 +236,34 @@ def test_cpu_sum_tiles(oracle):
             nxt[i] = acc
         lvl = nxt
     assert np.float32(s) == lvl[0]
+
+
+def test_matmul_and_dot_restatements_against_the_reference_specs(kat, oracle):
+    """CPUMatMul / CPUDot restated (oracle.matmul, oracle.dot) reproduce the values of Matrix_Multiplication_Spec.groovy
+    and Tensor_Dot_Product_Spec.groovy exactly, in both item types; on random data they agree with a float64 product
+    to the accuracy a rising-order sum in the item type has."""
+    for v in kat["matmul"]:
+        for dt in (np.float32, np.float64):
+            a = np.asarray(v["a"], dtype=dt).reshape(v["M"], v["K"])
+            b = np.asarray(v["b"], dtype=dt).reshape(v["K"], v["N"])
+            assert oracle.matmul(a, b).reshape(-1).tolist() == v["c"]
+    for v in kat["dot"]:
+        for dt in (np.float32, np.float64):
+            assert oracle.dot(np.asarray(v["a"], dtype=dt), np.asarray(v["b"], dtype=dt)) == v["value"]
+    rng = np.random.default_rng(1)
+    a, b = rng.standard_normal((33, 70)).astype(np.float32), rng.standard_normal((70, 21)).astype(np.float32)
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    assert np.abs(oracle.matmul(a, b) - want).max() <= 70 * 6e-8 * np.abs(want).max() * 4
+    # the summation order is the documented one: common index rising, separate multiply and add in the item type
+    acc = np.zeros((33, 21), dtype=np.float32)
+    for c in range(70):
+        acc = acc + (a[:, c:c + 1] * b[c:c + 1, :]).astype(np.float32)
+    assert np.array_equal(oracle.matmul(a, b), acc)
+    x, y = rng.standard_normal(1003).astype(np.float32), rng.standard_normal(1003).astype(np.float32)
+    s = [np.float32(0)] * 4
+    for i in range(0, 1000, 4):
+        for j in range(4):
+            s[j] = np.float32(s[j] + np.float32(x[i + j] * y[i + j]))
+    for i in range(1000, 1003):
+        s[0] = np.float32(s[0] + np.float32(x[i] * y[i]))
+    assert oracle.dot(x, y) == float(np.float32(np.float32(np.float32(s[0] + s[1]) + s[2]) + s[3]))
