@@ -184,97 +184,122 @@ static int nk_deconv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView
     const int Y = rank - 2;
     if (v0.shape[Y] > vk.shape[Y] && vk.shape[Y] <= 7 && v0.shape[Y] > 1 && vi.shape[Y] > 1) { has_y = true; KH = vk.shape[Y]; n_outer = rank - 2; }
     if (n_outer > 3 || 1 + (has_y ? 1 : 0) + n_outer > 5) return NK_OK;
-    TiledPlan p;
-    memset(&p, 0, sizeof(p));
-    p.n_outer = n_outer;
-    p.has_y = has_y ? 1 : 0;
-    p.NP = 1;
-    int64_t NQ = 1;
-    int64_t bK = vk.base;
-    for (int k = 0; k < n_outer; k++) {
-        const int64_t e0 = v0.shape[k], e1 = vk.shape[k], e2 = vi.shape[k];
-        p.oext[k] = e0; p.os[k] = v0.estride[k];
-        if (e0 > e1) {
-            // tau = p - q: flipped window of e1 taps over T2 starting at p - (e1 - 1); e1 == 1 is the batch-like case
-            p.qext[k] = e1; p.pI[k] = vi.estride[k]; p.qI[k] = vi.estride[k];
-            p.pK[k] = 0; p.qK[k] = -vk.estride[k];
-            bK += (e1 - 1) * vk.estride[k];
-            p.padO[k] = int(e1 - 1);
-        } else {
-            // tau = p + q, q over T2: only the consistent case p + q < e1 for every p, q is taken here
-            if (e0 + e2 - 1 > e1) return NK_OK;
-            p.qext[k] = e2; p.pI[k] = 0; p.qI[k] = vi.estride[k];
-            p.pK[k] = vk.estride[k]; p.qK[k] = vk.estride[k];
-            p.padO[k] = 0;
-        }
-        if (p.qext[k] > 65535) return NK_OK;
-        p.NP *= e0;
-        NQ *= p.qext[k];
-    }
-    if (NQ > 4096) return NK_OK;
-    p.NQ = int(NQ);
-    if (vi.shape[X] > 0x3fffffff || v0.shape[X] > 0x3fffffff) return NK_OK;
     const size_t es = nk_dtype_size(dtype);
     const int CW = int(16 / es);
-    p.IW = int(vi.shape[X]); p.OW = int(v0.shape[X]);
-    p.padX = int(KW - 1);
-    p.xoff = (CW - p.padX % CW) % CW;
-    p.sKx = -vk.estride[X];
-    bK += (KW - 1) * vk.estride[X];
-    if (has_y) {
-        p.IH = int(vi.shape[Y]); p.OH = int(v0.shape[Y]);
-        p.padY = int(KH - 1);
-        p.sIy = vi.estride[Y]; p.sOy = v0.estride[Y];
-        p.sKy = -vk.estride[Y];
-        bK += (KH - 1) * vk.estride[Y];
-    } else {
-        p.IH = 1; p.OH = 1;
-    }
-    p.bI = vi.base; p.bK = bK; p.bO = v0.base;
-    p.vec = 0;
-    bool vec_out = p.xoff == 0 && aligned_to(drn->ptr, 16) && (p.bO % CW == 0) && (p.sOy % CW == 0);
-    for (int k = 0; k < n_outer; k++)
-        if (p.os[k] % CW) vec_out = false;
-    p.vec_out = vec_out ? 1 : 0;
-
-    // tensor map over T2
+    TiledPlan p;
     TmaImage img;
-    if (!aligned_to(static_cast<const char*>(s2->ptr) + p.bI * int64_t(es), 16)) return NK_OK;
-    int n = 0;
-    img.base = static_cast<const char*>(s2->ptr) + p.bI * int64_t(es);
-    img.dims[n] = uint64_t(p.IW); img.strides_bytes[n] = es; n++;
-    if (has_y) {
-        if (p.sIy <= 0 || (p.sIy * int64_t(es)) % 16) return NK_OK;
-        img.dims[n] = uint64_t(p.IH); img.strides_bytes[n] = uint64_t(p.sIy) * es; n++;
-    }
-    for (int k = n_outer - 1; k >= 0; k--) {
-        const int64_t ext = vi.shape[k], st = vi.estride[k];
-        img.dims[n] = uint64_t(ext);
-        if (ext == 1) {
-            uint64_t prev = img.strides_bytes[n - 1] * img.dims[n - 1];
-            img.strides_bytes[n] = ((prev + 15) / 16) * 16;
-            if (img.strides_bytes[n] == 0) img.strides_bytes[n] = 16;
-        } else {
-            if (st <= 0 || (st * int64_t(es)) % 16 || uint64_t(st) * es >= (uint64_t(1) << 40)) return NK_OK;
-            img.strides_bytes[n] = uint64_t(st) * es;
+    // Builds the plan. with_wloop: outer dims in which the drain follows T1 while T2 has extent 1 (the output channels of
+    // an image gradient: they select weights and a drain plane, nothing else) are taken out of the tile index and become
+    // the weight loop of a chunk -- one tile load then feeds all of them.
+    auto build = [&](bool with_wloop) -> bool {
+        memset(&p, 0, sizeof(p));
+        p.has_y = has_y ? 1 : 0;
+        p.NP = 1;
+        int64_t NQ = 1;
+        int64_t bK = vk.base;
+        int no = 0;
+        int kept[NK_MAX_RANK];
+        for (int k = 0; k < n_outer; k++) {
+            const int64_t e0 = v0.shape[k], e1 = vk.shape[k], e2 = vi.shape[k];
+            if (with_wloop && !(e0 > e1) && e2 == 1 && e0 > 1) {
+                if (e0 + e2 - 1 > e1) return false;
+                p.wext[p.n_w] = e0; p.wos[p.n_w] = v0.estride[k]; p.wK[p.n_w] = vk.estride[k];
+                p.n_w++;
+                continue;
+            }
+            kept[no] = k;
+            p.oext[no] = e0; p.os[no] = v0.estride[k];
+            if (e0 > e1) {
+                // tau = p - q: flipped window of e1 taps over T2 starting at p - (e1 - 1); e1 == 1 is the batch-like case
+                p.qext[no] = e1; p.pI[no] = vi.estride[k]; p.qI[no] = vi.estride[k];
+                p.pK[no] = 0; p.qK[no] = -vk.estride[k];
+                bK += (e1 - 1) * vk.estride[k];
+                p.padO[no] = int(e1 - 1);
+            } else {
+                // tau = p + q, q over T2: only the consistent case p + q < e1 for every p, q is taken here
+                if (e0 + e2 - 1 > e1) return false;
+                p.qext[no] = e2; p.pI[no] = 0; p.qI[no] = vi.estride[k];
+                p.pK[no] = vk.estride[k]; p.qK[no] = vk.estride[k];
+                p.padO[no] = 0;
+            }
+            if (p.qext[no] > 65535) return false;
+            p.NP *= e0;
+            NQ *= p.qext[no];
+            no++;
         }
-        n++;
-    }
-    if (n < 2) return NK_OK;
-    img.nd = n;
-    p.tma_nd = n;
+        p.n_outer = no;
+        if (NQ > 4096) return false;
+        p.NQ = int(NQ);
+        p.wloop = (with_wloop && p.n_w > 0 && NQ == 1) ? 1 : 0;
+        if (with_wloop && !p.wloop) return false;
+        if (vi.shape[X] > 0x3fffffff || v0.shape[X] > 0x3fffffff) return false;
+        p.IW = int(vi.shape[X]); p.OW = int(v0.shape[X]);
+        p.padX = int(KW - 1);
+        p.xoff = (CW - p.padX % CW) % CW;
+        p.sKx = -vk.estride[X];
+        bK += (KW - 1) * vk.estride[X];
+        if (has_y) {
+            p.IH = int(vi.shape[Y]); p.OH = int(v0.shape[Y]);
+            p.padY = int(KH - 1);
+            p.sIy = vi.estride[Y]; p.sOy = v0.estride[Y];
+            p.sKy = -vk.estride[Y];
+            bK += (KH - 1) * vk.estride[Y];
+        } else {
+            p.IH = 1; p.OH = 1;
+        }
+        p.bI = vi.base; p.bK = bK; p.bO = v0.base;
+        p.vec = 0;
+        bool vec_out = p.xoff == 0 && aligned_to(drn->ptr, 16) && (p.bO % CW == 0) && (p.sOy % CW == 0);
+        for (int k = 0; k < no; k++)
+            if (p.os[k] % CW) vec_out = false;
+        for (int k = 0; k < p.n_w; k++)
+            if (p.wos[k] % CW) vec_out = false;
+        p.vec_out = vec_out ? 1 : 0;
 
-    int st;
-    const bool f32 = dtype == NK_F32;
-    if (f32) st = nk_tiled_dispatch_f32_tma4(ctx, int(KH), int(KW), (float*)drn->ptr, (const float*)s2->ptr, (const float*)s1->ptr, p, &img);
-    else st = nk_tiled_dispatch_f64_tma4(ctx, int(KH), int(KW), (double*)drn->ptr, (const double*)s2->ptr, (const double*)s1->ptr, p, &img);
+        // tensor map over T2 (the dims of the tile index only)
+        if (!aligned_to(static_cast<const char*>(s2->ptr) + p.bI * int64_t(es), 16)) return false;
+        int n = 0;
+        img.base = static_cast<const char*>(s2->ptr) + p.bI * int64_t(es);
+        img.dims[n] = uint64_t(p.IW); img.strides_bytes[n] = es; n++;
+        if (has_y) {
+            if (p.sIy <= 0 || (p.sIy * int64_t(es)) % 16) return false;
+            img.dims[n] = uint64_t(p.IH); img.strides_bytes[n] = uint64_t(p.sIy) * es; n++;
+        }
+        for (int j = no - 1; j >= 0; j--) {
+            const int k = kept[j];
+            const int64_t ext = vi.shape[k], st = vi.estride[k];
+            img.dims[n] = uint64_t(ext);
+            if (ext == 1) {
+                uint64_t prev = img.strides_bytes[n - 1] * img.dims[n - 1];
+                img.strides_bytes[n] = ((prev + 15) / 16) * 16;
+                if (img.strides_bytes[n] == 0) img.strides_bytes[n] = 16;
+            } else {
+                if (st <= 0 || (st * int64_t(es)) % 16 || uint64_t(st) * es >= (uint64_t(1) << 40)) return false;
+                img.strides_bytes[n] = uint64_t(st) * es;
+            }
+            n++;
+        }
+        if (n < 2 || n > 5) return false;
+        img.nd = n;
+        p.tma_nd = n;
+        return true;
+    };
+    auto dispatch = [&]() -> int {
+        if (dtype == NK_F32) return nk_tiled_dispatch_f32_tma4(ctx, int(KH), int(KW), (float*)drn->ptr, (const float*)s2->ptr, (const float*)s1->ptr, p, &img);
+        return nk_tiled_dispatch_f64_tma4(ctx, int(KH), int(KW), (double*)drn->ptr, (const double*)s2->ptr, (const double*)s1->ptr, p, &img);
+    };
+    int st = -1;
+    if (has_y && build(true)) st = dispatch();          // the weight loop first; -1 = it does not apply (sets too large, no persistent walk)
+    if (st == -1) {
+        if (!build(false)) return NK_OK;
+        st = dispatch();
+    }
     if (st == -1) return NK_OK;
     if (st != NK_OK) return st;
     ctx->last_conv_path = NK_CONV_TMA;
     *handled = true;
     return NK_OK;
 }
-
 // Returns NK_OK with *handled = true when the call was launched on a tiled family, NK_OK with *handled = false
 // when the views do not qualify (the caller then uses the generic family).
 int nk_conv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_buf* s1, const NkView& v1,

@@ -61,6 +61,12 @@ struct TiledPlan {
     int64_t tiles_total;
     int waves;            // whole waves: in wave w CTA b takes tile w * gridDim.x + b
     int wsets;        // persistent walk over tiles whose weights differ: weight sets staged at once (1 = same weights everywhere)
+    // Weight loop (persistent walks of one-channel chunks whose outer output dims that move the kernel -- the output
+    // channels of an image gradient -- touch neither the image nor the reduction): those dims are not part of the tile
+    // index at all. A chunk's image tile is loaded once and every weight set is run over it in turn, each result going to
+    // its own plane of the drain: wext / wos / wK are the extents, drain strides and kernel strides of those dims.
+    int wloop, n_w;
+    int64_t wext[NK_MAX_RANK], wos[NK_MAX_RANK], wK[NK_MAX_RANK];
     int cluster;   // channel-split CTAs of a tile form one thread-block cluster and add their tiles through shared memory
     int vec;       // LDGSTS: 16-byte global->shared copies are legal for every chunk
     int vec_out;   // 16-byte stores to the drain are legal
@@ -115,8 +121,10 @@ struct TiledCfg {
     static constexpr int CPR = SW / CW;                       // LDGSTS chunks per row
     static constexpr int NIT = (SH * CPR + 255) / 256;        // LDGSTS chunks per thread
     static size_t smem_bytes(int NQ, int wsets = 1) {
-        // [stages | mbarriers + abort word (128 B) | tile-info ring (256 B) | weights | channel table (32 B per channel)]
-        return size_t(STAGES) * STAGE_BYTES + 384 + size_t(wsets) * NQ * WPAD * sizeof(T) + 16 + size_t(NQ) * 4 * sizeof(int64_t);
+        // [stages | mbarriers + abort word (128 B) | tile-info ring (256 B) | weights | channel table (32 B per channel) |
+        //  drain offset per weight set (8 B each)]
+        return size_t(STAGES) * STAGE_BYTES + 384 + size_t(wsets) * NQ * WPAD * sizeof(T) + 16 + size_t(NQ) * 4 * sizeof(int64_t) +
+               size_t(wsets) * sizeof(int64_t);
     }
 };
 
@@ -144,6 +152,8 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     // (everything but x) ready for the producer thread -- it runs on the same issue port as two compute warps per
     // CTA, and every instruction it spends per tile is taken from them
     int64_t* ctab = reinterpret_cast<int64_t*>((reinterpret_cast<uintptr_t>(wsm + size_t(p.wsets) * p.NQ * WPAD) + 15) & ~uintptr_t(15));
+
+    int64_t* wofs = ctab + size_t(p.NQ) * 4;   // weight loop: where weight set ws stores, relative to the chunk's drain base
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -315,7 +325,11 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         const int ws = e / per_set, r = e - ws * per_set;
         const int c = c_begin + r / WPAD, t = r % WPAD;
         int64_t kb = baseK;   // one set: the weights of this CTA's (only, or every) tile
-        if (p.wsets > 1) {    // several: set ws belongs to the outer output indices that tile_set() folds into ws
+        if (p.wloop) {        // the sets of the weight loop: set ws belongs to index ws of the dims taken out of the tile index
+            kb = p.bK;
+            int rem = ws;
+            for (int k = p.n_w - 1; k >= 0; k--) { kb += int64_t(rem % int(p.wext[k])) * p.wK[k]; rem /= int(p.wext[k]); }
+        } else if (p.wsets > 1) {    // several: set ws belongs to the outer output indices that tile_set() folds into ws
             kb = p.bK;
             int rem = ws;
             for (int k = p.n_outer - 1; k >= 0; k--)
@@ -324,6 +338,15 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         T v = 0;
         if (t < KH * KW) v = K[kb + ctab[c * 4 + 1] + (t / KW) * p.sKy + (t % KW) * p.sKx];
         wsm[(size_t(ws) * p.NQ + c) * WPAD + t] = v;
+    }
+
+    if (p.wloop) {
+        for (int ws = tid; ws < p.wsets; ws += blockDim.x) {
+            int rem = ws;
+            int64_t o = 0;
+            for (int k = p.n_w - 1; k >= 0; k--) { o += int64_t(rem % int(p.wext[k])) * p.wos[k]; rem /= int(p.wext[k]); }
+            wofs[ws] = o;
+        }
     }
 
     // ---- loaders ------------------------------------------------------------------------------------------------
@@ -410,7 +433,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     };
     // Stores this thread's results of the tile / chunk the thread currently stands on (rh_cur rows per warp, rows below
     // y_end only): into the drain, or -- two-pass channel split -- into this part's plane of the scratch buffer.
-    auto store_tile = [&]() {
+    auto store_tile = [&](int64_t plane_off = 0) {
         const int ox = x0 + lane * CW;
 #pragma unroll
         for (int i = 0; i < RH; i++) {
@@ -419,7 +442,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             T* dst;
             bool vec_ok;
             if (p.splits == 1) {
-                dst = out + baseO + int64_t(oy) * p.sOy + ox;
+                dst = out + baseO + plane_off + int64_t(oy) * p.sOy + ox;
                 vec_ok = p.vec_out != 0;
             } else {
                 dst = partial + ((int64_t(split) * p.NP + pflat) * p.OH + oy) * int64_t(p.OW) + ox;
@@ -608,6 +631,27 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                 // the channel loop of one chunk, specialised on the rows per warp: the switch sits outside the loop, so the
                 // loop body is straight-line code the compiler can schedule across iterations, as for a fixed tile height
                 auto run_chunk = [&](auto rows_tag) {
+                    if (p.wloop) {
+                        // one image tile (a single channel), every weight set in turn: multiply-adds, store, clear. The
+                        // stage goes back to the producer only after the last set.
+                        const int stage = g % STAGES;
+                        if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; return; }
+                        for (int ws = 0; ws < p.wsets; ws++) {
+                            wset = ws;
+                            consume(rows_tag, stage, c_begin);
+                            if (ws + 1 < p.wsets) {
+                                store_tile(wofs[ws]);
+#pragma unroll
+                                for (int i = 0; i < RH; i++)
+#pragma unroll
+                                    for (int x = 0; x < CW; x++) acc[i][x] = T(0);
+                            }
+                        }
+                        __syncwarp();
+                        if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
+                        g++;
+                        return;
+                    }
                     for (int c = c_begin; c < c_end; c++, g++) {
                         const int stage = g % STAGES;
                         if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; break; }
@@ -629,7 +673,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                     }
                 }
                 if (!ok || !p.persist) break;   // one tile per CTA: its epilogue follows below
-                store_tile();
+                store_tile(p.wloop ? wofs[p.wsets - 1] : 0);
 #pragma unroll
                 for (int i = 0; i < RH; i++)
 #pragma unroll
@@ -760,6 +804,8 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     int64_t wsets = 1;
     for (int k = 0; k < p.n_outer; k++)
         if (p.pK[k] != 0) wsets *= p.oext[k];
+    if (p.wloop)   // those dims were taken out of the tile index by the caller: every chunk runs all of their weight sets
+        for (int k = 0; k < p.n_w; k++) wsets *= p.wext[k];
     const bool sets_fit = wsets == 1 || (TMA && wsets * int64_t(p.NQ) * C::WPAD * int64_t(sizeof(T)) <= 16384);
     size_t smem = 0;
     int64_t slots = 0;
@@ -792,6 +838,7 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     // The balanced persistent walk: a tensor map with a row dim, no channel split, and the same weights for every
     // strip or all weight sets resident at once.
     auto balanced = [&]() { return TMA && p.has_y && splits == 1 && (wsets == 1 || p.wsets > 1); };
+    if (p.wloop && (cst != 0 || !sets_fit || !balanced())) return -1;   // the caller plans the call again without the weight loop
     if (cst == 0 && p.wsets > 1 && !balanced()) {   // no persistent walk after all: one set per CTA
         p.wsets = 1;
         cst = configure(1);
@@ -819,7 +866,7 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
         if (p.persist) {
             // One resident wave of CTAs: whole waves of tiles first, then the rest in 8-row groups, at least two groups
             // (16 rows) per CTA (each chunk re-reads KH - 1 halo rows and pays a fixed set-up).
-            ring = p.NQ < 8;   // short chunks: decoding would cost as much as the chunk's arithmetic
+            ring = p.NQ < 8 && !p.wloop;   // short chunks: decoding would cost as much as the chunk's arithmetic
             grid = slots;
             if (tiles < grid) {
                 grid = tiles * RH / 2;
