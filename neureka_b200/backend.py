@@ -290,11 +290,14 @@ class CudaBackend:
 
     @staticmethod
     def find(key: str) -> Optional[CudaDevice]:
-        """BackendExtension.find (BackendExtension.java:40-48): 'cuda', 'gpu', 'nvidia', 'first' or an ordinal."""
+        """BackendExtension.find (BackendExtension.java:40-48): 'cuda', 'gpu', 'nvidia', 'first', an ordinal, or
+        'cuda:<ordinal>' / 'gpu:<ordinal>' for one of several GPUs in this process."""
         key = key.strip().lower()
         n = CudaDevice.count()
         if n == 0:
             return None
+        if key.startswith(("cuda:", "gpu:")):
+            key = key.split(":", 1)[1]
         if key.isdigit():
             return CudaDevice.get(int(key)) if int(key) < n else None
         if key in ("cuda", "gpu", "nvidia", "first", "any", "b200"):

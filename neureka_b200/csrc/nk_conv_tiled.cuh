@@ -25,12 +25,14 @@
 //     of the tensor (neighbouring column blocks of the same rows: their loads and stores form long contiguous runs in
 //     DRAM). The remaining tiles -- less than one per CTA -- are not dealt whole: each is cut into groups of 8 rows, and
 //     the groups of all remaining tiles, laid end to end in tile order, are dealt to the CTAs in equal contiguous ranges;
-//     a range is walked in chunks that stop at tile ends, a chunk of n groups giving every warp n rows (the
-//     multiply-add loop exists once per rows-per-warp value 1..RH) and loading through the tensor map whose box is
-//     8 n + KH - 1 rows high. So the last, partial wave costs its share of a tile instead of a whole one. The producer
-//     warp keeps loading across chunk boundaries; tiles with their own weights select one of the weight sets staged
-//     at once; for one-channel chunks (RING) the compute warps take chunk positions from a ring the producer fills
-//     instead of decoding them;
+//     a range is cut into chunks of 1, 2, 4 or 8 groups that stop at tile ends, a chunk of n groups giving every warp n rows
+//     (the multiply-add loop exists once per such n) and loading through the tensor map whose box is 8 n + KH - 1 rows
+//     high. So the last, partial wave costs its share of a tile instead of a whole one. A CTA's chunks of that wave (at
+//     most RH) are written into a table in shared memory by the producer thread during the prologue; the walk itself
+//     carries no more state through the multiply-add loop than a chunk counter. The producer warp keeps loading across
+//     chunk boundaries; tiles with their own weights select one of the weight sets staged at once; for one-channel
+//     chunks the compute warps take tile positions from a ring the producer fills instead of decoding them (RING), or
+//     run every weight set over the one image tile they hold (WLOOP, image gradients);
 //   * channel split -- fewer tiles than slots and many channels: up to 8 parts of a tile form a thread-block cluster
 //     and add their partial tiles through distributed shared memory; more parts go through scratch and a finish
 //     kernel. Both add in part order, so the result is deterministic and the same on either path.
@@ -120,34 +122,49 @@ struct TiledCfg {
     static constexpr bool WREG = KH * KW * int(sizeof(T)) <= 400;   // weights of one channel live in registers
     static constexpr int CPR = SW / CW;                       // LDGSTS chunks per row
     static constexpr int NIT = (SH * CPR + 255) / 256;        // LDGSTS chunks per thread
+    static constexpr int MAX_TAIL = 8;                        // chunks of the last, partial wave per CTA (at most RH groups, one each)
+    static constexpr int FIXED_BYTES = 384 + MAX_TAIL * 48;
     static size_t smem_bytes(int NQ, int wsets = 1) {
-        // [stages | mbarriers + abort word (128 B) | tile-info ring (256 B) | weights | channel table (32 B per channel) |
-        //  drain offset per weight set (8 B each)]
-        return size_t(STAGES) * STAGE_BYTES + 384 + size_t(wsets) * NQ * WPAD * sizeof(T) + 16 + size_t(NQ) * 4 * sizeof(int64_t) +
+        // [stages | mbarriers + abort word + tail count (128 B) | tile-info ring (256 B) | tail table (48 B per chunk) |
+        //  weights | channel table (32 B per channel) | drain offset per weight set (8 B each)]
+        return size_t(STAGES) * STAGE_BYTES + FIXED_BYTES + size_t(wsets) * NQ * WPAD * sizeof(T) + 16 + size_t(NQ) * 4 * sizeof(int64_t) +
                size_t(wsets) * sizeof(int64_t);
     }
 };
 
-// The tensor maps of a launch: entry r - 1 has a box of 8 * r + KH - 1 rows (r = rows per warp of a chunk).
+// The tensor maps of a launch: entry r - 1 has a box of 8 * r + KH - 1 rows (r = rows per warp of a chunk: 1, 2, 4 or 8).
 struct TmapSet { CUtensorMap m[8]; };
 template <int N> struct NkRows { static constexpr int value = N; };
+// Variants of the persistent TMA kernel: chunks decoded by the compute warps / taken from the producer's ring / weight loop
+#define NK_TILED_PLAIN 0
+#define NK_TILED_RING 1
+#define NK_TILED_WLOOP 2
 
-// RING (persistent walk over short chunks only): the compute warps take each chunk's position from a ring the producer
-// thread fills instead of decoding it themselves. A compile-time switch: with the ring code merely present
-// the long-chunk launches measured 3 % slower (register allocation of the main loop), so they get a kernel without it.
-template <class T, int KH, int KW, int RH, bool TMA, bool RING = false>
+// MODE: RING (persistent walk over short chunks only) -- the compute warps take each chunk's position from a ring the
+// producer thread fills instead of decoding it themselves; WLOOP -- every chunk runs all weight sets over its one image
+// tile. Compile-time switches: with the ring code merely present the long-chunk launches measured 3 % slower, and with the
+// weight loop present the kernel took 168 registers instead of 93 (one CTA per SM instead of two).
+// Two CTAs per SM are what the pipelined kernel is tuned for (18 warps share the issue ports; one CTA alone leaves a third
+// of them idle): the state a thread carries through the multiply-add loop is kept small enough for that (the last,
+// partial wave comes from a table in shared memory, not from arithmetic in registers).
+template <class T, int KH, int KW, int RH, bool TMA, int MODE = NK_TILED_PLAIN>
 __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __restrict__ out, T* __restrict__ partial,
                                                             const T* __restrict__ I, const T* __restrict__ K,
                                                             const TiledPlan p, const __grid_constant__ TmapSet tmaps) {
     using C = TiledCfg<T, KH, KW, RH>;
     constexpr int CW = C::CW, TW = C::TW, TH = C::TH, SW = C::SW, SH = C::SH, STAGES = C::STAGES, NS = C::NS, WPAD = C::WPAD;
+    constexpr bool RING = MODE == NK_TILED_RING, WLOOP = MODE == NK_TILED_WLOOP;
     extern __shared__ __align__(128) unsigned char nk_smem[];
     unsigned char* stage_base = nk_smem;
     uint64_t* mbar = reinterpret_cast<uint64_t*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES);
-    // persistent walk: the producer thread publishes where each chunk lives (x0, y0, weight set, rows, drain base), 32 bytes
-    // per chunk in a ring of STAGES + 1 entries; the compute warps pick an entry up after the chunk's first load landed
+    // Where a chunk lives, two int4: (x0, y0, weight set, first row below the chunk) and (drain base low, high, rows per
+    // warp, 0). Persistent walk, RING: the producer thread publishes every chunk in a ring of STAGES + 1 such entries and
+    // the compute warps pick an entry up after the chunk's first load landed.
     int4* tinfo = reinterpret_cast<int4*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES + 128);
-    T* wsm = reinterpret_cast<T*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES + 384);
+    // Persistent walk: the chunks of the last, partial wave of this CTA, written once in the prologue: entries of three
+    // int4, the two above and the chunk's tensor-map coordinates 1..4 without their channel part.
+    int4* tail_tab = reinterpret_cast<int4*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES + 384);
+    T* wsm = reinterpret_cast<T*>(nk_smem + size_t(STAGES) * C::STAGE_BYTES + C::FIXED_BYTES);
     // channel table, 32 bytes per channel: image offset, kernel offset, then the tile's tensor-map coordinates 1..4
     // (everything but x) ready for the producer thread -- it runs on the same issue port as two compute warps per
     // CTA, and every instruction it spends per tile is taken from them
@@ -158,18 +175,21 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     // ---- which tile / outer coordinate / channel range ----------------------------------------------------------
-    // One tile per CTA (the parts of a channel split are neighbours: one cluster), or -- persistent -- a walk over
-    // the CTA's range of strip rows with the load pipeline running on across chunk boundaries.
+    // One tile per CTA (the parts of a channel split are neighbours: one cluster), or -- persistent -- whole tiles
+    // blockIdx.x, blockIdx.x + gridDim.x, ... for p.waves steps and then the CTA's chunks of the last, partial wave, with the
+    // load pipeline running on across chunk boundaries.
     const int split = p.persist ? 0 : int(blockIdx.x % unsigned(p.splits));
+    const int64_t tile_first = p.persist ? (p.waves > 0 ? int64_t(blockIdx.x) : 0) : int64_t(blockIdx.x / unsigned(p.splits));
+    const int64_t tile_step = gridDim.x;
     int64_t baseI, baseK, baseO;
     int pidx[NK_TILED_MAX_OUTER];
     int x0, y0;
     int rh_cur = RH;        // rows per warp of the chunk / tile this thread stands on
     int y_end = p.OH;       // first row below it
     int wset = 0;   // which of the staged weight sets the current tile uses (outer output dims that move the kernel)
-    // Places the thread on a tile (divisions: once per thread, and once per chunk of long chunks; the producer thread of a
-    // persistent CTA steps on digit by digit instead, see below). Returns the tile's first row.
-    auto tile_set = [&](int64_t tile) -> int {
+    // Takes a tile index apart with divisions (once per thread, and once per tile of long tiles; the producer thread of a
+    // persistent CTA steps on digit by digit instead, see below).
+    auto tile_set = [&](int64_t tile) {
         const int tx = int(tile % p.tilesX); tile /= p.tilesX;
         const int ty = int(tile % p.tilesY); tile /= p.tilesY;
         baseI = p.bI; baseK = p.bK; baseO = p.bO;
@@ -184,70 +204,16 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         }
         wset = p.wsets > 1 ? ws : 0;
         x0 = tx * TW - p.xoff;
-        return ty * TH;
+        y0 = ty * TH;
     };
-    // Persistent walk of CTA b: steps 0 .. waves-1 are the whole tiles step * G + b; after them the CTA's range
-    // [q, q_hi) of 8-row groups of the remaining tiles (RH groups per tile), cut into chunks at tile ends.
-    const int64_t G = gridDim.x;
-    const int64_t tail_first = int64_t(p.waves) * G;                                    // first tile that is dealt in groups
-    const int64_t tail_groups = p.persist ? (p.tiles_total - tail_first) * RH : 0;
-    const int64_t q_lo = (int64_t(blockIdx.x) * tail_groups) / G, q_hi = (int64_t(blockIdx.x + 1) * tail_groups) / G;
-    // The chunk after `step` whole tiles and `q` groups: false when the walk is over. Sets the tile, y0, rh_cur, y_end
-    // and advances step / q. Chunks that lie entirely below the image's last row are skipped.
-    int step = 0;
-    int64_t q = q_lo;
-    int64_t cur_tile = 0;
-    auto next_chunk = [&]() -> bool {
-        while (true) {
-            if (step < p.waves) {
-                cur_tile = int64_t(step) * G + blockIdx.x;
-                const int ty0 = tile_set(cur_tile);
-                step++;
-                y0 = ty0;
-                int h = p.OH - y0;
-                if (h > TH) h = TH;
-                rh_cur = (h + 7) >> 3;
-                y_end = y0 + h;
-                return true;
-            }
-            if (q >= q_hi) return false;
-            const int64_t t = q / RH;
-            const int g0 = int(q - t * RH);
-            int n = RH - g0;
-            if (int64_t(n) > q_hi - q) n = int(q_hi - q);
-            q += n;
-            cur_tile = tail_first + t;
-            const int ty0 = tile_set(cur_tile);
-            y0 = ty0 + g0 * 8;
-            int h = p.OH - y0;
-            if (h <= 0) continue;
-            if (h > n * 8) h = n * 8;
-            rh_cur = (h + 7) >> 3;
-            y_end = y0 + h;
-            return true;
-        }
+    // puts the thread on a chunk described by two int4 (ring entry or the head of a table entry)
+    auto place = [&](const int4 a, const int4 b) {
+        x0 = a.x; y0 = a.y; wset = a.z; y_end = a.w;
+        baseO = (int64_t(b.y) << 32) | int64_t(unsigned(b.x));
+        rh_cur = b.z;
     };
-    int64_t pflat = 0;      // flat outer index: used by the two-pass split path (one tile per CTA)
-    bool have_work = true;
-    int n_chunks = 0;       // persistent: chunks of this CTA's walk (what the ring-fed compute warps count down)
-    if (p.persist) {
-        n_chunks = p.waves;
-        for (int64_t qq = q_lo; qq < q_hi;) {   // at most a few tiles: the range is less than one tile's worth per CTA, plus its cuts
-            const int64_t t = qq / RH;
-            const int g0 = int(qq - t * RH);
-            int n = RH - g0;
-            if (int64_t(n) > q_hi - qq) n = int(q_hi - qq);
-            qq += n;
-            const int ty = int(((tail_first + t) / p.tilesX) % p.tilesY);
-            if (ty * TH + g0 * 8 < p.OH) n_chunks++;
-        }
-        have_work = next_chunk();
-        if (!have_work) { tile_set(0); y0 = 0; rh_cur = 1; y_end = 0; }
-    } else {
-        const int64_t tile = int64_t(blockIdx.x / unsigned(p.splits));
-        pflat = tile / (int64_t(p.tilesX) * p.tilesY);
-        y0 = tile_set(tile);
-    }
+    tile_set(tile_first);
+    const int64_t pflat = tile_first / (int64_t(p.tilesX) * p.tilesY);   // used by the two-pass split path (one tile per CTA)
     const int cper = (p.NQ + p.splits - 1) / p.splits;
     const int c_begin = split * cper;
     const int c_end = (c_begin + cper < p.NQ) ? c_begin + cper : p.NQ;
@@ -257,6 +223,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     uint64_t* full_bar = mbar;
     uint64_t* empty_bar = mbar + STAGES;
     volatile int* abort_word = reinterpret_cast<volatile int*>(mbar + 2 * STAGES);
+    int* n_tail_word = reinterpret_cast<int*>(mbar + 2 * STAGES) + 1;   // entries of tail_tab
     const int n_it = c_end - c_begin;
     int issued = 0;                            // tiles requested so far (producer thread)
     // Tensor-map coordinates 1..4 of a tile load (coordinate 0 is x0 - padX): a part that depends on the channel only
@@ -283,10 +250,15 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         }
         return make_int4(b[0], b[1], b[2], b[3]);
     };
-    auto tma_fire = [&](int stage, int rh, int c1, int c2, int c3, int c4) {
+    // Bytes and tensor map of a tile load for a chunk of rh rows per warp: worked out once per chunk, not per load (every
+    // instruction of the producer thread is taken from the compute warps it shares an issue port with).
+    auto chunk_bytes = [&](int rh) -> unsigned {
         // without a row dim in the map the box is a single row; the other tile rows are never stored from
-        nk_mbar_expect_tx(&full_bar[stage], unsigned((p.has_y ? 8 * rh + KH - 1 : 1) * SW * sizeof(T)));
-        nk_tma_load5(stage_base + size_t(stage) * C::STAGE_BYTES, &tmaps.m[rh - 1], &full_bar[stage], p.tma_nd, x0 - p.padX, c1, c2, c3, c4);
+        return unsigned((p.has_y ? 8 * rh + KH - 1 : 1) * SW * sizeof(T));
+    };
+    auto tma_fire = [&](int stage, unsigned bytes, const CUtensorMap* map, int c1, int c2, int c3, int c4) {
+        nk_mbar_expect_tx(&full_bar[stage], bytes);
+        nk_tma_load5(stage_base + size_t(stage) * C::STAGE_BYTES, map, &full_bar[stage], p.tma_nd, x0 - p.padX, c1, c2, c3, c4);
         issued++;
     };
     if (TMA && tid == 256) {
@@ -296,11 +268,59 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         *abort_word = 0;
         nk_fence_barrier_init();
         nk_fence_proxy_async();
-        const int4 tb = tile_coords();
-        for (int it = 0; it < STAGES && it < n_it && have_work; it++) {
-            int cc[4];
-            chan_coords(c_begin + it, cc);
-            tma_fire(it, rh_cur, cc[0] + tb.x, cc[1] + tb.y, cc[2] + tb.z, cc[3] + tb.w);
+        auto first_loads = [&]() {
+            const int4 tb = tile_coords();
+            for (int it = 0; it < STAGES && it < n_it; it++) {
+                int cc[4];
+                chan_coords(c_begin + it, cc);
+                tma_fire(it, chunk_bytes(rh_cur), &tmaps.m[rh_cur - 1], cc[0] + tb.x, cc[1] + tb.y, cc[2] + tb.z, cc[3] + tb.w);
+            }
+        };
+        if (!p.persist) {
+            first_loads();
+        } else {
+            if (p.waves > 0) first_loads();
+            // The last, partial wave: the tiles after the whole waves are cut into groups of 8 rows (RH per tile) and the
+            // groups, laid end to end in tile order, dealt to the CTAs in equal contiguous ranges -- less than one tile's
+            // worth each. A range is cut into chunks of 1, 2, 4 or 8 groups (the rows per warp the multiply-add loop
+            // exists for) that stop at tile ends; chunks entirely below the image's last row are dropped.
+            const int64_t G = gridDim.x;
+            const int64_t tail_first = int64_t(p.waves) * G;
+            const int64_t tail_groups = (p.tiles_total - tail_first) * RH;
+            int64_t q = (int64_t(blockIdx.x) * tail_groups) / G;
+            const int64_t q_hi = (int64_t(blockIdx.x + 1) * tail_groups) / G;
+            int nt = 0;
+            while (q < q_hi && nt < C::MAX_TAIL) {
+                const int64_t t = q / RH;
+                const int g0 = int(q - t * RH);
+                int n = RH - g0;
+                if (int64_t(n) > q_hi - q) n = int(q_hi - q);
+                n = n >= 8 ? 8 : n >= 4 ? 4 : n >= 2 ? 2 : 1;
+                q += n;
+                tile_set(tail_first + t);
+                y0 += g0 * 8;
+                int h = p.OH - y0;
+                if (h <= 0) continue;
+                if (h > n * 8) h = n * 8;
+                const int r = (h + 7) >> 3;
+                int4* e = tail_tab + 3 * nt;
+                e[0] = make_int4(x0, y0, wset, y0 + h);
+                e[1] = make_int4(int(unsigned(baseO & 0xffffffffLL)), int(baseO >> 32), r > 4 ? 8 : r > 2 ? 4 : r, 0);
+                e[2] = tile_coords();
+                nt++;
+            }
+            *n_tail_word = nt;
+            if (p.waves > 0) {
+                tile_set(tile_first);   // back on the first whole tile
+            } else if (nt > 0) {
+                place(tail_tab[0], tail_tab[1]);
+                const int4 tb = tail_tab[2];
+                for (int it = 0; it < STAGES && it < n_it; it++) {
+                    int cc[4];
+                    chan_coords(c_begin + it, cc);
+                    tma_fire(it, chunk_bytes(rh_cur), &tmaps.m[rh_cur - 1], cc[0] + tb.x, cc[1] + tb.y, cc[2] + tb.z, cc[3] + tb.w);
+                }
+            }
         }
     }
 
@@ -471,42 +491,26 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             }
             return r > 0;
         };
+        // chunks of this CTA's walk: the whole tiles, then the entries of the table
+        const int n_chunks = p.persist ? p.waves + *n_tail_word : 1;
         if (warp == 8) {
-            if (lane == 0 && have_work) {
+            if (lane == 0 && n_chunks > 0) {
                 // `issued` counts tile loads over the CTA's whole life: load g uses stage g % STAGES in round g / STAGES.
-                // A tile index is a mixed-radix number (tx | ty | outer output indices, last outer dim fastest). The walk
-                // adds gridDim.x to it per whole wave and then 1 per tile of the CTA's range of row groups, digit by
-                // digit with carry -- a few adds and compares per chunk, no division. Everything the step needs sits in
-                // registers under compile-time indices (j counts the outer dims from the last one): the producer's time
-                // per chunk bounds short chunks.
+                // A tile index is a mixed-radix number (tx | ty | outer output indices, last outer dim fastest); a whole
+                // wave adds gridDim.x to it, digit by digit with carry -- a few adds and compares per tile, no division.
+                // Everything the step needs sits in registers under compile-time indices (j counts the outer dims from the
+                // last one): the producer's time per tile bounds short tiles. Chunks of the last, partial wave come from
+                // the table.
                 constexpr int NO = NK_TILED_MAX_OUTER, NDIG = 2 + NO;
                 int dg[NDIG], sg[NDIG], rx[NDIG], wmj[NO];
                 long long osj[NO];
                 bool foli[NO];
-                auto digits_of = [&](int64_t t) {
-#pragma unroll
-                    for (int i = 0; i < NDIG; i++) { dg[i] = int(t % rx[i]); t /= rx[i]; }
-                };
-                // puts the producer on the tile its digits name (drain base, weight set, x0, tensor-map coordinates 2..4)
-                int4 tb = tile_coords();
-                auto apply_digits = [&]() {
-                    baseO = p.bO;
-                    int ws = 0, P[NO];
-#pragma unroll
-                    for (int j = 0; j < NO; j++) {
-                        baseO += dg[2 + j] * osj[j];
-                        P[j] = foli[j] ? dg[2 + j] : 0;
-                        ws += dg[2 + j] * wmj[j];
-                    }
-                    wset = p.wsets > 1 ? ws : 0;
-                    x0 = dg[0] * TW - p.xoff;
-                    tb = make_int4(0, P[0], P[1], P[2]);   // persistent walks always have a row dim: coordinate 1 is y
-                };
-                if (p.persist) {
-                    int64_t st = G;
+                if (p.persist && p.waves > 1) {
+                    int64_t t = tile_first, st = tile_step;
 #pragma unroll
                     for (int i = 0; i < NDIG; i++) {
                         rx[i] = i == 0 ? p.tilesX : i == 1 ? p.tilesY : ((i - 2) < p.n_outer ? int(p.oext[p.n_outer - 1 - (i - 2)]) : 1);
+                        dg[i] = int(t % rx[i]); t /= rx[i];
                         sg[i] = int(st % rx[i]); st /= rx[i];
                     }
                     int wm = 1;
@@ -520,73 +524,46 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                         wmj[j] = moves_kernel ? wm : 0;
                         if (moves_kernel) wm *= int(p.oext[k]);
                     }
-                    digits_of(cur_tile);   // the tile of the first chunk (the prologue placed every thread on it)
                 }
-                int64_t ptile = cur_tile;
                 bool ok = true;
-                // the producer's own copy of the walk's position: `pstep` whole tiles done, `pq` = next row group of the
-                // range; (step, q) of this thread already stand after the first chunk
-                int pstep = step;
-                int64_t pq = q;
-                int rh = rh_cur, h = y_end - y0;
                 int chunk_no = 0;
                 bool announce = false;      // a new chunk's info still has to go into the ring (after the stage came free)
                 int c = c_begin + issued;   // the first loads of the first chunk were requested in the prologue
-                tb.x = y0;
+                int4 tb = p.persist && p.waves == 0 ? tail_tab[2] : tile_coords();
+                unsigned cur_bytes = chunk_bytes(rh_cur);
+                const CUtensorMap* cur_map = &tmaps.m[rh_cur - 1];
                 while (ok) {
                     if (c >= c_end) {
-                        if (!p.persist) break;
-                        bool found = false;
-                        while (!found) {
-                            if (pstep < p.waves) {
-                                {   // next whole tile: + gridDim.x (pstep >= 1 here: the first chunk was a whole tile)
-                                    int carry = 0;
-#pragma unroll
-                                    for (int i = 0; i < NDIG; i++) {
-                                        const int v = dg[i] + sg[i] + carry;
-                                        carry = v >= rx[i] ? 1 : 0;
-                                        dg[i] = v - (carry ? rx[i] : 0);
-                                    }
-                                    ptile += G;
-                                }
-                                pstep++;
-                                apply_digits();
-                                y0 = dg[1] * TH;
-                                h = p.OH - y0;
-                                if (h > TH) h = TH;
-                                found = true;
-                            } else {
-                                if (pq >= q_hi) break;
-                                const int64_t t = pq / RH;   // RH is a power of two or small constant: a shift / multiply
-                                const int g0 = int(pq - t * RH);
-                                int n = RH - g0;
-                                if (int64_t(n) > q_hi - pq) n = int(q_hi - pq);
-                                if (tail_first + t == ptile + 1) {   // next tile of the range: + 1
-                                    int carry = 1;
-#pragma unroll
-                                    for (int i = 0; i < NDIG; i++) {
-                                        const int v = dg[i] + carry;
-                                        carry = v >= rx[i] ? 1 : 0;
-                                        dg[i] = carry ? 0 : v;
-                                    }
-                                } else if (tail_first + t != ptile) {
-                                    digits_of(tail_first + t);   // once per CTA: where its range of row groups starts
-                                }
-                                ptile = tail_first + t;
-                                pq += n;
-                                apply_digits();
-                                y0 = dg[1] * TH + g0 * 8;
-                                h = p.OH - y0;
-                                if (h <= 0) continue;
-                                if (h > n * 8) h = n * 8;
-                                found = true;
-                            }
-                        }
-                        if (!found) break;
-                        rh = (h + 7) >> 3;
-                        tb.x = y0;
-                        c = c_begin;
                         chunk_no++;
+                        if (chunk_no >= n_chunks) break;
+                        if (chunk_no < p.waves) {
+                            int carry = 0;
+#pragma unroll
+                            for (int i = 0; i < NDIG; i++) {
+                                const int v = dg[i] + sg[i] + carry;
+                                carry = v >= rx[i] ? 1 : 0;
+                                dg[i] = v - (carry ? rx[i] : 0);
+                            }
+                            baseO = p.bO;
+                            int ws = 0, P[NO];
+#pragma unroll
+                            for (int j = 0; j < NO; j++) {
+                                baseO += dg[2 + j] * osj[j];
+                                P[j] = foli[j] ? dg[2 + j] : 0;
+                                ws += dg[2 + j] * wmj[j];
+                            }
+                            wset = p.wsets > 1 ? ws : 0;
+                            x0 = dg[0] * TW - p.xoff;
+                            y0 = dg[1] * TH;
+                            tb = make_int4(y0, P[0], P[1], P[2]);   // persistent walks always have a row dim: coordinate 1 is y
+                        } else {
+                            const int4* e = tail_tab + 3 * (chunk_no - p.waves);
+                            place(e[0], e[1]);
+                            tb = e[2];
+                            cur_bytes = chunk_bytes(rh_cur);
+                            cur_map = &tmaps.m[rh_cur - 1];
+                        }
+                        c = c_begin;
                         announce = true;
                     }
                     const int stage = issued % STAGES;
@@ -597,11 +574,11 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                             // every compute warp is past the chunk whose entry this overwrites (ring of STAGES + 1, at least
                             // one load per chunk, and the wait above); the arrive inside tma_fire publishes the stores
                             int4* e = tinfo + 2 * (chunk_no % (STAGES + 1));
-                            e[0] = make_int4(x0, y0, wset, h);
-                            *reinterpret_cast<int64_t*>(e + 1) = baseO;
+                            e[0] = make_int4(x0, y0, wset, y_end);
+                            e[1] = make_int4(int(unsigned(baseO & 0xffffffffLL)), int(baseO >> 32), rh_cur, 0);
                             announce = false;
                         }
-                        tma_fire(stage, rh, cc.x + tb.x, cc.y + tb.y, cc.z + tb.z, cc.w + tb.w);
+                        tma_fire(stage, cur_bytes, cur_map, cc.x + tb.x, cc.y + tb.y, cc.z + tb.z, cc.w + tb.w);
                     }
                     c++;
                 }
@@ -612,46 +589,32 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                     }
                 }
             }
-        } else if (have_work) {
+        } else {
             int g = 0;   // loads consumed so far, same numbering as the producer's
             bool ok = true;
-            int chunk_no = 0;
-            while (true) {
-                if (RING && chunk_no > 0) {
-                    // where this chunk lives: published by the producer before the chunk's first load, so wait for that
-                    // load (the loop below finds it complete) and pick the entry up
-                    if (!wait_or_abort(&full_bar[g % STAGES], unsigned(g / STAGES) & 1u)) { ok = false; break; }
-                    const int4* e = tinfo + 2 * (chunk_no % (STAGES + 1));
-                    const int4 a = e[0];
-                    x0 = a.x; y0 = a.y; wset = a.z;
-                    rh_cur = (a.w + 7) >> 3;
-                    y_end = a.y + a.w;
-                    baseO = *reinterpret_cast<const int64_t*>(e + 1);
-                }
-                // the channel loop of one chunk, specialised on the rows per warp: the switch sits outside the loop, so the
-                // loop body is straight-line code the compiler can schedule across iterations, as for a fixed tile height
-                auto run_chunk = [&](auto rows_tag) {
-                    if (p.wloop) {
-                        // one image tile (a single channel), every weight set in turn: multiply-adds, store, clear. The
-                        // stage goes back to the producer only after the last set.
-                        const int stage = g % STAGES;
-                        if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; return; }
-                        for (int ws = 0; ws < p.wsets; ws++) {
-                            wset = ws;
-                            consume(rows_tag, stage, c_begin);
-                            if (ws + 1 < p.wsets) {
-                                store_tile(wofs[ws]);
+            // the channel loop of one chunk, specialised on the rows per warp: the choice sits outside the loop, so the
+            // loop body is straight-line code the compiler can schedule across iterations, as for a fixed tile height
+            auto run_chunk = [&](auto rows_tag) {
+                if constexpr (WLOOP) {
+                    // one image tile (a single channel), every weight set in turn: multiply-adds, store, clear. The
+                    // stage goes back to the producer only after the last set.
+                    const int stage = g % STAGES;
+                    if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; return; }
+                    for (int ws = 0; ws < p.wsets; ws++) {
+                        wset = ws;
+                        consume(rows_tag, stage, c_begin);
+                        if (ws + 1 < p.wsets) {
+                            store_tile(wofs[ws]);
 #pragma unroll
-                                for (int i = 0; i < RH; i++)
+                            for (int i = 0; i < RH; i++)
 #pragma unroll
-                                    for (int x = 0; x < CW; x++) acc[i][x] = T(0);
-                            }
+                                for (int x = 0; x < CW; x++) acc[i][x] = T(0);
                         }
-                        __syncwarp();
-                        if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
-                        g++;
-                        return;
                     }
+                    __syncwarp();
+                    if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
+                    g++;
+                } else {
                     for (int c = c_begin; c < c_end; c++, g++) {
                         const int stage = g % STAGES;
                         if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; break; }
@@ -659,30 +622,34 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                         __syncwarp();
                         if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
                     }
-                };
-                if (!p.persist || rh_cur == RH) run_chunk(NkRows<RH>{});
-                else {
-                    switch (rh_cur) {
-                        case 1: run_chunk(NkRows<1>{}); break;
-                        case 2: if constexpr (RH > 2) run_chunk(NkRows<2>{}); break;
-                        case 3: if constexpr (RH > 3) run_chunk(NkRows<3>{}); break;
-                        case 4: if constexpr (RH > 4) run_chunk(NkRows<4>{}); break;
-                        case 5: if constexpr (RH > 5) run_chunk(NkRows<5>{}); break;
-                        case 6: if constexpr (RH > 6) run_chunk(NkRows<6>{}); break;
-                        default: if constexpr (RH > 7) run_chunk(NkRows<7>{}); break;
+                }
+            };
+            for (int chunk_no = 0; chunk_no < n_chunks; chunk_no++) {
+                if (chunk_no >= p.waves && p.persist) {
+                    // a chunk of the last, partial wave: 1, 2, 4 or RH rows per warp
+                    const int4* e = tail_tab + 3 * (chunk_no - p.waves);
+                    place(e[0], e[1]);
+                } else if (chunk_no > 0) {
+                    if (RING) {
+                        // where this tile lives: published by the producer before the tile's first load, so wait for that
+                        // load (the loop below finds it complete) and pick the entry up
+                        if (!wait_or_abort(&full_bar[g % STAGES], unsigned(g / STAGES) & 1u)) { ok = false; break; }
+                        const int4* e = tinfo + 2 * (chunk_no % (STAGES + 1));
+                        place(e[0], e[1]);
+                    } else {
+                        tile_set(tile_first + chunk_no * tile_step);   // long tiles: a dozen divisions per tile do not matter
                     }
                 }
+                if (rh_cur == RH) run_chunk(NkRows<RH>{});
+                else if (rh_cur == 1) run_chunk(NkRows<1>{});
+                else if (rh_cur == 2) { if constexpr (RH > 2) run_chunk(NkRows<2>{}); }
+                else { if constexpr (RH > 4) run_chunk(NkRows<4>{}); }
                 if (!ok || !p.persist) break;   // one tile per CTA: its epilogue follows below
-                store_tile(p.wloop ? wofs[p.wsets - 1] : 0);
+                store_tile(WLOOP ? wofs[p.wsets - 1] : 0);
 #pragma unroll
                 for (int i = 0; i < RH; i++)
 #pragma unroll
                     for (int x = 0; x < CW; x++) acc[i][x] = T(0);
-                chunk_no++;
-                // long chunks: a dozen divisions per chunk do not matter; with the ring the walk only has to be counted
-                // (the position comes from the ring entry at the top of the loop)
-                if (RING) { if (chunk_no >= n_chunks) break; }
-                else if (!next_chunk()) break;
             }
         }
         __syncthreads();
@@ -856,8 +823,8 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     if (TMA) {
         if (C::SW > 256 || C::SH > 256) return -1;
         p.persist = balanced() ? 1 : 0;
-        // persistent: one map per rows-per-warp value (box of 8 r + KH - 1 rows); otherwise only the full tile's map
-        for (int r = p.persist ? 1 : RH; r <= RH; r++) {
+        // persistent: one map per rows-per-warp value 1, 2, 4, (8) (box of 8 r + KH - 1 rows); otherwise only the full tile's map
+        for (int r = p.persist ? 1 : RH; r <= RH; r *= 2) {
             int st = nk_tma_encode(ctx, sizeof(T) == 4 ? NK_F32 : NK_F64, *img, C::SW, 8 * r + KH - 1, p.has_y != 0, &tmaps.m[r - 1]);
             if (st == -1) return -1;
             if (st) return st;
@@ -914,10 +881,16 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     }
     if constexpr (TMA) {
         if (ring) {
-            cudaError_t e = cudaFuncSetAttribute(nk_conv_tiled_kernel<T, KH, KW, RH, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+            cudaError_t e = cudaFuncSetAttribute(nk_conv_tiled_kernel<T, KH, KW, RH, true, NK_TILED_RING>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
             if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel, ring)");
-            nk_conv_tiled_kernel<T, KH, KW, RH, true, true><<<unsigned(grid), threads, smem, ctx->stream>>>(out, partial, I, K, p, tmaps);
+            nk_conv_tiled_kernel<T, KH, KW, RH, true, NK_TILED_RING><<<unsigned(grid), threads, smem, ctx->stream>>>(out, partial, I, K, p, tmaps);
             return nk_after_launch(ctx, "nk_conv_tiled_kernel<tma,ring>");
+        }
+        if (p.wloop) {
+            cudaError_t e = cudaFuncSetAttribute(nk_conv_tiled_kernel<T, KH, KW, RH, true, NK_TILED_WLOOP>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+            if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel, weight loop)");
+            nk_conv_tiled_kernel<T, KH, KW, RH, true, NK_TILED_WLOOP><<<unsigned(grid), threads, smem, ctx->stream>>>(out, partial, I, K, p, tmaps);
+            return nk_after_launch(ctx, "nk_conv_tiled_kernel<tma,wloop>");
         }
     }
     nk_conv_tiled_kernel<T, KH, KW, RH, TMA><<<unsigned(grid), threads, smem, ctx->stream>>>(out, partial, I, K, p, tmaps);

@@ -3,6 +3,7 @@ Function.of("i0 x i1"), XConvLeft/XConvRight, backward() of convolutions, broadc
 import numpy as np
 import pytest
 
+from neureka_b200 import _lib as L
 from neureka_b200.functions import Function
 from neureka_b200.tensor import Tensor
 

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 def test_find_by_keyword(device):
     assert CudaBackend.find("cuda") is device
     assert CudaBackend.find("gpu") is device
-    assert CudaBackend.find("0") is device
+    assert CudaBackend.find("0") is device and CudaBackend.find("cuda:0") is device and CudaBackend.find("gpu:99") is None
     assert CudaBackend.find("banana") is None
     assert device.props.sm_count > 0 and device.props.cc_major >= 10
 
