@@ -62,6 +62,7 @@ struct TiledPlan {
     int persist;      // TMA family: the grid is one resident wave; whole waves of tiles, then the rest dealt in 8-row groups
     int64_t tiles_total;
     int waves;            // whole waves: in wave w CTA b takes tile w * gridDim.x + b
+    int tail;             // the tiles after the whole waves are dealt in 16-row units (else whole, to the first CTAs)
     int wsets;        // persistent walk over tiles whose weights differ: weight sets staged at once (1 = same weights everywhere)
     // Weight loop (persistent walks of one-channel chunks whose outer output dims that move the kernel -- the output
     // channels of an image gradient -- touch neither the image nor the reduction): those dims are not part of the tile
@@ -122,7 +123,7 @@ struct TiledCfg {
     static constexpr bool WREG = KH * KW * int(sizeof(T)) <= 400;   // weights of one channel live in registers
     static constexpr int CPR = SW / CW;                       // LDGSTS chunks per row
     static constexpr int NIT = (SH * CPR + 255) / 256;        // LDGSTS chunks per thread
-    static constexpr int MAX_TAIL = 8;                        // chunks of the last, partial wave per CTA (at most RH groups, one each)
+    static constexpr int MAX_TAIL = 8;                        // chunks of the last, partial wave per CTA (at most RH / 2 units + 1, one each)
     static constexpr int FIXED_BYTES = 384 + MAX_TAIL * 48;
     static size_t smem_bytes(int NQ, int wsets = 1) {
         // [stages | mbarriers + abort word + tail count (128 B) | tile-info ring (256 B) | tail table (48 B per chunk) |
@@ -132,7 +133,7 @@ struct TiledCfg {
     }
 };
 
-// The tensor maps of a launch: entry r - 1 has a box of 8 * r + KH - 1 rows (r = rows per warp of a chunk: 1, 2, 4 or 8).
+// The tensor maps of a launch: entry r - 1 has a box of 8 * r + KH - 1 rows (r = rows per warp of a chunk: 2, 4 or 8).
 struct TmapSet { CUtensorMap m[8]; };
 template <int N> struct NkRows { static constexpr int value = N; };
 // Variants of the persistent TMA kernel: chunks decoded by the compute warps / taken from the producer's ring / weight loop
@@ -179,7 +180,9 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
     // blockIdx.x, blockIdx.x + gridDim.x, ... for p.waves steps and then the CTA's chunks of the last, partial wave, with the
     // load pipeline running on across chunk boundaries.
     const int split = p.persist ? 0 : int(blockIdx.x % unsigned(p.splits));
-    const int64_t tile_first = p.persist ? (p.waves > 0 ? int64_t(blockIdx.x) : 0) : int64_t(blockIdx.x / unsigned(p.splits));
+    // whole tiles of this CTA: p.waves, and one more for the first CTAs when the last, partial wave is dealt in whole tiles too
+    const int my_waves = p.waves + ((p.persist && !p.tail && int64_t(blockIdx.x) < p.tiles_total - int64_t(p.waves) * gridDim.x) ? 1 : 0);
+    const int64_t tile_first = p.persist ? (my_waves > 0 ? int64_t(blockIdx.x) : 0) : int64_t(blockIdx.x / unsigned(p.splits));
     const int64_t tile_step = gridDim.x;
     int64_t baseI, baseK, baseO;
     int pidx[NK_TILED_MAX_OUTER];
@@ -268,8 +271,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
         *abort_word = 0;
         nk_fence_barrier_init();
         nk_fence_proxy_async();
-        auto first_loads = [&]() {
-            const int4 tb = tile_coords();
+        auto first_loads = [&](const int4 tb) {   // of the chunk this thread stands on
             for (int it = 0; it < STAGES && it < n_it; it++) {
                 int cc[4];
                 chan_coords(c_begin + it, cc);
@@ -277,49 +279,45 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             }
         };
         if (!p.persist) {
-            first_loads();
+            first_loads(tile_coords());
         } else {
-            if (p.waves > 0) first_loads();
-            // The last, partial wave: the tiles after the whole waves are cut into groups of 8 rows (RH per tile) and the
-            // groups, laid end to end in tile order, dealt to the CTAs in equal contiguous ranges -- less than one tile's
-            // worth each. A range is cut into chunks of 1, 2, 4 or 8 groups (the rows per warp the multiply-add loop
-            // exists for) that stop at tile ends; chunks entirely below the image's last row are dropped.
+            if (my_waves > 0) first_loads(tile_coords());
+            // The last, partial wave (p.tail): the tiles after the whole waves are cut into units of 16 rows (RH / 2 per tile) and
+            // the units, laid end to end in tile order, dealt to the CTAs in equal contiguous ranges -- less than one tile's
+            // worth each. A range is cut into chunks of 1, 2 or 4 units (2, 4, 8 rows per warp: the multiply-add loop
+            // exists for those) that stop at tile ends; chunks entirely below the image's last row are dropped.
+            constexpr int UPT = RH / 2;
             const int64_t G = gridDim.x;
             const int64_t tail_first = int64_t(p.waves) * G;
-            const int64_t tail_groups = (p.tiles_total - tail_first) * RH;
-            int64_t q = (int64_t(blockIdx.x) * tail_groups) / G;
-            const int64_t q_hi = (int64_t(blockIdx.x + 1) * tail_groups) / G;
+            const int64_t tail_units = p.tail ? (p.tiles_total - tail_first) * UPT : 0;
+            int64_t q = (int64_t(blockIdx.x) * tail_units) / G;
+            const int64_t q_hi = (int64_t(blockIdx.x + 1) * tail_units) / G;
             int nt = 0;
             while (q < q_hi && nt < C::MAX_TAIL) {
-                const int64_t t = q / RH;
-                const int g0 = int(q - t * RH);
-                int n = RH - g0;
+                const int64_t t = q / UPT;
+                const int u0 = int(q - t * UPT);
+                int n = UPT - u0;
                 if (int64_t(n) > q_hi - q) n = int(q_hi - q);
-                n = n >= 8 ? 8 : n >= 4 ? 4 : n >= 2 ? 2 : 1;
+                n = n >= 4 ? 4 : n >= 2 ? 2 : 1;
                 q += n;
                 tile_set(tail_first + t);
-                y0 += g0 * 8;
+                y0 += u0 * 16;
                 int h = p.OH - y0;
                 if (h <= 0) continue;
-                if (h > n * 8) h = n * 8;
-                const int r = (h + 7) >> 3;
+                if (h > n * 16) h = n * 16;
+                const int r = (h + 7) >> 3;   // rows per warp: the next of 2, 4, 8 (rows below y0 + h are not stored)
                 int4* e = tail_tab + 3 * nt;
                 e[0] = make_int4(x0, y0, wset, y0 + h);
-                e[1] = make_int4(int(unsigned(baseO & 0xffffffffLL)), int(baseO >> 32), r > 4 ? 8 : r > 2 ? 4 : r, 0);
+                e[1] = make_int4(int(unsigned(baseO & 0xffffffffLL)), int(baseO >> 32), r > 4 ? 8 : r > 2 ? 4 : 2, 0);
                 e[2] = tile_coords();
                 nt++;
             }
             *n_tail_word = nt;
-            if (p.waves > 0) {
+            if (my_waves > 0) {
                 tile_set(tile_first);   // back on the first whole tile
             } else if (nt > 0) {
                 place(tail_tab[0], tail_tab[1]);
-                const int4 tb = tail_tab[2];
-                for (int it = 0; it < STAGES && it < n_it; it++) {
-                    int cc[4];
-                    chan_coords(c_begin + it, cc);
-                    tma_fire(it, chunk_bytes(rh_cur), &tmaps.m[rh_cur - 1], cc[0] + tb.x, cc[1] + tb.y, cc[2] + tb.z, cc[3] + tb.w);
-                }
+                first_loads(tail_tab[2]);
             }
         }
     }
@@ -417,9 +415,9 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
 
     // One channel's worth of multiply-adds for this thread, RHC rows per warp (tile rows warp*RHC .. +RHC, columns
     // lane*CW .. +CW). The order of the additions into one output does not depend on RHC: channel, then ky, then kx.
-    auto consume = [&](auto rows_tag, int stage, int c) {
+    auto consume = [&](auto rows_tag, const unsigned char* box, int c) {
         constexpr int RHC = decltype(rows_tag)::value;
-        const T* tile = reinterpret_cast<const T*>(stage_base + size_t(stage) * C::STAGE_BYTES) + (warp * RHC) * SW + lane * CW;
+        const T* tile = reinterpret_cast<const T*>(box) + (warp * RHC) * SW + lane * CW;
         const T* wc = wsm + (size_t(wset) * p.NQ + c) * WPAD;
         T w[C::WREG ? WPAD : CW];
         if (C::WREG) {
@@ -492,7 +490,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             return r > 0;
         };
         // chunks of this CTA's walk: the whole tiles, then the entries of the table
-        const int n_chunks = p.persist ? p.waves + *n_tail_word : 1;
+        const int n_chunks = p.persist ? my_waves + *n_tail_word : 1;
         if (warp == 8) {
             if (lane == 0 && n_chunks > 0) {
                 // `issued` counts tile loads over the CTA's whole life: load g uses stage g % STAGES in round g / STAGES.
@@ -505,7 +503,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                 int dg[NDIG], sg[NDIG], rx[NDIG], wmj[NO];
                 long long osj[NO];
                 bool foli[NO];
-                if (p.persist && p.waves > 1) {
+                if (p.persist && my_waves > 1) {
                     int64_t t = tile_first, st = tile_step;
 #pragma unroll
                     for (int i = 0; i < NDIG; i++) {
@@ -528,15 +526,15 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                 bool ok = true;
                 int chunk_no = 0;
                 bool announce = false;      // a new chunk's info still has to go into the ring (after the stage came free)
-                int c = c_begin + issued;   // the first loads of the first chunk were requested in the prologue
-                int4 tb = p.persist && p.waves == 0 ? tail_tab[2] : tile_coords();
+                int4 tb = p.persist && my_waves == 0 ? tail_tab[2] : tile_coords();
                 unsigned cur_bytes = chunk_bytes(rh_cur);
                 const CUtensorMap* cur_map = &tmaps.m[rh_cur - 1];
+                int c = c_begin + issued;   // the first loads of the first chunk were requested in the prologue
                 while (ok) {
                     if (c >= c_end) {
                         chunk_no++;
                         if (chunk_no >= n_chunks) break;
-                        if (chunk_no < p.waves) {
+                        if (chunk_no < my_waves) {
                             int carry = 0;
 #pragma unroll
                             for (int i = 0; i < NDIG; i++) {
@@ -557,7 +555,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                             y0 = dg[1] * TH;
                             tb = make_int4(y0, P[0], P[1], P[2]);   // persistent walks always have a row dim: coordinate 1 is y
                         } else {
-                            const int4* e = tail_tab + 3 * (chunk_no - p.waves);
+                            const int4* e = tail_tab + 3 * (chunk_no - my_waves);
                             place(e[0], e[1]);
                             tb = e[2];
                             cur_bytes = chunk_bytes(rh_cur);
@@ -567,7 +565,6 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                         announce = true;
                     }
                     const int stage = issued % STAGES;
-                    const int4 cc = *reinterpret_cast<const int4*>(&ctab[c * 4 + 2]);
                     if (issued >= STAGES) ok = wait_or_abort(&empty_bar[stage], unsigned(issued / STAGES - 1) & 1u);
                     if (ok) {
                         if (RING && announce) {
@@ -578,6 +575,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                             e[1] = make_int4(int(unsigned(baseO & 0xffffffffLL)), int(baseO >> 32), rh_cur, 0);
                             announce = false;
                         }
+                        const int4 cc = *reinterpret_cast<const int4*>(&ctab[c * 4 + 2]);
                         tma_fire(stage, cur_bytes, cur_map, cc.x + tb.x, cc.y + tb.y, cc.z + tb.z, cc.w + tb.w);
                     }
                     c++;
@@ -597,37 +595,59 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             auto run_chunk = [&](auto rows_tag) {
                 if constexpr (WLOOP) {
                     // one image tile (a single channel), every weight set in turn: multiply-adds, store, clear. The
-                    // stage goes back to the producer only after the last set.
+                    // stage goes back to the producer after the last set's multiply-adds.
+                    constexpr int RHC = decltype(rows_tag)::value;
                     const int stage = g % STAGES;
                     if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; return; }
+                    // where this thread's rows go does not depend on the weight set: worked out once per chunk
+                    const int ox = x0 + lane * CW;
+                    const bool fast = p.vec_out != 0 && ox >= 0 && ox + CW <= p.OW;   // whole 16-byte stores
+                    T* const dst0 = out + baseO + int64_t(y0 + warp * RHC) * p.sOy + ox;
+                    const int rows_ok = y_end - (y0 + warp * RHC);                     // rows of this thread inside the chunk
                     for (int ws = 0; ws < p.wsets; ws++) {
                         wset = ws;
-                        consume(rows_tag, stage, c_begin);
-                        if (ws + 1 < p.wsets) {
-                            store_tile(wofs[ws]);
-#pragma unroll
-                            for (int i = 0; i < RH; i++)
-#pragma unroll
-                                for (int x = 0; x < CW; x++) acc[i][x] = T(0);
+                        // the tile's address is made opaque per weight set: otherwise the compiler keeps the whole tile in
+                        // registers across the loop (168 of them, one CTA per SM: measured 20 % slower)
+                        int st = stage;
+                        asm volatile("" : "+r"(st));
+                        consume(rows_tag, stage_base + size_t(st) * C::STAGE_BYTES, c_begin);
+                        if (ws + 1 == p.wsets) {
+                            __syncwarp();
+                            if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
                         }
+                        if (fast) {
+                            T* d = dst0 + wofs[ws];
+#pragma unroll
+                            for (int i = 0; i < RHC; i++) {
+                                if (i < rows_ok) {
+                                    if (sizeof(T) == 4) *reinterpret_cast<float4*>(d) = *reinterpret_cast<float4*>(&acc[i][0]);
+                                    else *reinterpret_cast<double2*>(d) = *reinterpret_cast<double2*>(&acc[i][0]);
+                                }
+                                d += p.sOy;
+                            }
+                        } else {
+                            store_tile(wofs[ws]);
+                        }
+#pragma unroll
+                        for (int i = 0; i < RH; i++)
+#pragma unroll
+                            for (int x = 0; x < CW; x++) acc[i][x] = T(0);
                     }
-                    __syncwarp();
-                    if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
                     g++;
                 } else {
                     for (int c = c_begin; c < c_end; c++, g++) {
                         const int stage = g % STAGES;
                         if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; break; }
-                        consume(rows_tag, stage, c);
+                        consume(rows_tag, stage_base + size_t(stage) * C::STAGE_BYTES, c);
                         __syncwarp();
                         if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
                     }
                 }
             };
             for (int chunk_no = 0; chunk_no < n_chunks; chunk_no++) {
-                if (chunk_no >= p.waves && p.persist) {
-                    // a chunk of the last, partial wave: 1, 2, 4 or RH rows per warp
-                    const int4* e = tail_tab + 3 * (chunk_no - p.waves);
+                if (chunk_no >= my_waves && p.persist) {
+                    // a chunk of the last, partial wave: 2, 4 or RH rows per warp
+                    const int4* e = tail_tab + 3 * (chunk_no - my_waves);
                     place(e[0], e[1]);
                 } else if (chunk_no > 0) {
                     if (RING) {
@@ -641,15 +661,16 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                     }
                 }
                 if (rh_cur == RH) run_chunk(NkRows<RH>{});
-                else if (rh_cur == 1) run_chunk(NkRows<1>{});
-                else if (rh_cur == 2) { if constexpr (RH > 2) run_chunk(NkRows<2>{}); }
+                else if (rh_cur == 2) run_chunk(NkRows<2>{});
                 else { if constexpr (RH > 4) run_chunk(NkRows<4>{}); }
                 if (!ok || !p.persist) break;   // one tile per CTA: its epilogue follows below
-                store_tile(WLOOP ? wofs[p.wsets - 1] : 0);
+                if constexpr (!WLOOP) {         // (the weight loop stores every set's result itself)
+                    store_tile();
 #pragma unroll
-                for (int i = 0; i < RH; i++)
+                    for (int i = 0; i < RH; i++)
 #pragma unroll
-                    for (int x = 0; x < CW; x++) acc[i][x] = T(0);
+                        for (int x = 0; x < CW; x++) acc[i][x] = T(0);
+                }
             }
         }
         __syncthreads();
@@ -671,7 +692,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             const int nxt = it + STAGES - 1;
             if (nxt < n_it) ldgsts_stage(nxt % STAGES, c_begin + nxt);
             nk_cp_async_commit();
-            consume(NkRows<RH>{}, it % STAGES, c_begin + it);
+            consume(NkRows<RH>{}, stage_base + size_t(it % STAGES) * C::STAGE_BYTES, c_begin + it);
         }
         nk_cp_async_wait<0>();
     }
@@ -816,6 +837,7 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     p.persist = 0;
     p.tiles_total = tiles;
     p.waves = 0;
+    p.tail = 0;
     TmapSet tmaps;
     memset(&tmaps, 0, sizeof(tmaps));
     bool ring = false;
@@ -823,17 +845,31 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     if (TMA) {
         if (C::SW > 256 || C::SH > 256) return -1;
         p.persist = balanced() ? 1 : 0;
-        // persistent: one map per rows-per-warp value 1, 2, 4, (8) (box of 8 r + KH - 1 rows); otherwise only the full tile's map
-        for (int r = p.persist ? 1 : RH; r <= RH; r *= 2) {
+        // persistent: one map per rows-per-warp value 2, 4, (8) (box of 8 r + KH - 1 rows); otherwise only the full tile's map
+        for (int r = p.persist ? 2 : RH; r <= RH; r *= 2) {
             int st = nk_tma_encode(ctx, sizeof(T) == 4 ? NK_F32 : NK_F64, *img, C::SW, 8 * r + KH - 1, p.has_y != 0, &tmaps.m[r - 1]);
             if (st == -1) return -1;
             if (st) return st;
         }
         p.status = ctx->tma_status_dev;
         if (p.persist) {
-            // One resident wave of CTAs: whole waves of tiles first, then the rest in 8-row groups, at least two groups
-            // (16 rows) per CTA (each chunk re-reads KH - 1 halo rows and pays a fixed set-up).
+            // One resident wave of CTAs: whole waves of tiles first, then the rest in 16-row units, at least one per CTA
+            // (each chunk re-reads KH - 1 halo rows and pays a fixed set-up).
             ring = p.NQ < 8 && !p.wloop;   // short chunks: decoding would cost as much as the chunk's arithmetic
+            if constexpr (TMA) {
+                if (ring || p.wloop) {
+                    // these walks run another variant of the kernel: the resident wave is what THAT variant's registers allow
+                    auto kern = ring ? nk_conv_tiled_kernel<T, KH, KW, RH, true, NK_TILED_RING> : nk_conv_tiled_kernel<T, KH, KW, RH, true, NK_TILED_WLOOP>;
+                    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+                    if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel, variant)");
+                    int per_sm = 1;
+                    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 288, smem) != cudaSuccess || per_sm < 1) {
+                        cudaGetLastError();
+                        per_sm = 1;
+                    }
+                    slots = int64_t(ctx->prop.multiProcessorCount) * per_sm;
+                }
+            }
             grid = slots;
             if (tiles < grid) {
                 grid = tiles * RH / 2;
@@ -842,6 +878,14 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
             }
             p.waves = int(tiles / grid);
             if (tiles / grid > 0x3fffffff) return -1;
+            // The tiles left after the whole waves: dealt in 16-row units while that is cheaper than one more step of whole
+            // tiles for some CTAs. A short chunk runs at about half the rate of a whole tile -- with 2 rows per warp a thread
+            // loads 6 row segments from shared memory per 200 multiply-adds instead of 12 per 800, which makes the chunk
+            // shared-memory bound -- while the CTAs of a last whole-tile step run alone on their SMs, faster than in pairs.
+            // Measured on B200 (F32 5x5, 32 channels): units win at 0.46 tiles left per CTA (3.7 %), lose from 0.8 on.
+            static const int tail_pct = [] { const char* e = getenv("NK_TILED_TAIL_PCT"); return e ? atoi(e) : 50; }();
+            const int64_t left = tiles - int64_t(p.waves) * grid;
+            p.tail = (p.waves == 0 || left * 100 <= grid * tail_pct) ? 1 : 0;
         }
     }
     if (grid > 0x7fffffffLL) return -1;
@@ -881,14 +925,10 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     }
     if constexpr (TMA) {
         if (ring) {
-            cudaError_t e = cudaFuncSetAttribute(nk_conv_tiled_kernel<T, KH, KW, RH, true, NK_TILED_RING>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-            if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel, ring)");
             nk_conv_tiled_kernel<T, KH, KW, RH, true, NK_TILED_RING><<<unsigned(grid), threads, smem, ctx->stream>>>(out, partial, I, K, p, tmaps);
             return nk_after_launch(ctx, "nk_conv_tiled_kernel<tma,ring>");
         }
         if (p.wloop) {
-            cudaError_t e = cudaFuncSetAttribute(nk_conv_tiled_kernel<T, KH, KW, RH, true, NK_TILED_WLOOP>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-            if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel, weight loop)");
             nk_conv_tiled_kernel<T, KH, KW, RH, true, NK_TILED_WLOOP><<<unsigned(grid), threads, smem, ctx->stream>>>(out, partial, I, K, p, tmaps);
             return nk_after_launch(ctx, "nk_conv_tiled_kernel<tma,wloop>");
         }
