@@ -4,10 +4,13 @@
 //
 // One CTA walks a list of work units; a unit is one TH x TW tile of T2 (the error) for one outer reduction index,
 // together with the (TH+KH-1) x (TW+KW-1) tile of T1 (the image) at the same position. Both tiles arrive by TMA
-// (zero fill outside the tensors: a missing term contributes 0, exactly like the reference's range check) into a
-// three-stage shared-memory ring fed by a producer warp (full/empty mbarriers, every wait bounded; the eight compute
-// warps never meet a CTA-wide barrier inside the loop). A thread owns RH x CW positions of the error tile and keeps all KH x KW partial
-// sums in registers; every image row segment it loads feeds up to KH taps rows. After its last unit the CTA reduces
+// (zero fill outside the tensors: a missing term contributes 0, exactly like the reference's range check) into two
+// shared-memory rings fed by a producer warp (full/empty mbarriers, every wait bounded; the eight compute warps never
+// meet a CTA-wide barrier inside the loop). A thread owns RH x CW positions of the error tile, which it copies into
+// registers at the start of a unit -- so the error ring's slot is free again at once and needs fewer stages than the
+// image ring -- and keeps all KH x KW partial sums in registers; every image row segment it loads feeds up to KH tap
+// rows. Small F32 windows run 8 rows per thread (image ring of 2, error ring of 1: two CTAs per SM), the others 4 rows
+// (rings of 3 and 3, one barrier pair per slot for both tiles). After its last unit the CTA reduces
 // the partial sums (warp shuffles, then the eight warp results in order) and writes one partial window to scratch;
 // a second kernel adds the CTAs' windows in CTA order, so the result does not depend on scheduling.
 #pragma once
@@ -32,7 +35,7 @@ struct WgradPlan {
 template <class T, int KH, int KW>
 struct WgradCfg {
     static constexpr int CW = 16 / int(sizeof(T));
-    static constexpr int RH = 4;
+    static constexpr int RH = (sizeof(T) == 4 && KH * KW <= 25) ? 8 : 4;
     static constexpr int TW = 32 * CW;
     static constexpr int TH = 8 * RH;
     static constexpr int HALO_W = ((KW - 1 + CW - 1) / CW) * CW;
@@ -41,25 +44,29 @@ struct WgradCfg {
     static constexpr int NS = CW + HALO_W;
     static constexpr int A_BYTES = ((SH * SW * int(sizeof(T)) + 127) / 128) * 128;
     static constexpr int E_BYTES = ((TH * TW * int(sizeof(T)) + 127) / 128) * 128;
-    static constexpr int STAGES = 3;
-    static size_t smem_bytes() { return size_t(STAGES) * (A_BYTES + E_BYTES) + 128 + size_t(8) * KH * KW * sizeof(T); }
+    static constexpr int NA = RH == 8 ? 2 : 3;   // stages of the image ring
+    static constexpr int NE = RH == 8 ? 1 : 3;   // stages of the error ring
+    static size_t smem_bytes() { return size_t(NA) * A_BYTES + size_t(NE) * E_BYTES + 128 + size_t(8) * KH * KW * sizeof(T); }
 };
 
-// 288 threads: warps 0..7 multiply, warp 8 feeds the ring. full[s] completes when both tiles of a unit have landed
-// (one arrival + their bytes), empty[s] when all eight compute warps are done with stage s. Every wait is bounded.
+// 288 threads: warps 0..7 multiply, warp 8 feeds the rings. A full barrier completes when its tile has landed (one
+// arrival + the tile's bytes), an empty barrier when all eight compute warps are done with the slot. Every wait is bounded.
 template <class T, int KH, int KW>
 __global__ void __launch_bounds__(288) nk_conv_wgrad_kernel(T* __restrict__ partial, const WgradPlan p,
                                                             const __grid_constant__ CUtensorMap mapA,
                                                             const __grid_constant__ CUtensorMap mapE) {
     using C = WgradCfg<T, KH, KW>;
-    constexpr int CW = C::CW, RH = C::RH, TW = C::TW, TH = C::TH, SW = C::SW, SH = C::SH, NS = C::NS, STAGES = C::STAGES;
+    constexpr int CW = C::CW, RH = C::RH, TW = C::TW, TH = C::TH, SW = C::SW, SH = C::SH, NS = C::NS, NA = C::NA, NE = C::NE;
+    constexpr bool COUPLED = NA == NE;
     extern __shared__ __align__(128) unsigned char nk_smem[];
     unsigned char* a_base = nk_smem;
-    unsigned char* e_base = nk_smem + size_t(STAGES) * C::A_BYTES;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(nk_smem + size_t(STAGES) * (C::A_BYTES + C::E_BYTES));
-    uint64_t* empty_bar = full_bar + STAGES;
-    volatile int* abort_word = reinterpret_cast<volatile int*>(full_bar + 2 * STAGES);
-    T* red = reinterpret_cast<T*>(nk_smem + size_t(STAGES) * (C::A_BYTES + C::E_BYTES) + 128);
+    unsigned char* e_base = nk_smem + size_t(NA) * C::A_BYTES;
+    uint64_t* full_a = reinterpret_cast<uint64_t*>(nk_smem + size_t(NA) * C::A_BYTES + size_t(NE) * C::E_BYTES);
+    uint64_t* empty_a = full_a + NA;
+    uint64_t* full_e = empty_a + NA;
+    uint64_t* empty_e = full_e + NE;
+    volatile int* abort_word = reinterpret_cast<volatile int*>(empty_e + NE);   // 2 (NA + NE) <= 10 barriers: inside the 128 bytes
+    T* red = reinterpret_cast<T*>(nk_smem + size_t(NA) * C::A_BYTES + size_t(NE) * C::E_BYTES + 128);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int64_t pflat = blockIdx.x / p.chunks;
@@ -70,7 +77,8 @@ __global__ void __launch_bounds__(288) nk_conv_wgrad_kernel(T* __restrict__ part
     const int64_t n_it = u_end > u_begin ? u_end - u_begin : 0;
 
     if (tid == 256) {
-        for (int s = 0; s < STAGES; s++) { nk_mbar_init(&full_bar[s], 1); nk_mbar_init(&empty_bar[s], 8); }
+        for (int s = 0; s < NA; s++) { nk_mbar_init(&full_a[s], 1); nk_mbar_init(&empty_a[s], 8); }
+        for (int s = 0; s < NE; s++) { nk_mbar_init(&full_e[s], 1); nk_mbar_init(&empty_e[s], 8); }
         *abort_word = 0;
         nk_fence_barrier_init();
     }
@@ -104,23 +112,38 @@ __global__ void __launch_bounds__(288) nk_conv_wgrad_kernel(T* __restrict__ part
                 const int ty0 = int(rem % p.tilesY); rem /= p.tilesY;
                 for (int k = p.n_outer - 1; k >= 0; k--) { q[k] = int(rem % p.qext[k]); rem /= p.qext[k]; }
                 int tx = tx0, ty = ty0;
-                const unsigned bytes = unsigned(((p.has_y ? SH : 1) * SW + (p.has_y ? TH : 1) * TW) * sizeof(T));
+                const unsigned bytes_a = unsigned((p.has_y ? SH : 1) * SW * sizeof(T));
+                const unsigned bytes_e = unsigned((p.has_y ? TH : 1) * TW * sizeof(T));
                 nk_fence_proxy_async();
                 bool ok = true;
-                int64_t issued = 0;
+                int64_t issued_a = 0, issued_e = 0;
                 for (int64_t it = 0; it < n_it && ok; it++) {
-                    const int stage = int(it % STAGES);
+                    const int sa = int(it % NA), se = int(it % NE);
                     int ca[5], ce[5];
                     ca[0] = ce[0] = tx * TW;
                     int n = 1;
                     if (p.has_y) { ca[n] = ce[n] = ty * TH; n++; }
                     for (int k = p.n_outer - 1; k >= 0; k--) { ce[n] = q[k]; ca[n] = pidx[k] + q[k]; n++; }
-                    if (it >= STAGES) ok = wait_or_abort(&empty_bar[stage], unsigned(it / STAGES - 1) & 1u);
-                    if (!ok) break;
-                    nk_mbar_expect_tx(&full_bar[stage], bytes);
-                    nk_tma_load(a_base + size_t(stage) * C::A_BYTES, &mapA, &full_bar[stage], p.nd, ca);
-                    nk_tma_load(e_base + size_t(stage) * C::E_BYTES, &mapE, &full_bar[stage], p.nd, ce);
-                    issued++;
+                    if constexpr (COUPLED) {   // rings of equal depth: one barrier pair per slot serves both tiles
+                        if (it >= NA) ok = wait_or_abort(&empty_a[sa], unsigned(it / NA - 1) & 1u);
+                        if (!ok) break;
+                        nk_mbar_expect_tx(&full_a[sa], bytes_a + bytes_e);
+                        nk_tma_load(a_base + size_t(sa) * C::A_BYTES, &mapA, &full_a[sa], p.nd, ca);
+                        nk_tma_load(e_base + size_t(se) * C::E_BYTES, &mapE, &full_a[sa], p.nd, ce);
+                        issued_a++;
+                    } else {
+                        // the error slot comes free first (its readers copy it into registers when they start the unit before)
+                        if (it >= NE) ok = wait_or_abort(&empty_e[se], unsigned(it / NE - 1) & 1u);
+                        if (!ok) break;
+                        nk_mbar_expect_tx(&full_e[se], bytes_e);
+                        nk_tma_load(e_base + size_t(se) * C::E_BYTES, &mapE, &full_e[se], p.nd, ce);
+                        issued_e++;
+                        if (it >= NA) ok = wait_or_abort(&empty_a[sa], unsigned(it / NA - 1) & 1u);
+                        if (!ok) break;
+                        nk_mbar_expect_tx(&full_a[sa], bytes_a);
+                        nk_tma_load(a_base + size_t(sa) * C::A_BYTES, &mapA, &full_a[sa], p.nd, ca);
+                        issued_a++;
+                    }
                     if (++tx == p.tilesX) {
                         tx = 0;
                         if (++ty == p.tilesY) {
@@ -134,9 +157,10 @@ __global__ void __launch_bounds__(288) nk_conv_wgrad_kernel(T* __restrict__ part
                 }
                 if (!ok || *abort_word) {
                     // requested copies may still be landing in this CTA's shared memory: wait for the last ones (bounded)
-                    for (int64_t j = (issued > STAGES ? issued - STAGES : 0); j < issued; j++) {
-                        nk_mbar_wait_bounded(&full_bar[j % STAGES], unsigned(j / STAGES) & 1u, NK_WAIT_LIMIT_NS, nullptr);
-                    }
+                    for (int64_t j = (issued_a > NA ? issued_a - NA : 0); j < issued_a; j++)
+                        nk_mbar_wait_bounded(&full_a[j % NA], unsigned(j / NA) & 1u, NK_WAIT_LIMIT_NS, nullptr);
+                    for (int64_t j = (issued_e > NE ? issued_e - NE : 0); j < issued_e; j++)
+                        nk_mbar_wait_bounded(&full_e[j % NE], unsigned(j / NE) & 1u, NK_WAIT_LIMIT_NS, nullptr);
                 }
             }
         }
@@ -144,12 +168,12 @@ __global__ void __launch_bounds__(288) nk_conv_wgrad_kernel(T* __restrict__ part
         // when the maps have no row dim only row 0 of each tile is real: rows beyond it must not contribute
         const int rows = p.has_y ? RH : (warp == 0 ? 1 : 0);
         for (int64_t it = 0; it < n_it; it++) {
-            const int stage = int(it % STAGES);
-            if (!wait_or_abort(&full_bar[stage], unsigned(it / STAGES) & 1u)) break;
-            if (rows > 0) {
-                const T* at = reinterpret_cast<const T*>(a_base + size_t(stage) * C::A_BYTES) + (warp * RH) * SW + lane * CW;
-                const T* et = reinterpret_cast<const T*>(e_base + size_t(stage) * C::E_BYTES) + (warp * RH) * TW + lane * CW;
-                T ev[RH][CW];
+            const int sa = int(it % NA), se = int(it % NE);
+            // this thread's error values into registers, and the error slot goes back to the producer
+            if (!wait_or_abort(COUPLED ? &full_a[sa] : &full_e[se], unsigned(it / NE) & 1u)) break;
+            T ev[RH][CW];
+            auto load_ev = [&]() {
+                const T* et = reinterpret_cast<const T*>(e_base + size_t(se) * C::E_BYTES) + (warp * RH) * TW + lane * CW;
 #pragma unroll
                 for (int i = 0; i < RH; i++) {
                     if (i < rows) {
@@ -160,6 +184,16 @@ __global__ void __launch_bounds__(288) nk_conv_wgrad_kernel(T* __restrict__ part
                         for (int x = 0; x < CW; x++) ev[i][x] = T(0);
                     }
                 }
+            };
+            if constexpr (!COUPLED) {
+                load_ev();
+                __syncwarp();
+                if (lane == 0) nk_mbar_arrive(&empty_e[se]);
+                if (!wait_or_abort(&full_a[sa], unsigned(it / NA) & 1u)) break;
+            }
+            if (rows > 0) {
+                if constexpr (COUPLED) load_ev();   // (inside the branch: the row loads below are scheduled together with these)
+                const T* at = reinterpret_cast<const T*>(a_base + size_t(sa) * C::A_BYTES) + (warp * RH) * SW + lane * CW;
 #pragma unroll
                 for (int j = 0; j < RH + KH - 1; j++) {
                     if (!p.has_y && j > 0) break;
@@ -182,7 +216,7 @@ __global__ void __launch_bounds__(288) nk_conv_wgrad_kernel(T* __restrict__ part
                 }
             }
             __syncwarp();
-            if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
+            if (lane == 0) nk_mbar_arrive(&empty_a[sa]);
         }
     }
     __syncthreads();
