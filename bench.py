@@ -177,8 +177,19 @@ def bind_to_gpu_numa_node(gpu_index: int):
         bus = bus.lower()
         if len(bus.split(":")[0]) == 8:
             bus = bus[4:]
+        handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
         with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
             node = int(f.read().strip())
+        if node < 0:
+            # the PCI device carries no node (virtualised topology): ask the driver which host memory nodes are closest
+            try:
+                n_nodes = len([d for d in os.listdir("/sys/devices/system/node") if d.startswith("node") and d[4:].isdigit()])
+                words = pynvml.nvmlDeviceGetMemoryAffinity(handle, max(1, (n_nodes + 63) // 64), pynvml.NVML_AFFINITY_SCOPE_NODE)
+                nodes = [i for i in range(n_nodes) if (words[i // 64] >> (i % 64)) & 1]
+                if len(nodes) == 1 and n_nodes > 1:
+                    node = nodes[0]
+            except Exception:  # noqa: BLE001
+                pass
         if node < 0:
             return "numa node unknown (-1)"
         with open(f"/sys/devices/system/node/node{node}/cpulist") as f:

@@ -145,7 +145,7 @@ def _cfg3_ops(e: Env, n, m, kk, reps):
     r = {}
     total = 0.0
     for name, fn, nbytes in steps:
-        ms = _time(dev, lambda i, fn=fn: L.check(fn(i), ctx), 1, reps)
+        ms = _time(dev, lambda i, fn=fn: L.check(fn(i), ctx), 3, reps)
         if name != "relu":
             total += ms
         r[name] = _row(ms, nbytes, e.hbm, dev)
@@ -194,8 +194,8 @@ def sec_cfg3_fused(e: Env):
             bufs = (C.c_void_p * 2)(a.buf, b.buf)
             cfgs = (C.POINTER(C.c_int32) * 2)(pa, pb)
             nbytes = 4.0 * (N + n * kk + m * kk)
-            ms2 = _time(dev, lambda i: L.check(L.lib.nk_fused_run(ctx, h2, 3, y.buf, po, bufs, cfgs), ctx), 1, 3)
-            ms = _time(dev, lambda i: L.check(L.lib.nk_fused_run(ctx, h, 3, y.buf, po, bufs, cfgs), ctx), 1, 3)
+            ms2 = _time(dev, lambda i: L.check(L.lib.nk_fused_run(ctx, h2, 3, y.buf, po, bufs, cfgs), ctx), 3, 5)
+            ms = _time(dev, lambda i: L.check(L.lib.nk_fused_run(ctx, h, 3, y.buf, po, bufs, cfgs), ctx), 3, 5)
             r[name] = {"tanh_affine_ms": ms, "tanh_affine_gbs": nbytes / (ms * 1e-3) / 1e9, "tanh_affine_frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / e.hbm,
                        "affine_only_ms": ms2, "affine_only_gbs": nbytes / (ms2 * 1e-3) / 1e9, "affine_only_frac_of_hbm_peak": nbytes / (ms2 * 1e-3) / 1e9 / e.hbm,
                        "kernel": dev.last_kernel()}
@@ -222,12 +222,12 @@ def sec_contraction(e: Env):
             O = _Buf(dev, npdt, n * n)
             c1, p1 = _cfg([n, n, 1]); c2, p2 = _cfg([1, n, n]); c0, p0 = _cfg([n, 1, n])
             flops = 2.0 * n * n * n
-            ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, dt, 3, O.buf, p0, A.buf, p1, Bm.buf, p2, -1), ctx), 2, 5)
+            ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, dt, 3, O.buf, p0, A.buf, p1, Bm.buf, p2, -1), ctx), 3, 5)
             r[name] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "kernel": dev.last_kernel(),
                        "frac_of_measured_fma_peak": flops / (ms * 1e-3) / 1e12 / e.fma_peaks[fma_peak]}
             if not e.small and dt == L.NK_F32:   # the FMA family on the same call, for scale
                 dev.set_conv_path(L.NK_CONV_GEMM)
-                ms_f = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, dt, 3, O.buf, p0, A.buf, p1, Bm.buf, p2, -1), ctx), 1, 3)
+                ms_f = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, dt, 3, O.buf, p0, A.buf, p1, Bm.buf, p2, -1), ctx), 3, 3)
                 r[name]["fma_family_ms"] = ms_f
                 r[name]["fma_family_kernel"] = dev.last_kernel()
                 dev.set_conv_path(L.NK_CONV_AUTO)
@@ -277,9 +277,9 @@ def sec_cfg5_gradients(e: Env):
         flops = 2.0 * Bn * OH * OW * Cn * KH * KH
         nbytes = 4.0 * (Bn * Cn * H * W + Bn * OH * OW + Cn * KH * KH)
         r = {}
-        ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, gimg.buf, pi_, ker.buf, pkk, err.buf, pe, 0), ctx), 2, 5)
+        ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, gimg.buf, pi_, ker.buf, pkk, err.buf, pe, 0), ctx), 3, 10)
         r["grad_image"] = _row(ms, nbytes, e.hbm, dev, tflops=flops / (ms * 1e-3) / 1e12, frac_of_measured_fma_peak=flops / (ms * 1e-3) / 1e12 / e.fma_peaks["fp32"])
-        ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, gker.buf, pkk, img.buf, pi_, err.buf, pe, 0), ctx), 2, 5)
+        ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F32, 4, gker.buf, pkk, img.buf, pi_, err.buf, pe, 0), ctx), 3, 10)
         r["grad_kernel"] = _row(ms, nbytes, e.hbm, dev, tflops=flops / (ms * 1e-3) / 1e12, frac_of_measured_fma_peak=flops / (ms * 1e-3) / 1e12 / e.fma_peaks["fp32"])
         for bb in (img, err, ker, gimg, gker): bb.free()
         return {"cfg5_gradients_quarter_height" if e.small else "cfg5_gradients": r}
@@ -299,9 +299,9 @@ def sec_cfg4(e: Env):
     ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F64, 3, yb.buf, py, v.buf, pv, k.buf, pk, -1), ctx), 3, 10)
     r["forward"] = {"ms": ms, "gflops": flops / (ms * 1e-3) / 1e9, "kernel": dev.last_kernel()}
     # gradients for error = y itself (any error tensor does): XConvRight(error, other, zeros) -> (drain, other, error), d = 0
-    ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F64, 3, gv.buf, pv, k.buf, pk, yb.buf, py, 0), ctx), 2, 5)
+    ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F64, 3, gv.buf, pv, k.buf, pk, yb.buf, py, 0), ctx), 3, 10)
     r["grad_volume"] = {"ms": ms, "gflops": flops / (ms * 1e-3) / 1e9, "kernel": dev.last_kernel()}
-    ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F64, 3, gk.buf, pk, v.buf, pv, yb.buf, py, 0), ctx), 2, 5)
+    ms = _time(dev, lambda i: L.check(L.lib.nk_conv(ctx, L.NK_F64, 3, gk.buf, pk, v.buf, pv, yb.buf, py, 0), ctx), 3, 10)
     r["grad_kernel"] = {"ms": ms, "gflops": flops / (ms * 1e-3) / 1e9, "kernel": dev.last_kernel()}
     for v_ in r.values():
         v_["frac_of_fp64_fma_peak"] = v_["gflops"] / 1e3 / e.fma_peaks["fp64"]

@@ -423,7 +423,10 @@ int nk_conv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_
         // (only a short launch -- under two waves of tall tiles -- is dominated by that start-up; measured with 7 peers
         // storing into one owner: 0.198 ms against 0.227 ms; with more waves the tall tiles' efficiency wins again)
         // (with a tile per resident slot or more the launch is a balanced persistent walk: no wave rounding to compare)
-        const bool tall = p.OH >= 128 && (tiles8 >= slots || cost8 <= cost4) && !(p.remote_out && tiles8 < 2 * slots);
+        bool tall = p.OH >= 128 && (tiles8 >= slots || cost8 <= cost4) && !(p.remote_out && tiles8 < 2 * slots);
+        static const int force_rows = [] { const char* e = getenv("NK_TILED_ROWS"); return e ? atoi(e) : 0; }();   // tuning: 8 or 4
+        if (force_rows == 8) tall = true;
+        if (force_rows == 4) tall = false;
         if (tall) st = f32 ? nk_tiled_dispatch_f32_tma8(ctx, int(KH), int(KW), of, If, Kf, p, &img) : nk_tiled_dispatch_f64_tma8(ctx, int(KH), int(KW), od, Id, Kd, p, &img);
         if (st == -1) st = f32 ? nk_tiled_dispatch_f32_tma4(ctx, int(KH), int(KW), of, If, Kf, p, &img) : nk_tiled_dispatch_f64_tma4(ctx, int(KH), int(KW), od, Id, Kd, p, &img);
         if (st != -1) family = NK_CONV_TMA;
