@@ -60,7 +60,8 @@ typedef enum {
 } nk_fun;
 
 /* Which convolution kernel family a call is routed to. AUTO picks from the views; the others force a
- * family (NK_ERR_UNSUPPORTED if the views do not qualify) -- a testing/measurement knob. */
+ * family (NK_ERR_UNSUPPORTED if the views do not qualify) -- a testing/measurement knob. Forcing NK_CONV_TMA also
+ * selects the persistent tile walk wherever it applies (AUTO keeps one tile per CTA below 6 tiles per resident CTA). */
 typedef enum { NK_CONV_AUTO = 0, NK_CONV_GENERIC = 1, NK_CONV_TILED = 2, NK_CONV_TMA = 3, NK_CONV_GEMM = 4, NK_CONV_TC = 5 } nk_conv_path;
 
 typedef struct {

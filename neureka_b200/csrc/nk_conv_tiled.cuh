@@ -133,8 +133,9 @@ struct TiledCfg {
     }
 };
 
-// The tensor maps of a launch: entry r - 1 has a box of 8 * r + KH - 1 rows (r = rows per warp of a chunk: 2, 4 or 8).
-struct TmapSet { CUtensorMap m[8]; };
+// The tensor maps of a launch, one per rows-per-warp value r of a chunk (2, 4, 8 -> entry 0, 1, 2): a box of 8 r + KH - 1 rows.
+struct TmapSet { CUtensorMap m[3]; };
+__host__ __device__ constexpr int nk_tmap_slot(int r) { return r >= 8 ? 2 : (r >= 4 ? 1 : 0); }
 template <int N> struct NkRows { static constexpr int value = N; };
 // Variants of the persistent TMA kernel: chunks decoded by the compute warps / taken from the producer's ring / weight loop
 #define NK_TILED_PLAIN 0
@@ -275,7 +276,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
             for (int it = 0; it < STAGES && it < n_it; it++) {
                 int cc[4];
                 chan_coords(c_begin + it, cc);
-                tma_fire(it, chunk_bytes(rh_cur), &tmaps.m[rh_cur - 1], cc[0] + tb.x, cc[1] + tb.y, cc[2] + tb.z, cc[3] + tb.w);
+                tma_fire(it, chunk_bytes(rh_cur), &tmaps.m[nk_tmap_slot(rh_cur)], cc[0] + tb.x, cc[1] + tb.y, cc[2] + tb.z, cc[3] + tb.w);
             }
         };
         if (!p.persist) {
@@ -528,7 +529,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                 bool announce = false;      // a new chunk's info still has to go into the ring (after the stage came free)
                 int4 tb = p.persist && my_waves == 0 ? tail_tab[2] : tile_coords();
                 unsigned cur_bytes = chunk_bytes(rh_cur);
-                const CUtensorMap* cur_map = &tmaps.m[rh_cur - 1];
+                const CUtensorMap* cur_map = &tmaps.m[nk_tmap_slot(rh_cur)];
                 int c = c_begin + issued;   // the first loads of the first chunk were requested in the prologue
                 while (ok) {
                     if (c >= c_end) {
@@ -559,7 +560,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                             place(e[0], e[1]);
                             tb = e[2];
                             cur_bytes = chunk_bytes(rh_cur);
-                            cur_map = &tmaps.m[rh_cur - 1];
+                            cur_map = &tmaps.m[nk_tmap_slot(rh_cur)];
                         }
                         c = c_begin;
                         announce = true;
@@ -845,9 +846,16 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     if (TMA) {
         if (C::SW > 256 || C::SH > 256) return -1;
         p.persist = balanced() ? 1 : 0;
+        // Few tiles per resident CTA slot and the same weights everywhere: one tile per CTA, dealt by the hardware as CTAs
+        // retire, balances better than any fixed assignment and skips the walk's set-up. Measured on B200 (F32 5x5, 32
+        // channels; persistent / one tile per CTA): 1.7 tiles per slot 0.162 / 0.155 ms, 3.5: 0.288 / 0.268 ms, 6.9:
+        // 0.508 / 0.517 ms, 13.8: 0.993 / 1.007 ms; F64 7x7 at 3.3: 80 / 75.5 us. The walk starts at 6 tiles per slot.
+        static const int persist_min_x10 = [] { const char* e = getenv("NK_TILED_PERSIST_MIN_X10"); return e ? atoi(e) : 60; }();
+        // (a call that forces the TMA family -- the testing / measurement knob -- walks wherever the walk applies)
+        if (p.persist && ctx->conv_path != NK_CONV_TMA && wsets == 1 && !p.wloop && tiles * 10 < slots * persist_min_x10) p.persist = 0;
         // persistent: one map per rows-per-warp value 2, 4, (8) (box of 8 r + KH - 1 rows); otherwise only the full tile's map
         for (int r = p.persist ? 2 : RH; r <= RH; r *= 2) {
-            int st = nk_tma_encode(ctx, sizeof(T) == 4 ? NK_F32 : NK_F64, *img, C::SW, 8 * r + KH - 1, p.has_y != 0, &tmaps.m[r - 1]);
+            int st = nk_tma_encode(ctx, sizeof(T) == 4 ? NK_F32 : NK_F64, *img, C::SW, 8 * r + KH - 1, p.has_y != 0, &tmaps.m[nk_tmap_slot(r)]);
             if (st == -1) return -1;
             if (st) return st;
         }

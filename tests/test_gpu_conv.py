@@ -189,16 +189,18 @@ def test_stencil_shapes_all_kernel_families(device, oracle, dt, case):
 
 @pytest.mark.parametrize("dt", [np.float32, np.float64])
 @pytest.mark.parametrize("case", [
-    ([3, 6, 333, 700], [1, 6, 5, 5]),      # 108 tiles: no whole wave, every tile cut into groups of 8 rows
-    ([16, 9, 500, 300], [1, 9, 3, 3]),     # 384 tiles on ~300 CTAs: one whole wave, then the rest in 8-row groups
+    ([3, 6, 333, 700], [1, 6, 5, 5]),      # 108 tiles: no whole wave, every tile cut into units of 16 rows
+    ([16, 9, 500, 300], [1, 9, 3, 3]),     # 384 tiles on ~300 CTAs: one whole wave, then the rest in 16-row units
+    ([33, 8, 500, 300], [1, 8, 3, 3]),     # F32: 792 tiles, two whole waves, the remaining 200 dealt whole (more than half a tile per CTA)
     ([5, 70, 252], [1, 7, 7]),             # one channel per chunk: the ring-fed kernel
     ([40, 2, 90, 140], [1, 2, 5, 3]),      # many short strips (86 rows each)
 ])
 def test_balanced_walk_gives_the_same_bits_as_one_tile_per_cta(device, oracle, dt, case):
-    """The persistent TMA launch runs whole waves of tiles and deals the remaining tiles to the CTAs in groups of 8 rows,
-    walked in chunks of 1..RH rows per warp; the additions into one output still come in the same order (channel,
-    window row, window column), so the result must equal the one-tile-per-CTA LDGSTS family bit for bit, whatever the
-    tile count -- for the forward call and for the image gradient (the same kernel on a padded, flipped problem)."""
+    """The persistent TMA launch (forced here; AUTO walks only from 6 tiles per resident CTA on) runs whole waves of tiles
+    and deals the remaining tiles to the CTAs in units of 16 rows, walked in chunks of 2, 4 or 8 rows per warp; the additions
+    into one output still come in the same order (channel, window row, window column), so the result must equal the
+    one-tile-per-CTA LDGSTS family bit for bit, whatever the tile count -- for the forward call and for the image gradient
+    (the same kernel on a padded, flipped problem, weight-loop variant)."""
     rng = np.random.default_rng(41)
     sa, sb = case
     so = [abs(x - y) + 1 for x, y in zip(sa, sb)]
