@@ -8,6 +8,7 @@ of the same kernels that holds a few GB at most (still far larger than L2) -- th
 needs. Everything goes through the C ABI with device-resident buffers and is timed with the context's CUDA events
 after warm-up launches.
 
+  cfg5_group  config 5 through the in-process device group on every visible GPU (only with --only cfg5_group)
   cfg1  F32 [256,256] x [5,5]                  -> latency of one launch (the problem lives in L2: latency-bound)
   cfg2  F32 [64,512,512] x [64,3,3]            -> GB/s of algorithmic bytes, inputs rotated over 4 copies (> L2 in total)
   cfg3  F32 tanh(a*b+b), a [n,1,1024], b [1,m,1024] at n*m*1024 = 2^31 outputs and at the full 2^33 (which cannot exist
@@ -309,10 +310,67 @@ def sec_cfg4(e: Env):
     return {"cfg4_conv3d_f64_128_k7": r}
 
 
+def sec_cfg5_group(e: Env):
+    """cfg5's forward pass through the in-process device group (nk_conv_sharded) on every visible GPU: one host thread,
+    one context per GPU, slabs resident, result assembled in the first GPU's memory. Needs two GPUs or more."""
+    from neureka_b200.device import CudaDevice
+    from neureka_b200.sharding import plan_slabs
+    n = CudaDevice.count()
+    if n < 2:
+        return {"cfg5_in_process_group": {"skipped": "one GPU visible"}}
+    Bn, Cn, H, W, KH = 8, 32, 2048, 2048, 5
+    grp = C.c_void_p()
+    L.check(L.lib.nk_group_open((C.c_int32 * n)(*range(n)), n, C.byref(grp)))
+    try:
+        ctxs = []
+        for i in range(n):
+            c = C.c_void_p()
+            L.check(L.lib.nk_group_ctx(grp, i, C.byref(c)))
+            ctxs.append(c)
+        slabs = plan_slabs(H - KH + 1, n, KH - 1)
+        k_h = np.ascontiguousarray(B.cfg5_kernel(), dtype=np.float32)
+        sb, kb = [], []
+        for i, s in enumerate(slabs):
+            rows = s.in_hi - s.in_lo
+            b_, k_ = C.c_void_p(), C.c_void_p()
+            L.check(L.lib.nk_alloc(ctxs[i], L.NK_F32, Bn * Cn * rows * W, C.byref(b_)), ctxs[i])
+            L.check(L.lib.nk_fill(ctxs[i], b_, C.c_double(0.5), 0, Bn * Cn * rows * W), ctxs[i])
+            L.check(L.lib.nk_alloc(ctxs[i], L.NK_F32, k_h.size, C.byref(k_)), ctxs[i])
+            L.check(L.lib.nk_write(ctxs[i], k_, k_h.ctypes.data_as(C.c_void_p), 0, 0, k_h.size), ctxs[i])
+            sb.append(b_); kb.append(k_)
+        n_out = Bn * (H - KH + 1) * (W - KH + 1)
+        out = C.c_void_p()
+        L.check(L.lib.nk_alloc(ctxs[0], L.NK_F32, n_out, C.byref(out)), ctxs[0])
+        ish, ksh = (C.c_int64 * 4)(Bn, Cn, H, W), (C.c_int64 * 4)(1, Cn, KH, KH)
+        sl, kl = (C.c_void_p * n)(*sb), (C.c_void_p * n)(*kb)
+        run = lambda: L.check(L.lib.nk_conv_sharded(grp, L.NK_F32, 4, ish, ksh, 2, sl, kl, out), ctxs[0])
+        for _ in range(3):
+            run()
+        for c in ctxs:
+            L.check(L.lib.nk_sync(c), c)
+        reps = 20
+        L.check(L.lib.nk_timer_begin(ctxs[0]), ctxs[0])   # the first member's stream waits for every push: its timer sees whole passes
+        for _ in range(reps):
+            run()
+        ms = C.c_float(0)
+        L.check(L.lib.nk_timer_end(ctxs[0], C.byref(ms)), ctxs[0])
+        for c in ctxs:
+            L.check(L.lib.nk_sync(c), c)
+        ms = float(ms.value) / reps
+        flops = 2.0 * n_out * Cn * KH * KH
+        for i in range(n):
+            L.lib.nk_free(ctxs[i], sb[i]); L.lib.nk_free(ctxs[i], kb[i])
+        L.lib.nk_free(ctxs[0], out)
+        return {"cfg5_in_process_group": {"n_gpus": n, "ms_per_pass": ms, "tflops_total": flops / (ms * 1e-3) / 1e12,
+                                          "note": "one host thread, nk_conv_sharded; pushes of pass k overlap pass k+1"}}
+    finally:
+        L.check(L.lib.nk_group_close(grp))
+
+
 SECTIONS = {
     "fma_peaks": sec_fma_peaks, "cfg1": sec_cfg1, "cfg2": sec_cfg2, "cfg3": sec_cfg3, "cfg3_fused": sec_cfg3_fused,
     "cfg3_full": sec_cfg3_full, "contraction": sec_contraction, "cfg5_slabs": sec_cfg5_slabs,
-    "cfg5_gradients": sec_cfg5_gradients, "cfg4": sec_cfg4,
+    "cfg5_gradients": sec_cfg5_gradients, "cfg4": sec_cfg4, "cfg5_group": sec_cfg5_group,
 }
 
 
@@ -321,6 +379,8 @@ def run_extra(dev, hbm_peak_gbs: float, only=None, small: bool = False) -> dict:
     out = {}
     for name, fn in SECTIONS.items():
         if only and name not in only:
+            continue
+        if not only and name == "cfg5_group":   # uses every visible GPU: only when asked for by name
             continue
         out.update(fn(e))
     return out
