@@ -174,4 +174,68 @@ public final class CudaKernels
         } catch ( RuntimeException e ) { throw e; } catch ( Throwable t ) { throw new IllegalStateException(t); }
         return c;
     }
+
+    // ---- entry points added after the first glue: Min / Max, fused backward, several GPUs in one JVM ----------------------
+
+    /**
+     *  Min / Max as the reference's CLReduce / CPUReduce deliver it (operations/other/internal/CPUReduce.java:72-140): the flat
+     *  index of the extreme element, lowest index among equals, as a Tensor&lt;Integer&gt; of one item living on the device.
+     */
+    static Tensor<Integer> argReduce( CudaDevice dev, Tensor<?> in, boolean max ) {
+        Tensor<Integer> out = Tensor.of( Integer.class, neureka.Shape.of(1), 0 ).mut().setIsIntermediate(true);
+        out.mut().setIsVirtual(false);
+        dev.store( out );
+        try ( Arena a = Arena.ofConfined() ) {
+            NeurekaCuda.check((int) NeurekaCuda.ARG_REDUCE.invokeExact(dev.ctx, max ? 1 : 0, CudaDevice.typeOf(in.getItemType()), in.rank(),
+                    dev.bufOf(in), NeurekaCuda.cfg(a, in.getNDConf().asInlineArray()), dev.bufOf(out), 0L), dev.ctx);
+        } catch ( RuntimeException e ) { throw e; } catch ( Throwable t ) { throw new IllegalStateException(t); }
+        return out;
+    }
+
+    /**
+     *  Backward of a fused expression w.r.t. input `target`: one kernel recomputes the expression, multiplies `error`
+     *  through it and sums over the dims `target` is broadcast along. `terms` is the statement list of the reverse pass
+     *  ("term[0] = ...; ..." over x0..x5 and e, one term per occurrence of the target) -- built from the Function tree the way
+     *  neureka_b200/functions.py:fused_gradient_terms_of does; its Java twin is not written yet.
+     */
+    static Tensor<?> runFusedGrad( CudaDevice dev, String terms, int leaves, int target, Tensor<?> error, Tensor<?>[] in ) {
+        int rank = in[0].rank(), arity = in.length;
+        Tensor<?> grad = Tensor.of( in[target].getItemType(), in[target].shape(), 0 ).mut().setIsIntermediate(true);
+        grad.mut().setIsVirtual(false);
+        dev.store( (Tensor) grad );
+        int type = CudaDevice.typeOf( in[target].getItemType() );
+        try ( Arena a = Arena.ofConfined() ) {
+            MemorySegment handle = FUSED.computeIfAbsent( "grad:" + type + ":" + arity + ":" + target + ":" + terms, key -> {
+                try ( Arena b = Arena.ofConfined() ) {
+                    MemorySegment slot = b.allocate(ValueLayout.ADDRESS);
+                    NeurekaCuda.check((int) NeurekaCuda.FUSED_COMPILE_GRAD.invokeExact(dev.ctx, type, arity, target, leaves, b.allocateFrom(terms), slot), dev.ctx);
+                    return slot.get(ValueLayout.ADDRESS, 0);
+                } catch ( RuntimeException e ) { throw e; } catch ( Throwable t ) { throw new IllegalStateException(t); }
+            });
+            MemorySegment bufs = a.allocate(ValueLayout.ADDRESS, arity), cfgs = a.allocate(ValueLayout.ADDRESS, arity);
+            for ( int j = 0; j < arity; j++ ) {
+                bufs.setAtIndex(ValueLayout.ADDRESS, j, dev.bufOf(in[j]));
+                cfgs.setAtIndex(ValueLayout.ADDRESS, j, NeurekaCuda.cfg(a, in[j].getNDConf().asInlineArray()));
+            }
+            NeurekaCuda.check((int) NeurekaCuda.FUSED_RUN_GRAD.invokeExact(dev.ctx, handle, rank,
+                    dev.bufOf(grad), NeurekaCuda.cfg(a, grad.getNDConf().asInlineArray()),
+                    dev.bufOf(error), NeurekaCuda.cfg(a, error.getNDConf().asInlineArray()), bufs, cfgs), dev.ctx);
+        } catch ( RuntimeException e ) { throw e; } catch ( Throwable t ) { throw new IllegalStateException(t); }
+        return grad;
+    }
+
+    /**
+     *  Forward convolution cut along output dim `dim` over the members of a device group (nk_group_open): slabs[g] / kernels[g]
+     *  are the native buffers of member g's input slab and kernel copy, `out` the full result on the first member's device.
+     *  The slab extents come from nk_group_plan_slabs (NeurekaCuda.GROUP_PLAN).
+     */
+    static void convSharded( MemorySegment group, MemorySegment firstCtx, int type, long[] imageShape, long[] kernelShape, int dim,
+                             MemorySegment[] slabs, MemorySegment[] kernels, MemorySegment out ) {
+        try ( Arena a = Arena.ofConfined() ) {
+            MemorySegment sl = a.allocate(ValueLayout.ADDRESS, slabs.length), kl = a.allocate(ValueLayout.ADDRESS, kernels.length);
+            for ( int g = 0; g < slabs.length; g++ ) { sl.setAtIndex(ValueLayout.ADDRESS, g, slabs[g]); kl.setAtIndex(ValueLayout.ADDRESS, g, kernels[g]); }
+            NeurekaCuda.check((int) NeurekaCuda.CONV_SHARDED.invokeExact(group, type, imageShape.length,
+                    a.allocateFrom(ValueLayout.JAVA_LONG, imageShape), a.allocateFrom(ValueLayout.JAVA_LONG, kernelShape), dim, sl, kl, out), firstCtx);
+        } catch ( RuntimeException e ) { throw e; } catch ( Throwable t ) { throw new IllegalStateException(t); }
+    }
 }

@@ -43,6 +43,9 @@ public final class NeurekaCuda
     static final MethodHandle FILL_FUN     = h("nk_fill_fun",     FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, JAVA_DOUBLE, JAVA_INT));
     static final MethodHandle SUM          = h("nk_sum",          FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, JAVA_LONG));
 
+    // Min / Max: the flat index of the extreme element, written as one int into a device buffer (CLReduce's contract)
+    static final MethodHandle ARG_REDUCE   = h("nk_arg_reduce",   FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, JAVA_LONG));
+
     static final MethodHandle FUSED_COMPILE = h("nk_fused_compile", FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS));
     static final MethodHandle FUSED_RUN     = h("nk_fused_run",     FunctionDescriptor.of(JAVA_INT, ADDRESS, ADDRESS, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS));
     static final MethodHandle FUSED_FREE    = h("nk_fused_free",    FunctionDescriptor.of(JAVA_INT, ADDRESS));
