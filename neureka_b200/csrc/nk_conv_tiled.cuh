@@ -41,7 +41,9 @@
 #pragma once
 #include <cuda.h>
 #include <cooperative_groups.h>
+#include <mutex>
 #include <type_traits>
+#include <vector>
 #include "nk_conv_plan.h"
 #include "nk_ptx.cuh"
 
@@ -782,6 +784,36 @@ struct TmaImage {
 };
 int nk_tma_encode(nk_ctx* ctx, int dtype, const TmaImage& img, int box_w, int box_h, bool has_y, CUtensorMap* out);
 
+// CTAs of `kern` resident per SM with `smem` bytes of dynamic shared memory, after allowing the kernel that much. Both runtime
+// calls are made once per (kernel, device, size): they cost microseconds each, which is most of a launch for problems that
+// live in L2.
+inline int nk_tiled_occupancy(nk_ctx* ctx, const void* kern, int threads, size_t smem, int* per_sm) {
+    struct Entry { const void* kern; int device; size_t smem; int per_sm; };   // per_sm < 0: the largest size allowed so far
+    static std::mutex mu;
+    static std::vector<Entry> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    Entry* allowed = nullptr;
+    for (Entry& e : cache) {
+        if (e.kern != kern || e.device != ctx->device) continue;
+        if (e.per_sm < 0) allowed = &e;
+        else if (e.smem == smem) { *per_sm = e.per_sm; return 0; }
+    }
+    if (!allowed || allowed->smem < smem) {   // the attribute is a maximum: only ever raised
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel)");
+        if (allowed) allowed->smem = smem;
+        else cache.push_back(Entry{kern, ctx->device, smem, -1});
+    }
+    int n = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem) != cudaSuccess || n < 1) {
+        cudaGetLastError();
+        n = 1;
+    }
+    *per_sm = n;
+    cache.push_back(Entry{kern, ctx->device, smem, n});
+    return 0;
+}
+
 template <class T, int KH, int KW, int RH, bool TMA>
 int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, const TmaImage* img) {
     using C = TiledCfg<T, KH, KW, RH>;
@@ -803,13 +835,9 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
     auto configure = [&](int w) -> int {
         smem = C::smem_bytes(p.NQ, w);
         if (smem > size_t(ctx->prop.sharedMemPerBlockOptin)) return -1;   // caller falls back to another family
-        cudaError_t e = cudaFuncSetAttribute(nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel)");
         int per_sm = 1;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, nk_conv_tiled_kernel<T, KH, KW, RH, TMA>, TMA ? 288 : 256, smem) != cudaSuccess || per_sm < 1) {
-            cudaGetLastError();
-            per_sm = 1;
-        }
+        const int ost = nk_tiled_occupancy(ctx, reinterpret_cast<const void*>(nk_conv_tiled_kernel<T, KH, KW, RH, TMA>), TMA ? 288 : 256, smem, &per_sm);
+        if (ost) return ost;
         slots = int64_t(ctx->prop.multiProcessorCount) * per_sm;
         // channel split: only when the tiles alone cannot fill the machine and each part keeps >= 4 channels; the
         // CTA count stays within one resident wave (a second, nearly empty wave would double the time)
@@ -868,13 +896,9 @@ int nk_launch_tiled(nk_ctx* ctx, T* out, const T* I, const T* K, TiledPlan& p, c
                 if (ring || p.wloop) {
                     // these walks run another variant of the kernel: the resident wave is what THAT variant's registers allow
                     auto kern = ring ? nk_conv_tiled_kernel<T, KH, KW, RH, true, NK_TILED_RING> : nk_conv_tiled_kernel<T, KH, KW, RH, true, NK_TILED_WLOOP>;
-                    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-                    if (e != cudaSuccess) return nk_cuda_fail(ctx, e, "cudaFuncSetAttribute(nk_conv_tiled_kernel, variant)");
                     int per_sm = 1;
-                    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 288, smem) != cudaSuccess || per_sm < 1) {
-                        cudaGetLastError();
-                        per_sm = 1;
-                    }
+                    const int ost = nk_tiled_occupancy(ctx, reinterpret_cast<const void*>(kern), 288, smem, &per_sm);
+                    if (ost) return ost;
                     slots = int64_t(ctx->prop.multiProcessorCount) * per_sm;
                 }
             }
