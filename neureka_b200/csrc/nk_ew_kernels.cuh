@@ -97,6 +97,37 @@ template <class T, int OP> struct ScalarFix {
     __device__ __forceinline__ T operator()(T a, T) const { return nkf::bin<2>(OP, -1, a, value); }
 };
 
+// Functors whose function has a straight-line form for all but a few inputs: the kernels evaluate fast() for every element
+// of a vector first and repair the rare ones afterwards (see tanh32_fast in nk_scalarfun.cuh for why).
+template <class F> struct TwoPhase { static constexpr bool value = false; };
+template <bool DERIVE> struct TwoPhase<UnaryFix<float, NK_FUN_TANH, DERIVE>> {
+    static constexpr bool value = true;
+    static __device__ __forceinline__ float fast(float a) {
+        const float t = nkf::tanh32_fast(a);
+        if (!DERIVE) return t;
+        const double td = double(t);
+        return float(1 - td * td);
+    }
+    static __device__ __forceinline__ bool rare(float a) { return nkf::tanh32_rare(a); }
+};
+// out[k] = f(a[k], b[k]) for the N elements of one vector
+template <class T, int N, int NIN, class F>
+__device__ __forceinline__ void apply_vec(const F& f, const T* a, const T* b, T* o) {
+    if constexpr (TwoPhase<F>::value) {
+        bool any = false;
+#pragma unroll
+        for (int k = 0; k < N; k++) { o[k] = TwoPhase<F>::fast(a[k]); any = any || TwoPhase<F>::rare(a[k]); }
+        if (any) {
+#pragma unroll
+            for (int k = 0; k < N; k++)
+                if (TwoPhase<F>::rare(a[k])) o[k] = f(a[k], T(0));
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < N; k++) o[k] = f(a[k], NIN == 2 ? b[k] : T(0));
+    }
+}
+
 template <class T> struct Vec4 { using type = float4; static constexpr int N = 4; };
 template <> struct Vec4<double> { using type = double2; static constexpr int N = 2; };
 
@@ -112,6 +143,32 @@ __global__ void __launch_bounds__(256) nk_ew_linear_kernel(T* __restrict__ out, 
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     T sa0 = sa ? T(0) : a[0], sb0 = (NIN == 2 && !sb) ? b[0] : T(0);
+    if constexpr (TwoPhase<F>::value && NIN == 1) {
+        // Arithmetic-heavy function (hundreds of instructions per vector): the next trip's vectors are requested before this
+        // trip's arithmetic starts, so their latency passes under it (without this the kernel waited on its loads: ncu,
+        // long_scoreboard 3.7 per issued instruction, FP64 pipe 61 % busy).
+        if (sa) {
+            V cur[2], nxt[2];
+            int64_t i = tid;
+            if (i < nvec) cur[0] = __ldcs(reinterpret_cast<const V*>(a) + i);
+            if (i + stride < nvec) cur[1] = __ldcs(reinterpret_cast<const V*>(a) + i + stride);
+            for (; i < nvec; i += 2 * stride) {
+                const int64_t j = i + stride, ni = i + 2 * stride, nj = ni + stride;
+                if (ni < nvec) nxt[0] = __ldcs(reinterpret_cast<const V*>(a) + ni);
+                if (nj < nvec) nxt[1] = __ldcs(reinterpret_cast<const V*>(a) + nj);
+                T ov[N];
+                apply_vec<T, N, NIN>(f, reinterpret_cast<const T*>(&cur[0]), static_cast<const T*>(nullptr), ov);
+                __stcs(reinterpret_cast<V*>(out) + i, *reinterpret_cast<V*>(ov));
+                if (j < nvec) {
+                    apply_vec<T, N, NIN>(f, reinterpret_cast<const T*>(&cur[1]), static_cast<const T*>(nullptr), ov);
+                    __stcs(reinterpret_cast<V*>(out) + j, *reinterpret_cast<V*>(ov));
+                }
+                cur[0] = nxt[0]; cur[1] = nxt[1];
+            }
+            for (int64_t t = nvec * N + tid; t < n; t += stride) out[t] = f(a[t], T(0));
+            return;
+        }
+    }
     for (int64_t i = tid; i < nvec; i += 2 * stride) {
         const int64_t j = i + stride;
         const bool two = j < nvec;
@@ -130,12 +187,10 @@ __global__ void __launch_bounds__(256) nk_ew_linear_kernel(T* __restrict__ out, 
                 for (int k = 0; k < N; k++) bv[0][k] = bv[1][k] = sb0;
             }
         }
-#pragma unroll
-        for (int k = 0; k < N; k++) ov[k] = f(av[0][k], NIN == 2 ? bv[0][k] : T(0));
+        apply_vec<T, N, NIN>(f, av[0], bv[0], ov);
         __stcs(reinterpret_cast<V*>(out) + i, *reinterpret_cast<V*>(ov));
         if (two) {
-#pragma unroll
-            for (int k = 0; k < N; k++) ov[k] = f(av[1][k], NIN == 2 ? bv[1][k] : T(0));
+            apply_vec<T, N, NIN>(f, av[1], bv[1], ov);
             __stcs(reinterpret_cast<V*>(out) + j, *reinterpret_cast<V*>(ov));
         }
     }
@@ -214,8 +269,7 @@ __global__ void __launch_bounds__(256) nk_ew_rows_kernel(T* __restrict__ out, co
             for (int u = 0; u < RPT; u++) {
                 if (!ok[u]) continue;
                 T ov[N];
-#pragma unroll
-                for (int k = 0; k < N; k++) ov[k] = f(av[u][k], NIN == 2 ? bv[u][k] : T(0));
+                apply_vec<T, N, NIN>(f, av[u], bv[u], ov);
                 __stcs(reinterpret_cast<V*>(out + q0[u]) + c, *reinterpret_cast<V*>(ov));
             }
         }

@@ -50,7 +50,63 @@ __device__ __forceinline__ double cbrt_cr(double x) {
 
 __device__ __forceinline__ double sig64(double x) { return 1.0 / (1.0 + exp(-x)); }
 __device__ __forceinline__ double tanh64(double x) { return 2 / (1 + exp(-x * 2)) - 1; }
-__device__ __forceinline__ float tanh32(float x) { return float(2 / (1 + exp(double(-x * 2))) - 1); }
+__device__ __forceinline__ float tanh32_literal(float x) { return float(2 / (1 + exp(double(-x * 2))) - 1); }
+// exp(t) for |t| <= 40 without the library routine's range checks and special cases: k = round(t / ln 2) by the 1.5 * 2^52
+// trick, a two-step Cody-Waite reduction, the Taylor polynomial of degree 12 on |f| <= ln 2 / 2 (truncation below 2^-51
+// relative; for tiny t the last step 1 + f * p rounds once, i.e. correctly) and 2^k added into the exponent field (the
+// result stays far from the ends of the exponent range).
+__device__ __forceinline__ double nk_exp_reduced(double t) {
+    const double magic = 6755399441055744.0;
+    const double kd = fma(t, 1.4426950408889634074, magic);
+    const int k = __double2loint(kd);
+    const double kf = kd - magic;
+    double f = fma(kf, -6.93147180369123816490e-01, t);
+    f = fma(kf, -1.90821492927058770002e-10, f);
+    double p = 2.08767569878680989792e-09;            // 1/12!
+    p = fma(p, f, 2.50521083854417187751e-08);        // 1/11!
+    p = fma(p, f, 2.75573192239858906526e-07);        // 1/10!
+    p = fma(p, f, 2.75573192239858906526e-06);        // 1/9!
+    p = fma(p, f, 2.48015873015873015873e-05);        // 1/8!
+    p = fma(p, f, 1.98412698412698412698e-04);        // 1/7!
+    p = fma(p, f, 1.38888888888888888889e-03);        // 1/6!
+    p = fma(p, f, 8.33333333333333333333e-03);        // 1/5!
+    p = fma(p, f, 4.16666666666666666667e-02);        // 1/4!
+    p = fma(p, f, 1.66666666666666666667e-01);        // 1/3!
+    p = fma(p, f, 0.5);
+    p = fma(p, f, 1.0);
+    p = fma(p, f, 1.0);
+    return __hiloint2double(__double2hiint(p) + (k << 20), __double2loint(p));
+}
+// The reference's F32 tanh, (float)(2 / (1 + Math.exp(-2x)) - 1) evaluated in double (ScalarTanh.java:24-25). The literal
+// form above is bound by instruction issue, not by the FP64 pipe: 75 instructions per element, most of them integer and
+// branch work inside the library's exp and the division's fix-up path. tanh32_fast performs the same operations in the
+// same order -- exp, 1 + E, 2 / d, - 1, round to float -- with the lean exp and a quotient made of a hardware reciprocal seed
+// and two Newton steps: 22 double-precision instructions, straight-line. Both intermediate results are within a few units
+// in the last place of a double of the exactly rounded ones, far below the float rounding, so the float result is the
+// literal form's except where the double value falls within ~2^-48 of a float rounding boundary (one ulp then; all 2^32
+// inputs are checked against the CPU oracle). That margin does not exist for |x| < 2^-26, where the result is the
+// cancellation residue of 2 / d - 1 and near-ties of the quotient decide it, nor for NaN (the clamp swallows it):
+// tanh32_rare names those inputs, and they take the literal form. Kernels that evaluate several elements per thread call
+// the two halves separately (all fast values first, fix-ups after), so that the elements are evaluated side by side and
+// share every constant; with the branch between elements the constants were rebuilt in registers for each one.
+__device__ __forceinline__ float tanh32_fast(float x) {
+    // beyond |2x| = 40 the formula gives exactly -1 / +1 in float; the clamp keeps the scaling inside the exponent range
+    const float t = fminf(fmaxf(x * -2.0f, -40.0f), 40.0f);
+    const double d = 1.0 + nk_exp_reduced(double(t));
+    double r;
+    asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(r) : "d"(d));
+    double e = fma(-d, r, 1.0);
+    r = fma(r, e, r);
+    e = fma(-d, r, 1.0);
+    r = fma(r, e, r);
+    return float(fma(2.0, r, -1.0));   // 2r is exact, so this is (2 / d) - 1 with the one rounding the subtraction has
+}
+__device__ __forceinline__ bool tanh32_rare(float x) { return !(fabsf(x) >= 1.490116119384765625e-08f); }
+__device__ __forceinline__ float tanh32(float x) {
+    float y = tanh32_fast(x);
+    if (tanh32_rare(x)) y = tanh32_literal(x);
+    return y;
+}
 __device__ __forceinline__ double softsign64(double x) { return x / (1.0 + fabs(x)); }
 __device__ __forceinline__ float softsign32(float x) { return x / (1.0f + fabsf(x)); }
 __device__ __forceinline__ double selu64(double x) {
