@@ -169,6 +169,19 @@ __device__ __forceinline__ T nk_eval(const T* x) {
     return nk_expr(x[0], NK_NIN > 1 ? x[NK_NIN > 1 ? 1 : 0] : T(0), NK_NIN > 2 ? x[NK_NIN > 2 ? 2 : 0] : T(0), NK_NIN > 3 ? x[NK_NIN > 3 ? 3 : 0] : T(0),
                    NK_NIN > 4 ? x[NK_NIN > 4 ? 4 : 0] : T(0), NK_NIN > 5 ? x[NK_NIN > 5 ? 5 : 0] : T(0));
 }
+// The same expression with the straight-line F32 tanh (nkf::tanh32_fast): inputs that form is not valid for are reported
+// through nk_rare instead of branching, so that the elements of a vector are evaluated side by side; the rows kernel
+// repeats a vector with the exact form above if any of its elements reported. Without a tanh, or in F64, nk_rare stays
+// false and the two forms are the same code.
+__device__ __forceinline__ double nk_tanh_flagged(double a, bool&) { return nkf::fun(NK_FUN_TANH, false, a); }
+__device__ __forceinline__ float nk_tanh_flagged(float a, bool& rare) { rare = rare || nkf::tanh32_rare(a); return nkf::tanh32_fast(a); }
+#define f_tanh(a) nk_tanh_flagged((a), nk_rare)
+__device__ __forceinline__ T nk_expr_fast(T x0, T x1, T x2, T x3, T x4, T x5, bool& nk_rare) { return NK_EXPR; }
+#undef f_tanh
+__device__ __forceinline__ T nk_eval_fast(const T* x, bool& rare) {
+    return nk_expr_fast(x[0], NK_NIN > 1 ? x[NK_NIN > 1 ? 1 : 0] : T(0), NK_NIN > 2 ? x[NK_NIN > 2 ? 2 : 0] : T(0), NK_NIN > 3 ? x[NK_NIN > 3 ? 3 : 0] : T(0),
+                        NK_NIN > 4 ? x[NK_NIN > 4 ? 4 : 0] : T(0), NK_NIN > 5 ? x[NK_NIN > 5 ? 5 : 0] : T(0), rare);
+}
 
 // Rows form. Rows are dealt to CTAs in contiguous blocks; a CTA decodes its first row with one division and then walks
 // row by row with an odometer over the (one or two) outer dims -- adds and compares only. Within a row the threads
@@ -239,12 +252,22 @@ __device__ __forceinline__ void nk_fused_rows(const FusedRows& a) {
             for (int u = 0; u < NK_RPT; u++) {
                 if (!ok[u]) continue;
                 T res[VECW];
+                bool rare = false;
 #pragma unroll
                 for (int e = 0; e < VECW; e++) {
                     T in[NK_NIN];
 #pragma unroll
                     for (int j = 0; j < NK_NIN; j++) in[j] = x[u][j][e];
-                    res[e] = nk_eval(in);
+                    res[e] = nk_eval_fast(in, rare);
+                }
+                if (rare) {
+#pragma unroll
+                    for (int e = 0; e < VECW; e++) {
+                        T in[NK_NIN];
+#pragma unroll
+                        for (int j = 0; j < NK_NIN; j++) in[j] = x[u][j][e];
+                        res[e] = nk_eval(in);
+                    }
                 }
                 __stcs(reinterpret_cast<V*>(out + q0[u]) + c, *reinterpret_cast<V*>(res));
             }

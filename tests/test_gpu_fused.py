@@ -49,6 +49,24 @@ def test_fused_equals_op_by_op_bit_for_bit(device, dt, expr, shapes):
     fused.close()
 
 
+def test_fused_tanh_on_tiny_inputs_zeros_infinities_and_nans(device):
+    """The F32 tanh has a straight-line form for ordinary inputs and the literal formula for |x| < 2^-26 and NaN; the fused
+    kernel evaluates a vector with the first and repeats it with the second when an element asks for it. Vectors that mix
+    both kinds must give the operator kernel's bits."""
+    special = np.asarray([0.0, -0.0, 1e-9, -1e-9, 1.4e-45, 3e-39, 1.4901161e-08, 1.49e-08, np.inf, -np.inf, np.nan, 1e-20,
+                          0.5, -0.5, 20.0, -20.5, 88.0, 1e30, -1e30, 2.0 ** -27], dtype=np.float32)
+    rng = np.random.default_rng(5)
+    x = rng.uniform(-3, 3, 4096).astype(np.float32)
+    x[rng.choice(4096, 400, replace=False)] = rng.choice(special, 400)
+    t = Tensor.of(np.float32, [16, 256], x).to(device)
+    one = Tensor.of(np.float32, [1, 256], np.ones(256, dtype=np.float32)).to(device)
+    f = Function.of("tanh(i0*i1)", False)
+    fused = device.optimized_operation_of(f, "tanh_special")
+    got, want = fused(t, one), f(t, one)
+    assert _same_bits(got.items, want.items)
+    fused.close()
+
+
 def test_fused_on_views_and_against_the_oracle(device, oracle):
     """A strided slice and a permuted operand; and the fused tanh(a*b+b) against the CPU restatement (<= 1 ulp)."""
     rng = np.random.default_rng(42)
