@@ -1,7 +1,7 @@
 """The tensor-core (tcgen05, 3xTF32) family for F32 contraction-shaped calls, through nk_conv, against the CPU oracle.
 
 Tolerance: the convolution bound of the path, |gpu - oracle| <= 1e-5 * sum|a||b| per element, no extra factor
-(test_gpu_conv.check_conv). The split keeps 22 significant bits per operand, so the error is expected around 1e-6 of
+(test_gpu_conv.check_conv). The split keeps 22 significant bits per operand, so the error is expected near 1e-6 of
 that magnitude; the tests record nothing looser than the stated bound."""
 import numpy as np
 import pytest
