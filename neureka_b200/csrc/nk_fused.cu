@@ -16,6 +16,7 @@
 
 #include <dlfcn.h>
 
+#include <cstring>
 #include <string>
 #include <vector>
 
@@ -274,8 +275,10 @@ __device__ __forceinline__ void nk_fused_rows(const FusedRows& a) {
         }
     }
 }
-extern "C" __global__ void __launch_bounds__(256) nk_fused_rows1(const FusedRows a) { nk_fused_rows<1>(a); }
-extern "C" __global__ void __launch_bounds__(256) nk_fused_rows2(const FusedRows a) { nk_fused_rows<2>(a); }
+// NK_MIN_CTAS: 3 for expressions made of operators only -- a pure stream, where three resident CTAs per SM (24 warps' worth of
+// loads and stores in flight) matter more than registers; 1 when scalar functions are called (their evaluation wants them).
+extern "C" __global__ void __launch_bounds__(256, NK_MIN_CTAS) nk_fused_rows1(const FusedRows a) { nk_fused_rows<1>(a); }
+extern "C" __global__ void __launch_bounds__(256, NK_MIN_CTAS) nk_fused_rows2(const FusedRows a) { nk_fused_rows<2>(a); }
 
 extern "C" __global__ void __launch_bounds__(256) nk_fused_kernel(const FusedFlat a) {
     T* out = reinterpret_cast<T*>(a.out);
@@ -464,7 +467,9 @@ extern "C" int nk_fused_compile(nk_ctx* ctx, int32_t dtype, int32_t n_inputs, co
     if (!expr || !*expr) return nk_fail(ctx, NK_ERR_BAD_ARG, "nk_fused_compile: empty expression");
     nk_fused* f = new (std::nothrow) nk_fused();
     if (!f) return nk_fail(ctx, NK_ERR_OOM, "nk_fused_compile: out of host memory");
-    int st = compile_unit(ctx, "nk_fused_compile", dtype, n_inputs, std::string("#define NK_EXPR (") + expr + ")\n", k_forward_src, &f->lib);
+    const bool calls_functions = strstr(expr, "f_") != nullptr || strstr(expr, "op_pow") != nullptr || strstr(expr, "op_mod") != nullptr;
+    const std::string defs = std::string("#define NK_EXPR (") + expr + ")\n#define NK_MIN_CTAS " + (calls_functions ? "1" : "3") + "\n";
+    int st = compile_unit(ctx, "nk_fused_compile", dtype, n_inputs, defs, k_forward_src, &f->lib);
     if (st) { delete f; return st; }
     cudaError_t e = cudaLibraryGetKernel(&f->kernel, f->lib, "nk_fused_kernel");
     if (e == cudaSuccess) e = cudaLibraryGetKernel(&f->rows1, f->lib, "nk_fused_rows1");
