@@ -533,6 +533,9 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                 unsigned cur_bytes = chunk_bytes(rh_cur);
                 const CUtensorMap* cur_map = &tmaps.m[nk_tmap_slot(rh_cur)];
                 int c = c_begin + issued;   // the first loads of the first chunk were requested in the prologue
+                // stage and round parity of load number `issued`, counted along instead of divided out (STAGES may be 3)
+                int pstage = issued == STAGES ? 0 : issued;
+                unsigned pround = issued == STAGES ? 1u : 0u;
                 while (ok) {
                     if (c >= c_end) {
                         chunk_no++;
@@ -567,8 +570,9 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                         c = c_begin;
                         announce = true;
                     }
-                    const int stage = issued % STAGES;
-                    if (issued >= STAGES) ok = wait_or_abort(&empty_bar[stage], unsigned(issued / STAGES - 1) & 1u);
+                    const int stage = pstage;
+                    if (issued >= STAGES) ok = wait_or_abort(&empty_bar[stage], (pround & 1u) ^ 1u);
+                    if (++pstage == STAGES) { pstage = 0; pround++; }
                     if (ok) {
                         if (RING && announce) {
                             // every compute warp is past the chunk whose entry this overwrites (ring of STAGES + 1, at least
@@ -591,7 +595,8 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                 }
             }
         } else {
-            int g = 0;   // loads consumed so far, same numbering as the producer's
+            int cstage = 0;        // stage and round parity of the next load to consume (same numbering as the producer's)
+            unsigned cpar = 0;
             bool ok = true;
             // the channel loop of one chunk, specialised on the rows per warp: the choice sits outside the loop, so the
             // loop body is straight-line code the compiler can schedule across iterations, as for a fixed tile height
@@ -600,8 +605,8 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                     // one image tile (a single channel), every weight set in turn: multiply-adds, store, clear. The
                     // stage goes back to the producer after the last set's multiply-adds.
                     constexpr int RHC = decltype(rows_tag)::value;
-                    const int stage = g % STAGES;
-                    if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; return; }
+                    const int stage = cstage;
+                    if (!wait_or_abort(&full_bar[stage], cpar)) { ok = false; return; }
                     // where this thread's rows go does not depend on the weight set: worked out once per chunk
                     const int ox = x0 + lane * CW;
                     const bool fast = p.vec_out != 0 && ox >= 0 && ox + CW <= p.OW;   // whole 16-byte stores
@@ -636,14 +641,15 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
 #pragma unroll
                             for (int x = 0; x < CW; x++) acc[i][x] = T(0);
                     }
-                    g++;
+                    if (++cstage == STAGES) { cstage = 0; cpar ^= 1u; }
                 } else {
-                    for (int c = c_begin; c < c_end; c++, g++) {
-                        const int stage = g % STAGES;
-                        if (!wait_or_abort(&full_bar[stage], unsigned(g / STAGES) & 1u)) { ok = false; break; }
+                    for (int c = c_begin; c < c_end; c++) {
+                        const int stage = cstage;
+                        if (!wait_or_abort(&full_bar[stage], cpar)) { ok = false; break; }
                         consume(rows_tag, stage_base + size_t(stage) * C::STAGE_BYTES, c);
                         __syncwarp();
                         if (lane == 0) nk_mbar_arrive(&empty_bar[stage]);
+                        if (++cstage == STAGES) { cstage = 0; cpar ^= 1u; }
                     }
                 }
             };
@@ -656,7 +662,7 @@ __global__ void __launch_bounds__(TMA ? 288 : 256) nk_conv_tiled_kernel(T* __res
                     if (RING) {
                         // where this tile lives: published by the producer before the tile's first load, so wait for that
                         // load (the loop below finds it complete) and pick the entry up
-                        if (!wait_or_abort(&full_bar[g % STAGES], unsigned(g / STAGES) & 1u)) { ok = false; break; }
+                        if (!wait_or_abort(&full_bar[cstage], cpar)) { ok = false; break; }
                         const int4* e = tinfo + 2 * (chunk_no % (STAGES + 1));
                         place(e[0], e[1]);
                     } else {
