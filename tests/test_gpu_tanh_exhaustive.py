@@ -24,33 +24,38 @@ def _chunk(i):
     return np.arange(i * CHUNK, (i + 1) * CHUNK, dtype=np.uint64).astype(np.uint32).view(np.float32)
 
 
-def test_tanh_f32_on_all_float_bit_patterns(device, oracle):
+def _sweep(device, oracle, fun, d, step, max_ulp=1):
+    """fun (d = -1 forward, 0 derivative) on the bit patterns 0, step, 2 step, ...; returns how many results differ."""
     cfg = ND.of_shape([CHUNK])
     inline = cfg.as_inline_array()
     differing = 0
     want = np.empty(CHUNK, dtype=np.float32)
-    for i in range((1 << 32) // CHUNK):
-        x = _chunk(i)
-        got = gpu_unary(device, L.FUN["tanh"], np.empty(CHUNK, dtype=np.float32), cfg, x, cfg)
-        oracle.unary("tanh", want, inline, x, inline, threads=16)
+    for i in range((1 << 32) // (CHUNK * step)):
+        x = (np.arange(i * CHUNK, (i + 1) * CHUNK, dtype=np.uint64) * step).astype(np.uint32).view(np.float32)
+        got = gpu_unary(device, L.FUN[fun], np.empty(CHUNK, dtype=np.float32), cfg, x, cfg, d=d)
+        oracle.unary(fun, want, inline, x, inline, d=d, threads=16)
         gi, wi = got.view(np.int32), want.view(np.int32)
         idx = np.flatnonzero(gi != wi)                      # few, or a block of NaNs whose payloads differ
         if idx.size == 0:
             continue
-        nan_in = np.isnan(x[idx])
-        assert np.array_equal(np.isnan(got[idx]), nan_in) and np.array_equal(np.isnan(want[idx]), nan_in), f"NaN pattern differs in chunk {i}"
-        idx = idx[~nan_in]
+        nan_w = np.isnan(want[idx])
+        assert np.array_equal(np.isnan(got[idx]), nan_w), f"{fun} d={d}: NaN pattern differs in chunk {i}"
+        idx = idx[~nan_w]
         if idx.size:
-            d = ulp_diff(got[idx], want[idx])
-            assert d.max() <= 1, f"chunk {i}: {d.max()} ulp at x = {x[idx[int(d.argmax())]]!r}"
+            dd = ulp_diff(got[idx], want[idx])
+            assert dd.max() <= max_ulp, f"{fun} d={d} chunk {i}: {dd.max()} ulp at x = {x[idx[int(dd.argmax())]]!r}"
             differing += idx.size
     # the NaN inputs themselves (equal bit patterns pass the filter above only if both sides are NaN or both are not)
     for bits in (0x7fc00000, 0xffc00000, 0x7f800001, 0xff812345):
         x = np.full(16, bits, dtype=np.uint32).view(np.float32)
         c = ND.of_shape([16])
-        assert np.isnan(gpu_unary(device, L.FUN["tanh"], np.zeros(16, dtype=np.float32), c, x, c)).all()
-    # measured: a few hundred of 4 294 967 296; the bound leaves room for another libm on the host
-    assert differing <= 1 << 16, differing
+        assert np.isnan(gpu_unary(device, L.FUN[fun], np.zeros(16, dtype=np.float32), c, x, c, d=d)).all()
+    return differing
+
+
+def test_tanh_f32_on_all_float_bit_patterns(device, oracle):
+    # measured: a few hundred of 4 294 967 296 differ (by one ulp); the bound leaves room for another libm on the host
+    assert _sweep(device, oracle, "tanh", -1, 1) <= 1 << 16
 
 
 def test_tanh_derivative_f32_on_a_dense_sample_of_bit_patterns(device, oracle):
