@@ -100,15 +100,18 @@ template <class T, int OP> struct ScalarFix {
 // Functors whose function has a straight-line form for all but a few inputs: the kernels evaluate fast() for every element
 // of a vector first and repair the rare ones afterwards (see tanh32_fast in nk_scalarfun.cuh for why).
 template <class F> struct TwoPhase { static constexpr bool value = false; };
-template <bool DERIVE> struct TwoPhase<UnaryFix<float, NK_FUN_TANH, DERIVE>> {
-    static constexpr bool value = true;
+template <int FUN, bool DERIVE> struct TwoPhase<UnaryFix<float, FUN, DERIVE>> {
+    // tanh (and its derivative): fast form + literal repair; sig, silu, gelu forward: straight-line already, they only want
+    // the kernel loop that keeps the next loads in flight under their arithmetic
+    static constexpr bool value = FUN == NK_FUN_TANH || (!DERIVE && (FUN == NK_FUN_SIG || FUN == NK_FUN_SILU || FUN == NK_FUN_GELU));
     static __device__ __forceinline__ float fast(float a) {
+        if (FUN != NK_FUN_TANH) return nkf::fun(FUN, DERIVE, a);
         const float t = nkf::tanh32_fast(a);
         if (!DERIVE) return t;
         const double td = double(t);
         return float(1 - td * td);
     }
-    static __device__ __forceinline__ bool rare(float a) { return nkf::tanh32_rare(a); }
+    static __device__ __forceinline__ bool rare(float a) { return FUN == NK_FUN_TANH && nkf::tanh32_rare(a); }
 };
 // out[k] = f(a[k], b[k]) for the N elements of one vector
 template <class T, int N, int NIN, class F>

@@ -51,10 +51,10 @@ __device__ __forceinline__ double cbrt_cr(double x) {
 __device__ __forceinline__ double sig64(double x) { return 1.0 / (1.0 + exp(-x)); }
 __device__ __forceinline__ double tanh64(double x) { return 2 / (1 + exp(-x * 2)) - 1; }
 __device__ __forceinline__ float tanh32_literal(float x) { return float(2 / (1 + exp(double(-x * 2))) - 1); }
-// exp(t) for |t| <= 40 without the library routine's range checks and special cases: k = round(t / ln 2) by the 1.5 * 2^52
+// exp(t) for |t| <= 700 without the library routine's range checks and special cases: k = round(t / ln 2) by the 1.5 * 2^52
 // trick, a two-step Cody-Waite reduction, the Taylor polynomial of degree 12 on |f| <= ln 2 / 2 (truncation below 2^-51
 // relative; for tiny t the last step 1 + f * p rounds once, i.e. correctly) and 2^k added into the exponent field (the
-// result stays far from the ends of the exponent range).
+// result stays inside the normal exponent range).
 __device__ __forceinline__ double nk_exp_reduced(double t) {
     const double magic = 6755399441055744.0;
     const double kd = fma(t, 1.4426950408889634074, magic);
@@ -106,6 +106,33 @@ __device__ __forceinline__ float tanh32(float x) {
     float y = tanh32_fast(x);
     if (tanh32_rare(x)) y = tanh32_literal(x);
     return y;
+}
+// The sigmoid inside the F32 functions sig, silu and gelu: 1 / (1 + Math.exp(-a)) in double (ScalarSigmoid.java,
+// ScalarSiLU.java, ScalarGeLU.java), evaluated like tanh32_fast -- lean exp, Newton reciprocal, straight line, no
+// cancellation and therefore no literal branch. `a` must lie within +-700 (the lean exp's exponent arithmetic); the callers
+// clamp the float they start from, which changes no float result: the sigmoid is 1 to the last bit above 37, and below
+// -700 it and its product with any float underflow to zero. The clamp swallows a NaN, and -inf * 0 is a NaN in silu and
+// gelu: the callers put those back. All 2^32 inputs of sig, every 16th of silu and gelu were checked against the oracle.
+__device__ __forceinline__ double sig_lean(double a) {
+    const double d = 1.0 + nk_exp_reduced(-a);
+    double r;
+    asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(r) : "d"(d));
+    double e = fma(-d, r, 1.0);
+    r = fma(r, e, r);
+    e = fma(-d, r, 1.0);
+    return fma(r, e, r);
+}
+__device__ __forceinline__ float sig32(float x) {
+    const float y = float(sig_lean(double(fminf(fmaxf(x, -700.0f), 700.0f))));
+    return x != x ? x + x : y;
+}
+__device__ __forceinline__ float silu32(float x) {
+    const float y = float(double(x) * sig_lean(double(fminf(fmaxf(x, -700.0f), 700.0f))));
+    return (x != x || x == __int_as_float(0xff800000)) ? x - x : y;
+}
+__device__ __forceinline__ float gelu32(float x) {
+    const float y = float(double(x) * sig_lean(double(fminf(fmaxf(x, -411.0f), 411.0f)) * 1.702));
+    return (x != x || x == __int_as_float(0xff800000)) ? x - x : y;
 }
 __device__ __forceinline__ double softsign64(double x) { return x / (1.0 + fabs(x)); }
 __device__ __forceinline__ float softsign32(float x) { return x / (1.0f + fabsf(x)); }
@@ -183,14 +210,14 @@ __device__ __forceinline__ float fun(int f, bool derive, float x) {
         case NK_FUN_GASU: return softsign32(x * x * x);
         case NK_FUN_GATU: return tanh32(x * x * x);
         case NK_FUN_FAST_GAUS: return 1 / (1 + x * x);
-        case NK_FUN_GELU: return float(double(x) * sig64(double(x) * 1.702));
+        case NK_FUN_GELU: return gelu32(x);
         case NK_FUN_IDY: return x;
         case NK_FUN_LOG10: return float(log10(double(x)));
         case NK_FUN_QUAD: return x * x;
         case NK_FUN_RELU: return x >= 0 ? x : x * .01f;
         case NK_FUN_SELU: return float(selu64(double(x)));
-        case NK_FUN_SILU: return float(double(x) * sig64(double(x)));
-        case NK_FUN_SIG: return float(sig64(double(x)));
+        case NK_FUN_SILU: return silu32(x);
+        case NK_FUN_SIG: return sig32(x);
         case NK_FUN_SOFTSIGN: return softsign32(x);
         case NK_FUN_SQRT: return float(sqrt(double(x)));
         case NK_FUN_TANH: return tanh32(x);

@@ -1,4 +1,4 @@
-"""Every one of the 2^32 float bit patterns through the device's F32 tanh.
+"""Every one of the 2^32 float bit patterns through the device's F32 tanh and sigmoid.
 
 The reference defines tanh on floats as (float)(2 / (1 + Math.exp(-2x)) - 1) evaluated in double
 (backend/main/implementations/fun/ScalarTanh.java:24-25). The device evaluates the same sequence of operations with a lean
@@ -56,6 +56,17 @@ def _sweep(device, oracle, fun, d, step, max_ulp=1):
 def test_tanh_f32_on_all_float_bit_patterns(device, oracle):
     # measured: a few hundred of 4 294 967 296 differ (by one ulp); the bound leaves room for another libm on the host
     assert _sweep(device, oracle, "tanh", -1, 1) <= 1 << 16
+
+
+def test_sigmoid_f32_on_all_float_bit_patterns(device, oracle):
+    """1 / (1 + Math.exp(-x)) in double (ScalarSigmoid.java), evaluated with the same lean exp and Newton reciprocal."""
+    assert _sweep(device, oracle, "sig", -1, 1) <= 1 << 16
+
+
+@pytest.mark.parametrize("fun", ["silu", "gelu"])
+def test_silu_and_gelu_f32_on_every_16th_bit_pattern(device, oracle, fun):
+    """x * sig(x) and x * sig(1.702 x) (ScalarSiLU.java, ScalarGeLU.java) on the same sigmoid; -inf gives NaN (-inf * 0)."""
+    assert _sweep(device, oracle, fun, -1, 16) <= 1 << 14
 
 
 def test_tanh_derivative_f32_on_a_dense_sample_of_bit_patterns(device, oracle):
