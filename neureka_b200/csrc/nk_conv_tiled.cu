@@ -106,6 +106,77 @@ static bool nk_describe_for_tma(const nk_buf* buf, const NkView& v, size_t es, b
     return n >= 2 && n <= 5;
 }
 
+// ---- staging of operands a tensor map cannot describe ----------------------------------------------------------------
+// A tensor map wants a 16-byte aligned base and strides that are multiples of 16 bytes; a tensor of, say, 126 floats per row
+// has neither. Such an operand of a deconvolution is copied once into a dense block whose rows are padded to 16 bytes and
+// the TMA kernels read the copy: for the error tensor of an image gradient that is 1/channels of the traffic, against a
+// fallback to the gather family that measured 20 times slower. The block comes from the device's stream-ordered pool:
+// copy, kernel and release all queue on the context's stream.
+struct StageDims {
+    int rank;
+    long long total, base;
+    long long div[NK_MAX_RANK], sstride[NK_MAX_RANK], dstride[NK_MAX_RANK];
+};
+template <class T>
+__global__ void __launch_bounds__(256) nk_stage_kernel(T* __restrict__ dst, const T* __restrict__ src, StageDims d) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < d.total; i += stride) {
+        long long rem = i, so = d.base, dof = 0;
+        for (int k = 0; k < d.rank; k++) {
+            const long long idx = rem / d.div[k];
+            rem -= idx * d.div[k];
+            so += idx * d.sstride[k];
+            dof += idx * d.dstride[k];
+        }
+        dst[dof] = src[so];
+    }
+}
+struct Staged {
+    nk_buf buf;     // stands in for the operand's handle (pointer, dtype, device)
+    NkView view;    // dense, rows padded to 16 bytes, base 0
+    bool used = false;
+};
+static int nk_stage_operand(nk_ctx* ctx, int dtype, const nk_buf* src, const NkView& v, Staged* out) {
+    const size_t es = nk_dtype_size(dtype);
+    const int rank = v.rank, X = rank - 1;
+    const int64_t cw = int64_t(16 / es);
+    const int64_t pitch = ((v.shape[X] + cw - 1) / cw) * cw;
+    StageDims d;
+    memset(&d, 0, sizeof(d));
+    d.rank = rank;
+    d.base = v.base;
+    out->view = v;
+    out->view.base = 0;
+    int64_t ds = 1, dv = 1;
+    for (int k = rank - 1; k >= 0; k--) {
+        d.div[k] = dv;
+        dv *= v.shape[k];
+        d.sstride[k] = v.estride[k];
+        d.dstride[k] = ds;
+        out->view.estride[k] = ds;
+        ds *= (k == X) ? pitch : v.shape[k];
+    }
+    d.total = dv;
+    out->view.dense_row_major = pitch == v.shape[X];
+    if (ds >= (int64_t(1) << 40)) return -1;
+    void* ptr = nullptr;
+    cudaError_t e = cudaMallocAsync(&ptr, size_t(ds) * es, ctx->stream);
+    if (e != cudaSuccess) { cudaGetLastError(); return -1; }   // no room for a copy: the caller falls back to another family
+    out->buf = *src;
+    out->buf.ptr = ptr;
+    out->buf.n_elems = ds;
+    out->buf.owned = false;
+    out->used = true;
+    const int grid = nk_grid_for(ctx, d.total, 256, 16);
+    if (dtype == NK_F32) nk_stage_kernel<float><<<grid, 256, 0, ctx->stream>>>(static_cast<float*>(ptr), static_cast<const float*>(src->ptr), d);
+    else nk_stage_kernel<double><<<grid, 256, 0, ctx->stream>>>(static_cast<double*>(ptr), static_cast<const double*>(src->ptr), d);
+    return nk_after_launch(ctx, "nk_stage_kernel");
+}
+static void nk_stage_release(nk_ctx* ctx, Staged* s) {
+    if (s->used) cudaFreeAsync(s->buf.ptr, ctx->stream);
+    s->used = false;
+}
+
 // Deconvolution (d >= 0) whose result is the small, kernel-like tensor: D[p] = sum_q T1[p+q] * T2[q] in every dim
 // (the drain is not larger than T1 anywhere), the last one or two dims being a window of few taps over large planes.
 static int nk_wgrad_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, nk_buf* s1, const NkView& v1,
@@ -143,11 +214,26 @@ static int nk_wgrad_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView& v0, n
     p.bD = v0.base;
     const size_t es = nk_dtype_size(dtype);
     TmaImage imgA, imgE;
-    if (!nk_describe_for_tma(s1, v1, es, has_y, n_outer, &imgA)) return NK_OK;
-    if (!nk_describe_for_tma(s2, v2, es, has_y, n_outer, &imgE)) return NK_OK;
-    p.nd = imgA.nd;
-    int st = (dtype == NK_F32) ? nk_wgrad_dispatch_f32(ctx, int(KH), int(KW), (float*)drn->ptr, p, imgA, imgE)
+    Staged stA, stE;
+    bool ok = true;
+    if (!nk_describe_for_tma(s1, v1, es, has_y, n_outer, &imgA)) {
+        const int sst = nk_stage_operand(ctx, dtype, s1, v1, &stA);
+        if (sst > 0) return sst;
+        ok = sst == 0 && nk_describe_for_tma(&stA.buf, stA.view, es, has_y, n_outer, &imgA);
+    }
+    if (ok && !nk_describe_for_tma(s2, v2, es, has_y, n_outer, &imgE)) {
+        const int sst = nk_stage_operand(ctx, dtype, s2, v2, &stE);
+        if (sst > 0) { nk_stage_release(ctx, &stA); return sst; }
+        ok = sst == 0 && nk_describe_for_tma(&stE.buf, stE.view, es, has_y, n_outer, &imgE);
+    }
+    int st = -1;
+    if (ok) {
+        p.nd = imgA.nd;
+        st = (dtype == NK_F32) ? nk_wgrad_dispatch_f32(ctx, int(KH), int(KW), (float*)drn->ptr, p, imgA, imgE)
                                : nk_wgrad_dispatch_f64(ctx, int(KH), int(KW), (double*)drn->ptr, p, imgA, imgE);
+    }
+    nk_stage_release(ctx, &stA);
+    nk_stage_release(ctx, &stE);
     if (st == -1) return NK_OK;
     if (st != NK_OK) return st;
     ctx->last_conv_path = NK_CONV_TMA;
@@ -171,9 +257,10 @@ static int nk_deconv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView
         int st = nk_wgrad_try(ctx, dtype, drn, v0, s1, v1, s2, v2, handled);
         if (st || *handled) return st;
     }
-    const NkView& vi = v2;   // image = T2 (the error)
+    NkView vi = v2;          // image = T2 (the error); replaced by a padded copy below if a tensor map cannot describe it
+    const void* iptr = s2->ptr;
     const NkView& vk = v1;   // weights = T1
-    if (vi.estride[X] != 1 || v0.estride[X] != 1) return NK_OK;
+    if (v0.estride[X] != 1) return NK_OK;
     // sliding dim X: tau = p - q (drain larger than T1), window of s1 taps
     if (!(v0.shape[X] > vk.shape[X])) return NK_OK;
     const int64_t KW = vk.shape[X];
@@ -186,6 +273,21 @@ static int nk_deconv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView
     if (n_outer > 3 || 1 + (has_y ? 1 : 0) + n_outer > 5) return NK_OK;
     const size_t es = nk_dtype_size(dtype);
     const int CW = int(16 / es);
+    Staged staged;
+    {
+        bool describable = vi.estride[X] == 1 && (reinterpret_cast<uintptr_t>(static_cast<const char*>(iptr) + vi.base * int64_t(es)) % 16) == 0;
+        for (int k = 0; k < X && describable; k++)
+            if (vi.shape[k] > 1 && (vi.estride[k] <= 0 || (vi.estride[k] * int64_t(es)) % 16)) describable = false;
+        if (!describable) {
+            // only worth a copy if the window is one the tiled family is instantiated for; the dispatch below decides, and a
+            // wasted copy of the (small) error tensor is cheap next to the gather family it falls back to
+            const int sst = nk_stage_operand(ctx, dtype, s2, v2, &staged);
+            if (sst > 0) return sst;
+            if (sst < 0) return NK_OK;
+            vi = staged.view;
+            iptr = staged.buf.ptr;
+        }
+    }
     TiledPlan p;
     TmaImage img;
     // Builds the plan. with_wloop: outer dims in which the drain follows T1 while T2 has extent 1 (the output channels of
@@ -257,9 +359,9 @@ static int nk_deconv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView
         p.vec_out = vec_out ? 1 : 0;
 
         // tensor map over T2 (the dims of the tile index only)
-        if (!aligned_to(static_cast<const char*>(s2->ptr) + p.bI * int64_t(es), 16)) return false;
+        if (!aligned_to(static_cast<const char*>(iptr) + p.bI * int64_t(es), 16)) return false;
         int n = 0;
-        img.base = static_cast<const char*>(s2->ptr) + p.bI * int64_t(es);
+        img.base = static_cast<const char*>(iptr) + p.bI * int64_t(es);
         img.dims[n] = uint64_t(p.IW); img.strides_bytes[n] = es; n++;
         if (has_y) {
             if (p.sIy <= 0 || (p.sIy * int64_t(es)) % 16) return false;
@@ -285,15 +387,13 @@ static int nk_deconv_tiled_try(nk_ctx* ctx, int dtype, nk_buf* drn, const NkView
         return true;
     };
     auto dispatch = [&]() -> int {
-        if (dtype == NK_F32) return nk_tiled_dispatch_f32_tma4(ctx, int(KH), int(KW), (float*)drn->ptr, (const float*)s2->ptr, (const float*)s1->ptr, p, &img);
-        return nk_tiled_dispatch_f64_tma4(ctx, int(KH), int(KW), (double*)drn->ptr, (const double*)s2->ptr, (const double*)s1->ptr, p, &img);
+        if (dtype == NK_F32) return nk_tiled_dispatch_f32_tma4(ctx, int(KH), int(KW), (float*)drn->ptr, (const float*)iptr, (const float*)s1->ptr, p, &img);
+        return nk_tiled_dispatch_f64_tma4(ctx, int(KH), int(KW), (double*)drn->ptr, (const double*)iptr, (const double*)s1->ptr, p, &img);
     };
     int st = -1;
     if (has_y && build(true)) st = dispatch();          // the weight loop first; -1 = it does not apply (sets too large, no persistent walk)
-    if (st == -1) {
-        if (!build(false)) return NK_OK;
-        st = dispatch();
-    }
+    if (st == -1 && build(false)) st = dispatch();
+    nk_stage_release(ctx, &staged);
     if (st == -1) return NK_OK;
     if (st != NK_OK) return st;
     ctx->last_conv_path = NK_CONV_TMA;

@@ -225,6 +225,39 @@ def test_balanced_walk_gives_the_same_bits_as_one_tile_per_cta(device, oracle, d
 
 
 @pytest.mark.parametrize("dt", [np.float32, np.float64])
+def test_gradients_of_tensors_whose_rows_no_tensor_map_can_describe(device, oracle, dt):
+    """Rows of 127 and 125 elements are no multiple of 16 bytes in either type, so neither the image nor the error can be
+    given to a tensor map as it lies. Both gradients must still run on the TMA families -- on a copy with rows padded to
+    16 bytes -- and agree with the gather family and (sampled) with the oracle."""
+    rng = np.random.default_rng(77)
+    sa, sb = [8, 8, 70, 127], [1, 8, 3, 3]
+    so = [abs(x - y) + 1 for x, y in zip(sa, sb)]
+    a = rng.standard_normal(int(np.prod(sa))).astype(dt)
+    b = rng.standard_normal(int(np.prod(sb))).astype(dt)
+    e = rng.standard_normal(int(np.prod(so))).astype(dt)
+    c0, c1, c2 = ND.of_shape(so), ND.of_shape(sa), ND.of_shape(sb)
+    tol = 1e-5 if dt == np.float32 else 1e-12
+    rngs = np.random.default_rng(78)
+    # image gradient: drain image-shaped, T1 = kernel, T2 = error
+    grad = gpu_conv(device, np.full(c1.size, 777.0, dtype=dt), c1, b, c2, e, c0, d=0)
+    assert device.last_conv_path() == L.NK_CONV_TMA and device.last_kernel().startswith("nk_conv_tiled_kernel<tma"), device.last_kernel()
+    generic = gpu_conv(device, np.zeros(c1.size, dtype=dt), c1, b, c2, e, c0, d=0, path=L.NK_CONV_GENERIC)
+    assert np.abs(grad - generic).max() <= tol * np.abs(generic).max() * 4
+    check_against_oracle_sampled(oracle, dt, grad, c1, b, c2, e, c0, 0, rngs, n_ranges=3, span=40)
+    # kernel gradient: drain kernel-shaped, T1 = image, T2 = error
+    gk = gpu_conv(device, np.full(c2.size, 777.0, dtype=dt), c2, a, c1, e, c0, d=0)
+    assert device.last_conv_path() == L.NK_CONV_TMA and device.last_kernel() == "nk_conv_wgrad_finish_kernel", device.last_kernel()
+    gk_generic = gpu_conv(device, np.zeros(c2.size, dtype=dt), c2, a, c1, e, c0, d=0, path=L.NK_CONV_GENERIC)
+    assert np.abs(gk - gk_generic).max() <= tol * 8 * np.abs(gk_generic).max()
+    # the same tensors as strided views of wider parents: still one padded copy, same numbers
+    par = np.zeros([8, 1, 68, 200], dtype=dt)
+    par[..., 3:128] = e.reshape(so)
+    cpar = ND.of_shape([8, 1, 68, 200]).sliced(so, [0, 0, 0, 3], [1, 1, 1, 1])
+    grad_v = gpu_conv(device, np.full(c1.size, 777.0, dtype=dt), c1, b, c2, par.ravel(), cpar, d=0)
+    assert np.array_equal(grad_v, grad)
+
+
+@pytest.mark.parametrize("dt", [np.float32, np.float64])
 @pytest.mark.parametrize("case", [
     ([32, 64, 256], [32, 3, 3], 8), ([16, 70, 132], [16, 5, 5], 4), ([24, 50, 260], [24, 3, 3], 6),
     ([2, 16, 40, 128], [1, 16, 3, 3], 4), ([64, 40, 256], [64, 3, 3], 16),
