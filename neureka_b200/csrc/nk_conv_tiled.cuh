@@ -153,9 +153,10 @@ template <int N> struct NkRows { static constexpr int value = N; };
 // partial wave comes from a table in shared memory, not from arithmetic in registers).
 // The 4-rows-per-thread F32 kernels fit three CTAs per SM (three stages of 19 KB each) if their registers allow it: 72
 // instead of the 92-94 the compiler takes by itself, without spills (measured 2-6 % faster on short images and their
-// gradients).
+// gradients). Every other instantiation passes 0 = no statement: an explicit 1 makes the compiler spend registers freely
+// (the 8-row F32 5x5 kernel went from 96 to 111 and lost its second CTA per SM: 0.99 -> 1.22 ms on config 5).
 template <class T, int KH, int KW, int RH, bool TMA, int MODE = NK_TILED_PLAIN>
-__global__ void __launch_bounds__(TMA ? 288 : 256, (TMA && RH == 4 && sizeof(T) == 4) ? 3 : 1) nk_conv_tiled_kernel(T* __restrict__ out, T* __restrict__ partial,
+__global__ void __launch_bounds__(TMA ? 288 : 256, (TMA && RH == 4 && sizeof(T) == 4) ? 3 : 0) nk_conv_tiled_kernel(T* __restrict__ out, T* __restrict__ partial,
                                                             const T* __restrict__ I, const T* __restrict__ K,
                                                             const TiledPlan p, const __grid_constant__ TmapSet tmaps) {
     using C = TiledCfg<T, KH, KW, RH>;
